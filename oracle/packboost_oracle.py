@@ -1,0 +1,737 @@
+"""CPU oracle for the PackBoost training / prediction hot path.
+
+TEST INFRASTRUCTURE ONLY.  This module is a CPU restatement (numpy + torch CPU
+ops) of the reference's torch frontier.  It exists so that the CUDA path can be
+checked against known-good answers and so that a CPU baseline can be timed on
+the same workload.  Nothing in the shipped package imports it: only the tests,
+the smoke check and the CPU-baseline / reference legs of the benchmark do.
+
+Parity status: PINNED.  ``tests/golden/make_golden.py`` runs the unmodified
+reference (``device="cpu"``, no native backend) and stores its trees and
+predictions; ``tests/test_oracle_golden.py`` requires this restatement to
+reproduce those fixtures bit-for-bit (tree structure exactly, leaf values and
+predictions exactly as float32/float64 bit patterns).
+
+Every function cites the reference lines it restates (paths are relative to the
+reference project root).  The reference builds B identical trees per round (it
+has no per-tree randomness and de-duplicates identical frontier nodes,
+``packboost/booster.py:1670-1682,2128-2131``); the oracle therefore grows one
+tree per round and records it ``pack_size`` times, and the golden fixtures prove
+that this is what the reference produces.
+
+The arithmetic order matters for bit-exactness and is kept identical to the
+reference: float32 ``torch.bincount`` sums in (node, era, row) order, float32
+``cumsum`` along bins, float32 ``sum`` for era totals, a sequential weighted
+Welford recursion over eras, and float64 scalar arithmetic for leaf values.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Iterable, Sequence
+
+import numpy as np
+import torch
+
+
+# --------------------------------------------------------------------------
+# parameters
+# --------------------------------------------------------------------------
+
+@dataclass
+class OracleParams:
+    """Hyper-parameters of the path (``packboost/config.py:68-90``)."""
+
+    pack_size: int = 8
+    max_depth: int = 6
+    learning_rate: float = 0.1
+    lambda_l2: float = 1e-6
+    lambda_dro: float = 0.0
+    direction_weight: float = 0.0
+    min_samples_leaf: int = 20
+    max_bins: int = 63
+    k_cuts: int = 0
+    cut_selection: str = "mass"
+    layer_feature_fraction: float = 1.0
+    era_alpha: float = 0.0
+    feature_block_size: int = 32
+    random_state: int | None = None
+    prebinned: bool = False
+    # ``max_bins`` above 128 is refused by the reference (int8 storage,
+    # ``packboost/booster.py:394-395``, ``packboost/data.py:47-48``).  The
+    # widened oracle stores codes as int16 instead and is otherwise identical.
+    allow_wide_bins: bool = False
+
+    @classmethod
+    def from_config(cls, cfg, **extra) -> "OracleParams":
+        names = [f for f in cls.__dataclass_fields__ if f != "allow_wide_bins"]
+        kw = {n: getattr(cfg, n) for n in names if hasattr(cfg, n)}
+        kw.update(extra)
+        return cls(**kw)
+
+
+# --------------------------------------------------------------------------
+# binning (packboost/data.py)
+# --------------------------------------------------------------------------
+
+def detect_prebinned(X: np.ndarray, max_bins: int) -> bool:
+    """Integer input whose values already are bin ids (``data.py:32-42``)."""
+    if not np.issubdtype(X.dtype, np.integer):
+        return False
+    if X.min(initial=0) < 0:
+        return False
+    top = int(X.max(initial=0))
+    if top >= max_bins:
+        return False
+    return top <= 127
+
+
+def quantile_edges(X: np.ndarray, max_bins: int) -> np.ndarray:
+    """Per-column edges at the interior quantiles (``data.py:49-50``).
+
+    ``np.quantile`` interpolates in float64; the result is cast to float32.
+    Returns ``[max_bins-1, F]`` float32.
+    """
+    q = np.linspace(0.0, 1.0, max_bins + 1, dtype=np.float64)[1:-1]
+    return np.quantile(X, q, axis=0, method="linear").astype(np.float32)
+
+
+def bin_codes(X: np.ndarray, edges: np.ndarray, max_bins: int, *, wide: bool = False) -> np.ndarray:
+    """``searchsorted(edges, x, 'left')`` clipped to the bin range
+    (``data.py:51-57`` for training, ``data.py:105-110`` at predict time).
+    NaN sorts after every edge and lands in the last bin."""
+    Xf = np.asarray(X).astype(np.float32, copy=False)
+    out = np.empty(Xf.shape, dtype=np.int16 if wide else np.int8)
+    for j in range(Xf.shape[1]):
+        col = np.searchsorted(edges[:, j], Xf[:, j], side="left").astype(np.int16)
+        np.clip(col, 0, max_bins - 1, out=col)
+        out[:, j] = col
+    return out
+
+
+def preprocess(X: np.ndarray, p: OracleParams) -> tuple[np.ndarray, np.ndarray | None]:
+    """Training-time preprocessing (``data.py:61-93``): pass integer bin ids
+    through (also when ``prebinned`` is False but the input looks binned),
+    otherwise quantile-bin.  Returns ``(codes, edges-or-None)``."""
+    Xn = np.asarray(X)
+    wide = p.allow_wide_bins and p.max_bins > 128
+    if not wide and p.max_bins > 128:
+        raise ValueError("max_bins must be <= 128 (int8 storage)")
+    if p.prebinned:
+        if not detect_prebinned(Xn, p.max_bins):
+            raise ValueError("prebinned=True requires X to contain integer bins within [0, max_bins).")
+        return Xn.astype(np.int8, copy=False), None
+    if detect_prebinned(Xn, p.max_bins):
+        return Xn.astype(np.int8, copy=False), None
+    Xf = Xn.astype(np.float32, copy=False)
+    edges = quantile_edges(Xf, p.max_bins)
+    return bin_codes(Xf, edges, p.max_bins, wide=wide), edges
+
+
+def apply_bins(X: np.ndarray, edges: np.ndarray | None, max_bins: int, *, wide: bool = False) -> np.ndarray:
+    """Predict-time binning (``data.py:96-111``)."""
+    Xn = np.asarray(X)
+    if edges is None:
+        if not detect_prebinned(Xn, max_bins):
+            raise ValueError("Input must already be prebinned when no edges are provided")
+        return Xn.astype(np.int8, copy=False)
+    return bin_codes(Xn, edges, max_bins, wide=wide)
+
+
+def encode_eras(era: Iterable[int] | None, n_rows: int) -> tuple[np.ndarray, int]:
+    """Dense era codes (``booster.py:396-408``): ``None`` collapses all rows
+    into one era; otherwise ``np.unique`` on the int16-cast ids."""
+    if era is None:
+        return np.zeros(n_rows, dtype=np.int16), 1
+    era_np = np.asarray(era, dtype=np.int16)
+    if era_np.shape[0] != n_rows:
+        raise ValueError("era must align with X rows")
+    uniq, inv = np.unique(era_np, return_inverse=True)
+    return inv.astype(np.int16), int(uniq.shape[0])
+
+
+# --------------------------------------------------------------------------
+# trees
+# --------------------------------------------------------------------------
+
+@dataclass
+class OracleTree:
+    """Structure-of-arrays tree with the reference's BFS-compact numbering
+    (``booster.py:172-190``: a split appends ``left=len, right=len+1``)."""
+
+    feature: list[int] = field(default_factory=lambda: [-1])
+    threshold: list[int] = field(default_factory=lambda: [0])
+    left: list[int] = field(default_factory=lambda: [-1])
+    right: list[int] = field(default_factory=lambda: [-1])
+    value: list[float] = field(default_factory=lambda: [0.0])
+    is_leaf: list[bool] = field(default_factory=lambda: [True])
+
+    def set_leaf(self, nid: int, value: float) -> None:
+        self.value[nid] = float(value)
+        self.is_leaf[nid] = True
+        self.feature[nid] = -1
+        self.threshold[nid] = 0
+        self.left[nid] = -1
+        self.right[nid] = -1
+
+    def split(self, nid: int, feature: int, threshold: int) -> tuple[int, int]:
+        l = len(self.feature)
+        r = l + 1
+        self.feature[nid] = int(feature)
+        self.threshold[nid] = int(threshold)
+        self.is_leaf[nid] = False
+        self.left[nid] = l
+        self.right[nid] = r
+        for _ in range(2):
+            self.feature.append(-1)
+            self.threshold.append(0)
+            self.left.append(-1)
+            self.right.append(-1)
+            self.value.append(0.0)
+            self.is_leaf.append(True)
+        return l, r
+
+    def arrays(self) -> dict[str, np.ndarray]:
+        return {
+            "feature": np.asarray(self.feature, dtype=np.int32),
+            "threshold": np.asarray(self.threshold, dtype=np.int32),
+            "left": np.asarray(self.left, dtype=np.int32),
+            "right": np.asarray(self.right, dtype=np.int32),
+            "value": np.asarray(self.value, dtype=np.float64),
+            "is_leaf": np.asarray(self.is_leaf, dtype=np.bool_),
+        }
+
+
+def route_tree(tree: dict[str, np.ndarray], codes: np.ndarray) -> np.ndarray:
+    """Leaf value per row for one tree (``booster.py:131-169``): a row goes
+    left when ``code <= threshold``.  Returns float32 ``[N]``."""
+    n = codes.shape[0]
+    out = np.zeros(n, dtype=np.float32)
+    if n == 0:
+        return out
+    value32 = tree["value"].astype(np.float32)
+    node = np.zeros(n, dtype=np.int32)
+    live = np.arange(n, dtype=np.int64)
+    while live.size:
+        cur = node[live]
+        at_leaf = tree["is_leaf"][cur]
+        if at_leaf.any():
+            out[live[at_leaf]] = value32[cur[at_leaf]]
+            live = live[~at_leaf]
+            cur = cur[~at_leaf]
+            if live.size == 0:
+                break
+        go_left = codes[live, tree["feature"][cur]] <= tree["threshold"][cur]
+        node[live] = np.where(go_left, tree["left"][cur], tree["right"][cur])
+    return out
+
+
+def predict_codes(trees: Sequence[dict[str, np.ndarray]], codes: np.ndarray, tree_weight: float) -> np.ndarray:
+    """``pred += tree_weight * tree(codes)`` in tree order, float32
+    (``booster.py:709-712``)."""
+    pred = torch.zeros(codes.shape[0], dtype=torch.float32)
+    for t in trees:
+        pred += tree_weight * torch.from_numpy(route_tree(t, codes))
+    return pred.numpy()
+
+
+# --------------------------------------------------------------------------
+# threshold subsets (k_cuts)
+# --------------------------------------------------------------------------
+
+def even_cuts(num_bins: int, k: int) -> torch.Tensor:
+    """Evenly spaced threshold ids (``booster.py:1006-1010``)."""
+    k = max(1, min(k, max(1, num_bins - 1)))
+    idx = torch.round(torch.linspace(0, num_bins - 2, k)).to(torch.int64)
+    return torch.unique(idx, sorted=True).clamp_(0, num_bins - 2)
+
+
+def mass_cuts(counts: torch.Tensor, k: int) -> torch.Tensor:
+    """Per-feature thresholds at count-mass quantiles (``booster.py:1567-1594``).
+    ``counts`` is ``[B, Nn, E, bins]``; returns ``[B, K]`` int64."""
+    nb = counts.shape[-1]
+    k = max(1, min(k, max(1, nb - 1)))
+    per_feat: list[torch.Tensor] = []
+    for b in range(counts.shape[0]):
+        mass = counts[b].sum(dim=(0, 1))
+        total = mass.sum()
+        if total <= 0:
+            per_feat.append(even_cuts(nb, k))
+            continue
+        cdf = torch.cumsum(mass.to(torch.float64), dim=0)
+        q = torch.linspace(0, float(total.item()) * (1 - 1e-12), k)
+        idx = torch.searchsorted(cdf, q).clamp_(max=nb - 1)
+        thr = torch.unique((idx - 1).clamp_(0, nb - 2).to(torch.int64), sorted=True)
+        if thr.numel() < k:
+            thr = torch.unique(torch.cat([thr, even_cuts(nb, k - thr.numel())]), sorted=True).clamp_(0, nb - 2)
+        per_feat.append(thr)
+    width = max(k, max(t.numel() for t in per_feat))
+    table = torch.empty((counts.shape[0], width), dtype=torch.int64)
+    for i, t in enumerate(per_feat):
+        if t.numel() < width:
+            t = torch.unique(torch.cat([t, even_cuts(nb, width - t.numel())]), sorted=True).clamp_(0, nb - 2)
+        table[i] = t
+    return table
+
+
+# --------------------------------------------------------------------------
+# frontier: histograms -> DES scores -> winners
+# --------------------------------------------------------------------------
+
+@dataclass
+class NodeSplit:
+    """Winner of one frontier node (``SplitDecision``, ``booster.py:205-217``)."""
+
+    feature: int
+    threshold: int
+    score: float
+    left_grad: float
+    left_hess: float
+    right_grad: float
+    right_hess: float
+    left_count: int
+    right_count: int
+
+
+def era_weights(counts: torch.Tensor, alpha: float) -> torch.Tensor:
+    """1 for every era with rows (or ``count + alpha`` when ``alpha > 0``), 0
+    for absent eras (``booster.py:815-826``)."""
+    w = torch.zeros_like(counts, dtype=torch.float32)
+    present = counts > 0
+    if not torch.any(present):
+        return w
+    alpha = max(0.0, float(alpha))
+    if alpha > 0.0:
+        w[present] = counts[present].to(torch.float32) + alpha
+    else:
+        w[present] = 1.0
+    return w
+
+
+def block_histograms(codes_blk, g_rows, h_rows, era_rows, node_rows, n_nodes, n_eras, n_bins):
+    """Counts (int64) and float32 grad / hess sums per (feature, node, era, bin)
+    for one feature block (``booster.py:933-977``).  ``torch.bincount`` adds the
+    float32 weights sequentially in row order, which fixes the rounding."""
+    R, B = codes_blk.shape
+    size = int(B * n_nodes * n_eras * n_bins)
+    kdt = torch.int32 if size < (1 << 31) else torch.int64
+    key = torch.arange(B, dtype=kdt).view(1, B) * (n_nodes * n_eras * n_bins)
+    key = key + node_rows.to(kdt).view(R, 1) * (n_eras * n_bins)
+    key = key + era_rows.to(kdt).view(R, 1) * n_bins
+    key = (key + codes_blk.to(kdt)).reshape(-1)
+    shape = (B, n_nodes, n_eras, n_bins)
+    cnt = torch.bincount(key, minlength=size).reshape(shape)
+    gw = g_rows.view(R, 1).expand(R, B).reshape(-1)
+    hw = h_rows.view(R, 1).expand(R, B).reshape(-1)
+    gh = torch.bincount(key, weights=gw, minlength=size).reshape(shape)
+    hh = torch.bincount(key, weights=hw, minlength=size).reshape(shape)
+    return cnt, gh, hh
+
+
+def find_splits(
+    node_rows: Sequence[torch.Tensor],
+    node_eras: Sequence[torch.Tensor],
+    grad: torch.Tensor,
+    hess: torch.Tensor,
+    codes: torch.Tensor,
+    feature_subset: torch.Tensor,
+    n_eras: int,
+    p: OracleParams,
+    trace: dict | None = None,
+) -> list[NodeSplit | None]:
+    """Best split of every frontier node (``booster.py:1598-2133``).
+
+    ``node_rows[i]`` holds the node's row ids ordered by (era, row);
+    ``node_eras[i]`` the matching era codes.  Nodes below ``2*min_samples_leaf``
+    rows get ``None`` (``booster.py:1666-1668``).  ``trace`` (optional dict)
+    receives intermediate tensors for kernel-level parity tests.
+    """
+    M = len(node_rows)
+    out: list[NodeSplit | None] = [None] * M
+    nb = int(p.max_bins)
+    full_T = nb - 1
+    feats = feature_subset.to(torch.int64)
+    if M == 0 or full_T <= 0 or feats.numel() == 0:
+        return out
+
+    lam = float(p.lambda_l2)
+    lam_dro = float(p.lambda_dro)
+    dir_w = float(p.direction_weight)
+    min_leaf = int(p.min_samples_leaf)
+
+    # ---- node contexts (booster.py:1663-1743) ----
+    ctx_of: list[int] = []
+    g_chunks, h_chunks, r_chunks, e_chunks, n_chunks = [], [], [], [], []
+    tot_g: list[float] = []
+    tot_h: list[float] = []
+    tot_c: list[int] = []
+    w_rows: list[torch.Tensor] = []
+    p_dir: list[torch.Tensor] = []
+    for i in range(M):
+        rows = node_rows[i]
+        cnt = int(rows.numel())
+        if cnt < 2 * min_leaf:
+            continue
+        g_r = grad.index_select(0, rows)
+        h_r = hess.index_select(0, rows)
+        g_t = float(g_r.sum().item())
+        h_t = float(h_r.sum().item())
+        p_dir.append(torch.sign(torch.tensor(-g_t / (h_t + lam), dtype=torch.float32)))
+        per_era = torch.bincount(node_eras[i].to(torch.int64), minlength=n_eras).to(torch.float32)
+        w_rows.append(era_weights(per_era, p.era_alpha))
+        cid = len(ctx_of)
+        ctx_of.append(i)
+        r_chunks.append(rows)
+        e_chunks.append(node_eras[i])
+        g_chunks.append(g_r)
+        h_chunks.append(h_r)
+        n_chunks.append(torch.full((cnt,), cid, dtype=torch.int32))
+        tot_g.append(g_t)
+        tot_h.append(h_t)
+        tot_c.append(cnt)
+    if not ctx_of:
+        return out
+
+    Nn = len(ctx_of)
+    rows_cat = torch.cat(r_chunks)
+    era_cat = torch.cat(e_chunks)
+    g_cat = torch.cat(g_chunks)
+    h_cat = torch.cat(h_chunks)
+    n_cat = torch.cat(n_chunks)
+    codes_cat = codes.index_select(0, rows_cat)
+    W = torch.stack(w_rows, 0).contiguous()                       # [Nn, E]
+    G_tot = torch.tensor(tot_g, dtype=torch.float32)
+    H_tot = torch.tensor(tot_h, dtype=torch.float32)
+    C_tot = torch.tensor(tot_c, dtype=torch.int64)
+    P_dir = torch.stack(p_dir, 0)
+
+    best_score = torch.full((Nn,), float("-inf"))
+    best_feat = torch.full((Nn,), -1, dtype=torch.int32)
+    best_thr = torch.full((Nn,), -1, dtype=torch.int32)
+    best_lg = torch.zeros(Nn, dtype=torch.float32)
+    best_lh = torch.zeros(Nn, dtype=torch.float32)
+    best_lc = torch.full((Nn,), -1, dtype=torch.int64)
+
+    n_feat = int(feats.numel())
+    blk = int(p.feature_block_size)
+    if blk <= 0 or blk > n_feat:
+        blk = n_feat
+    if trace is not None:
+        trace["blocks"] = []
+        trace["context_nodes"] = list(ctx_of)
+
+    for start in range(0, n_feat, blk):
+        fblock = feats[start:start + blk]
+        if fblock.numel() == 0:
+            continue
+        cnt, gh, hh = block_histograms(
+            codes_cat.index_select(1, fblock), g_cat, h_cat, era_cat, n_cat, Nn, n_eras, nb
+        )
+        # prefix sums over the first T bins and era totals (booster.py:1781-1787)
+        Lc = cnt[:, :, :, :-1].cumsum(3)
+        Lg = gh[:, :, :, :-1].cumsum(3)
+        Lh = hh[:, :, :, :-1].cumsum(3)
+        Tc = cnt.sum(3, keepdim=True)
+        Tg = gh.sum(3, keepdim=True)
+        Th = hh.sum(3, keepdim=True)
+
+        # thresholds (booster.py:1790-1802)
+        k_user = int(p.k_cuts)
+        use_k = 0 < k_user < full_T
+        per_feat_thr = None
+        if use_k and p.cut_selection == "mass":
+            # The reference computes this table but then fails while mapping the
+            # in-block winner back to a threshold (booster.py:1940 raises
+            # "Index tensor must have the same number of dimensions as input
+            # tensor"), so the mass policy has no reference result to match.
+            raise RuntimeError("k_cuts with cut_selection='mass' raises in the reference torch frontier")
+        elif use_k:
+            thr_ids = even_cuts(nb, k_user).to(torch.int64)
+        else:
+            thr_ids = torch.arange(full_T, dtype=torch.int64)
+        K = int(thr_ids.shape[-1])
+        Bb = Lc.shape[0]
+        if per_feat_thr is not None:
+            pick = per_feat_thr.unsqueeze(1).expand(Bb, Nn, K)
+        else:
+            pick = thr_ids.view(1, 1, K).expand(Bb, Nn, K)
+
+        # ---- DES: sequential weighted Welford over eras (booster.py:1804-1894) ----
+        wsum = torch.zeros((Bb, Nn, K), dtype=torch.float32)
+        mean = torch.zeros_like(wsum)
+        m2 = torch.zeros_like(wsum)
+        lc_all = torch.zeros((Bb, Nn, K), dtype=cnt.dtype)
+        use_dir = (dir_w != 0.0) and bool((P_dir != 0).any())
+        if use_dir:
+            a_num = torch.zeros_like(wsum)
+            a_den = torch.zeros_like(wsum)
+            pa = P_dir.view(1, Nn, 1).expand(Bb, Nn, K)
+        for e in range(n_eras):
+            w_e = W[:, e]
+            if not torch.any(w_e > 0):
+                continue
+            w_full = w_e.view(1, Nn, 1).expand(Bb, Nn, K).to(torch.float32)
+            lc = Lc[:, :, e, :].gather(2, pick)
+            lg = Lg[:, :, e, :].to(torch.float32).gather(2, pick)
+            lh = Lh[:, :, e, :].to(torch.float32).gather(2, pick)
+            tc = Tc[:, :, e, 0].unsqueeze(-1).expand(Bb, Nn, K)
+            tg = Tg[:, :, e, 0].unsqueeze(-1).expand(Bb, Nn, K)
+            th = Th[:, :, e, 0].unsqueeze(-1).expand(Bb, Nn, K)
+            rc = tc - lc
+            rg = tg - lg
+            rh = th - lh
+            ok = (lc > 0) & (rc > 0)
+            w_full = torch.where(ok, w_full, torch.zeros((), dtype=torch.float32))
+            dl = lh + lam
+            dr = rh + lam
+            parent = 0.5 * (tg * tg) / (th + lam)
+            gain = 0.5 * ((lg * lg) / dl + (rg * rg) / dr) - parent
+            wsum_new = wsum + w_full
+            factor = torch.zeros_like(wsum_new)
+            nz = wsum_new > 0
+            factor[nz] = w_full[nz] / wsum_new[nz]
+            delta = gain - mean
+            mean = mean + factor * delta
+            m2 = m2 + w_full * delta * (gain - mean)
+            wsum = wsum_new
+            if use_dir:
+                vl = -lg / dl
+                vr = -rg / dr
+                agree = 0.5 * ((torch.sign(vl) == pa).float() + (torch.sign(vr) == pa).float())
+                a_num = a_num + w_full * agree
+                a_den = a_den + w_full
+            lc_all = lc_all + lc
+        std = torch.sqrt(torch.clamp_min(m2 / torch.clamp_min(wsum, 1e-12), 0.0))
+        score = mean - lam_dro * std
+        if use_dir:
+            agr = torch.zeros_like(a_num)
+            nzd = a_den > 0
+            agr[nzd] = a_num[nzd] / a_den[nzd]
+            score = score + dir_w * agr
+
+        # ---- global min_samples_leaf and in-block winner (booster.py:1897-1919) ----
+        rc_all = C_tot.view(1, Nn, 1) - lc_all
+        ok_all = (lc_all >= min_leaf) & (rc_all >= min_leaf)
+        s_nbk = torch.where(ok_all.permute(1, 0, 2), score.permute(1, 0, 2),
+                            torch.full((), float("-inf")))
+        s_flat = s_nbk.reshape(Nn, -1)
+        c_flat = lc_all.permute(1, 0, 2).reshape(Nn, -1)
+        top = s_flat.max(dim=1).values
+        tie1 = s_flat == top.unsqueeze(1)
+        low = torch.iinfo(torch.int64).min
+        top_c = torch.where(tie1, c_flat, torch.full_like(c_flat, low)).max(dim=1).values
+        tie2 = tie1 & (c_flat == top_c.unsqueeze(1))
+        pos = torch.arange(s_flat.shape[1], dtype=torch.int64).view(1, -1)
+        sel = torch.where(tie2, pos, torch.full_like(pos, -1)).max(dim=1).values
+        has = sel >= 0
+        if trace is not None:
+            trace["blocks"].append({
+                "features": fblock.clone(), "counts": cnt, "grad_hist": gh,
+                "score": s_nbk.clone(), "left_count": lc_all.permute(1, 0, 2).clone(),
+                "sel": sel.clone(), "K": K,
+            })
+        if not torch.any(has):
+            continue
+        gi = sel.clamp_min(0).view(-1, 1)
+        c_score = s_flat.gather(1, gi).squeeze(1)
+        c_cnt = c_flat.gather(1, gi).squeeze(1)
+        f_in = (sel // K).to(torch.int64).clamp_(0, fblock.numel() - 1)
+        t_in = (sel % K).to(torch.int64).clamp_(0, K - 1)
+        c_feat = fblock.gather(0, f_in).to(torch.int32)
+        if per_feat_thr is not None:
+            c_thr = per_feat_thr.gather(0, f_in.view(-1, 1).expand(-1, K)).gather(1, t_in.view(-1, 1)).squeeze(1).to(torch.int32)
+        else:
+            c_thr = thr_ids.gather(0, t_in).to(torch.int32)
+        # left grad / hess totals of the winner: float32 sum over eras of the
+        # float32 prefix sums (booster.py:1948-1960)
+        lg_flat = Lg.sum(dim=2).gather(2, pick).permute(1, 0, 2).reshape(Nn, -1)
+        lh_flat = Lh.sum(dim=2).gather(2, pick).permute(1, 0, 2).reshape(Nn, -1)
+        c_lg = lg_flat.gather(1, gi).squeeze(1)
+        c_lh = lh_flat.gather(1, gi).squeeze(1).to(torch.float32)
+
+        # ---- cross-block merge: strictly greater on (score, left count,
+        #      feature id, threshold) (booster.py:1963-1981) ----
+        upd = has & (
+            (c_score > best_score)
+            | ((c_score == best_score) & (
+                (c_cnt > best_lc)
+                | ((c_cnt == best_lc) & (
+                    (c_feat > best_feat) | ((c_feat == best_feat) & (c_thr > best_thr))))))
+        )
+        best_score = torch.where(upd, c_score, best_score)
+        best_lc = torch.where(upd, c_cnt.to(torch.int64), best_lc)
+        best_lg = torch.where(upd, c_lg, best_lg)
+        best_lh = torch.where(upd, c_lh, best_lh)
+        best_feat = torch.where(upd, c_feat, best_feat)
+        best_thr = torch.where(upd, c_thr, best_thr)
+
+    # ---- decisions (booster.py:2095-2126): right stats are total - left in
+    #      float64 scalar arithmetic on float32 values ----
+    for cid, i in enumerate(ctx_of):
+        f = int(best_feat[cid].item())
+        if f < 0:
+            continue
+        l_g = float(best_lg[cid].item())
+        l_h = float(best_lh[cid].item())
+        l_c = int(best_lc[cid].item())
+        out[i] = NodeSplit(
+            feature=f,
+            threshold=int(best_thr[cid].item()),
+            score=float(best_score[cid].item()),
+            left_grad=l_g,
+            left_hess=l_h,
+            right_grad=float(G_tot[cid].item() - l_g),
+            right_hess=float(H_tot[cid].item() - l_h),
+            left_count=l_c,
+            right_count=int(C_tot[cid].item() - best_lc[cid].item()),
+        )
+    return out
+
+
+# --------------------------------------------------------------------------
+# training loop
+# --------------------------------------------------------------------------
+
+@dataclass
+class OracleModel:
+    params: OracleParams
+    trees: list[dict[str, np.ndarray]]
+    bin_edges: np.ndarray | None
+    tree_weight: float
+    train_preds: np.ndarray
+    depth_records: list[dict]
+    round_seconds: list[float]
+    wide: bool = False
+
+    def predict(self, X: np.ndarray) -> np.ndarray:
+        """``PackBoost.predict`` on the CPU route (``booster.py:658-712``)."""
+        codes = apply_bins(X, self.bin_edges, self.params.max_bins, wide=self.wide)
+        if not self.trees:
+            return np.zeros(codes.shape[0], dtype=np.float32)
+        return predict_codes(self.trees, codes, self.tree_weight)
+
+
+def sample_features(rng: torch.Generator, n_features: int, fraction: float) -> torch.Tensor:
+    """One ``randperm`` per depth on a CPU generator; the first
+    ``max(1, round(fraction*F))`` entries in permutation order
+    (``booster.py:787-792``)."""
+    k = max(1, int(round(float(fraction) * n_features)))
+    k = min(k, n_features)
+    return torch.randperm(n_features, generator=rng)[:k]
+
+
+def fit(
+    X: np.ndarray,
+    y: np.ndarray,
+    era: Iterable[int] | None,
+    p: OracleParams,
+    num_rounds: int,
+    *,
+    record_depths: bool = False,
+) -> OracleModel:
+    """Squared-loss boosting rounds (``booster.py:375-656`` without eval sets
+    and metric logging)."""
+    from time import perf_counter
+
+    Xn = np.asarray(X)
+    y32 = np.asarray(y, dtype=np.float32)
+    if y32.ndim != 1:
+        raise ValueError("y must be 1-D")
+    N, F = Xn.shape
+    if N != y32.shape[0]:
+        raise ValueError("X and y row mismatch")
+    era_codes, E = encode_eras(era, N)
+    codes_np, edges = preprocess(Xn, p)
+    wide = codes_np.dtype == np.int16
+    codes = torch.from_numpy(np.ascontiguousarray(codes_np))
+    y_t = torch.from_numpy(y32)
+
+    rng = torch.Generator(device="cpu")
+    if p.random_state is not None:
+        rng.manual_seed(int(p.random_state))
+
+    grad = torch.zeros(N, dtype=torch.float32)
+    hess = torch.ones(N, dtype=torch.float32)
+    preds = torch.zeros(N, dtype=torch.float32)
+
+    # rows ordered by (era, row): the reference keeps one ascending row list per
+    # era and concatenates them (data.py:114-134, booster.py:2156-2170)
+    era_t = torch.from_numpy(era_codes.astype(np.int64))
+    order = torch.sort(era_t, stable=True).indices
+    root_rows = order
+    root_eras = era_t[order].to(torch.int16)
+
+    lam = float(p.lambda_l2)
+    lr32 = float(p.learning_rate)
+    trees: list[dict[str, np.ndarray]] = []
+    depth_records: list[dict] = []
+    round_seconds: list[float] = []
+
+    with torch.no_grad():
+        for rnd in range(num_rounds):
+            t0 = perf_counter()
+            grad.copy_(preds - y_t)                                  # booster.py:2149-2151
+            hess.fill_(1.0)
+            tree = OracleTree()
+            leaves: dict[int, torch.Tensor] = {0: root_rows}
+            if root_rows.numel() == 0:
+                tree.set_leaf(0, 0.0)
+            else:
+                g = float(grad[root_rows].sum().item())
+                h = float(hess[root_rows].sum().item())
+                tree.set_leaf(0, -g / (h + lam))
+            frontier: list[tuple[int, torch.Tensor, torch.Tensor]] = [(0, root_rows, root_eras)]
+
+            for depth in range(p.max_depth):
+                active = [n for n in frontier if int(n[1].numel()) >= 2 * p.min_samples_leaf]
+                if not active:
+                    break
+                subset = sample_features(rng, F, p.layer_feature_fraction)
+                splits = find_splits([a[1] for a in active], [a[2] for a in active],
+                                     grad, hess, codes, subset, E, p)
+                nxt: list[tuple[int, torch.Tensor, torch.Tensor]] = []
+                for (nid, rows, eras_r), dec in zip(active, splits):
+                    if dec is None:
+                        val = 0.0
+                        if rows.numel() > 0:
+                            g = float(grad[rows].sum().item())
+                            h = float(hess[rows].sum().item())
+                            val = -g / (h + lam)
+                        leaves.setdefault(nid, rows)
+                        tree.set_leaf(nid, val)
+                        continue
+                    l_id, r_id = tree.split(nid, dec.feature, dec.threshold)
+                    tree.set_leaf(l_id, -dec.left_grad / (dec.left_hess + lam))
+                    tree.set_leaf(r_id, -dec.right_grad / (dec.right_hess + lam))
+                    go_left = codes[:, dec.feature].index_select(0, rows) <= dec.threshold  # booster.py:2172-2188
+                    leaves.pop(nid, None)
+                    leaves[l_id] = rows[go_left]
+                    leaves[r_id] = rows[~go_left]
+                    nxt.append((l_id, rows[go_left], eras_r[go_left]))
+                    nxt.append((r_id, rows[~go_left], eras_r[~go_left]))
+                    if record_depths:
+                        depth_records.append({
+                            "round": rnd, "depth": depth, "node": nid, "feature": dec.feature,
+                            "threshold": dec.threshold, "score": dec.score,
+                            "left_count": dec.left_count, "right_count": dec.right_count,
+                        })
+                frontier = nxt
+
+            # pack aggregation (booster.py:582-599): every one of the B identical
+            # trees adds its float32 leaf value, then preds += lr * pack_sum
+            arr = tree.arrays()
+            pack_sum = torch.zeros_like(preds)
+            for _ in range(p.pack_size):
+                for leaf_id, rows in leaves.items():
+                    if rows.numel() == 0:
+                        continue
+                    pack_sum.index_add_(0, rows, torch.full((rows.numel(),), float(arr["value"][leaf_id]),
+                                                            dtype=torch.float32))
+            preds += lr32 * pack_sum
+            for _ in range(p.pack_size):
+                trees.append(arr)
+            round_seconds.append(perf_counter() - t0)
+
+    return OracleModel(params=p, trees=trees, bin_edges=edges, tree_weight=lr32,
+                       train_preds=preds.numpy().copy(), depth_records=depth_records,
+                       round_seconds=round_seconds, wide=wide)
