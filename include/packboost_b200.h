@@ -1,0 +1,278 @@
+/*
+ * packboost_b200 — C ABI of the B200 (sm_100a) backend for PackBoost's training and
+ * prediction hot path.
+ *
+ * The library is loaded with ctypes / dlopen.  Every entry point is `extern "C"`, takes
+ * plain device pointers, sizes and a CUDA stream (as an opaque `void*`, i.e. a
+ * `cudaStream_t`), allocates nothing on the device (the one exception is stated at its
+ * declaration), never synchronises the device unless its comment says so, and returns 0
+ * on success or a negative `PB_ERR_*` code; `pb_last_error()` then holds a thread-local
+ * message.  Callers own every buffer.
+ *
+ * Each declaration cites the reference interface it stands in for (paths are relative to
+ * the reference project root).
+ *
+ * Data layout shared by the training entry points
+ * -----------------------------------------------
+ *  rows        are ordered by (era, original row); `era_offsets[e]..era_offsets[e+1]` is the
+ *              row range of era `e` (int32, E+1 entries).
+ *  codes       feature-major bin codes, one row of `pitch` bytes per (locally owned)
+ *              feature.  `code_bits == 8`: one byte per row.  `code_bits == 4` (max_bins
+ *              <= 16): two rows per byte, even row in the low nibble.  `pitch` is a
+ *              multiple of 128 and covers `rows_padded = roundup(n_rows, 256)` rows.
+ *  gq          int32 fixed-point gradient per row, `gq = rint(g * scale)` with `scale` a
+ *              power of two chosen per round so that `max|gq| <= 2^30`.
+ *  slot        uint16 frontier slot of the row at the current depth (index into the list of
+ *              active nodes) or 0xFFFF when the row sits in a finished leaf.
+ *  leaf        uint16 id of the tree node the row currently sits in (BFS-compact ids: a
+ *              split appends `left = n_nodes, right = n_nodes + 1`).
+ *  histograms  `cnt` uint32 and `gsum` int64, both `[feature][node][era][bin]`.
+ */
+#ifndef PACKBOOST_B200_H
+#define PACKBOOST_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define PB_OK 0
+#define PB_ERR_ARG (-1)      /* bad argument (null pointer, size out of range, misalignment) */
+#define PB_ERR_CUDA (-2)     /* a CUDA runtime call failed; message starts with "CUDA error" */
+#define PB_ERR_WORKSPACE (-3)/* workspace too small */
+#define PB_ERR_NO_DEVICE (-4)
+
+#define PB_SLOT_NONE 0xFFFFu
+#define PB_MAX_DEPTH 12
+
+/* ---- library / device probes --------------------------------------------------------- */
+
+/* Thread-local message of the last failing call ("" if none). */
+const char* pb_last_error(void);
+
+/* ABI version of this header; bumped on any layout or signature change. */
+int pb_abi_version(void);
+
+/* Number of visible CUDA devices with compute capability 10.x; 0 when there is none.
+ * Stands in for `_cuda_available()` (packboost/backends/cuda/frontier_cuda.cu:1077,
+ * probed by packboost/backends/__init__.py:101-119). */
+int pb_device_count(void);
+
+/* ---- binning and packing (packboost/data.py:45-58, 96-111) ---------------------------- */
+
+/* Bin a row-major float32 chunk `x[n_chunk][n_features]` with per-feature edges
+ * `edges[n_edges][n_features]` (code = number of edges < x, NaN -> last bin, clipped to
+ * max_bins-1) and write the codes feature-major into `codes` at rows
+ * `row_offset..row_offset+n_chunk`.  Replaces the searchsorted loop of quantile_bin /
+ * apply_bins (packboost/data.py:51-57, 105-110). `row_offset` must be even in 4-bit mode.
+ * `feature_map[j]` gives the destination feature row of input column j, or -1 to drop the
+ * column (used by feature sharding); NULL maps column j to row j. */
+int pb_bin_pack_f32(const float* x, int64_t n_chunk, int64_t n_features, int64_t row_offset,
+                    const float* edges, int64_t n_edges, int64_t max_bins,
+                    const int32_t* feature_map, uint8_t* codes, int64_t pitch,
+                    int64_t code_bits, void* stream);
+
+/* Same for input that already holds bin ids (uint8/int8 values in [0, max_bins)); the
+ * prebinned passthrough of packboost/data.py:78-91. */
+int pb_pack_codes_u8(const uint8_t* x, int64_t n_chunk, int64_t n_features, int64_t row_offset,
+                     const int32_t* feature_map, uint8_t* codes, int64_t pitch,
+                     int64_t code_bits, void* stream);
+
+/* Row-major packing for the predictor: `out[row][pitch_row]`, 4-bit (two features per byte,
+ * even feature in the low nibble) or 8-bit.  Float input is binned with `edges` first
+ * (`edges == NULL`: input is uint8 bin ids). */
+int pb_pack_rows(const void* x, int64_t x_is_f32, int64_t n_rows, int64_t n_features,
+                 const float* edges, int64_t n_edges, int64_t max_bins,
+                 uint8_t* out, int64_t pitch_row, int64_t code_bits, void* stream);
+
+/* ---- training state ------------------------------------------------------------------ */
+
+/* All fields are 8 bytes wide so that a ctypes.Structure mirrors the layout trivially. */
+typedef struct pb_train_state {
+    /* problem shape */
+    int64_t n_rows;
+    int64_t n_features_total;    /* F of the data set (feature ids in trees are global) */
+    int64_t n_features_local;    /* feature rows held in `codes` on this device */
+    int64_t n_eras;
+    int64_t max_bins;
+    int64_t code_bits;           /* 4 or 8 */
+    int64_t pitch;               /* bytes per feature row of `codes` */
+    /* hyper-parameters (packboost/config.py:68-90) */
+    int64_t max_depth;
+    int64_t pack_size;
+    int64_t min_samples_leaf;
+    int64_t n_thresholds;        /* K: max_bins-1 for the full sweep, fewer for k_cuts */
+    int64_t feature_block_size;  /* resolved block size of the sampled-feature order */
+    double lambda_l2;
+    double lambda_dro;
+    double direction_weight;
+    double era_alpha;
+    double learning_rate;
+    /* device buffers owned by the caller */
+    const uint8_t* codes;        /* [n_features_local][pitch] */
+    const int32_t* era_offsets;  /* [n_eras + 1] */
+    const int32_t* thr_ids;      /* [n_thresholds] threshold (bin) ids, ascending */
+    const int32_t* feat_local;   /* [n_features_total] local row of a global feature, -1 if not held */
+    const float* y;              /* [n_rows] */
+    float* preds;                /* [n_rows] */
+    int32_t* gq;                 /* [rows_padded] */
+    uint16_t* slot;              /* [rows_padded] */
+    uint16_t* leaf;              /* [rows_padded] */
+    void* ctl;                   /* control block, pb_ctl_bytes() bytes, zero-initialised once */
+    void* workspace;             /* histogram + candidate scratch */
+    int64_t workspace_bytes;
+    /* tiling of the rows computed by pb_train_prepare (host side, read-only afterwards) */
+    int64_t max_era_rows;
+    int64_t hist_rows_per_tile;
+    int64_t reserved[6];
+} pb_train_state;
+
+/* sizeof(pb_train_state), so that a binding can verify its mirror of the struct. */
+int64_t pb_train_state_bytes(void);
+
+/* Bytes of the device control block (`ctl`): round scalars, frontier tables, the
+ * per-round decision log and the leaf-value tables. */
+int64_t pb_ctl_bytes(void);
+
+/* Smallest useful `workspace_bytes` for the shape in `st` (enough for one block of
+ * `feature_block_size` features at the deepest level is NOT required: the histogram pass
+ * loops over as many features as fit). */
+int64_t pb_workspace_min_bytes(const pb_train_state* st);
+
+/* Validate `st`, derive the tiling fields.  `era_offsets_host` is the host copy of the era
+ * offsets.  No device work. */
+int pb_train_prepare(pb_train_state* st, const int32_t* era_offsets_host);
+
+/* ---- one boosting round, phase by phase ------------------------------------------------
+ * Together these replace the per-round body of PackBoost.fit (packboost/booster.py:494-599)
+ * and the torch frontier it calls (packboost/booster.py:1598-2133).  The host keeps the
+ * control flow: it draws the per-depth feature subset with its own generator
+ * (packboost/booster.py:787-792) and launches the phases in order on one stream. */
+
+/* Start of a round (packboost/booster.py:496-513, 582-597 of the PREVIOUS round, and
+ * 2149-2154): preds += delta[leaf] when `apply_previous` != 0, then g = preds - y, the
+ * per-round power-of-two scale, gq, every row back to slot 0 / tree node 0, and the root
+ * entry of the frontier (count, gradient sum, root leaf value). */
+int pb_round_begin(const pb_train_state* st, int64_t apply_previous, void* stream);
+
+/* Histograms and DES scores for one depth (packboost/booster.py:933-977, 1759-1908):
+ * `feat_rows[i]` is the local feature row of the i-th locally held sampled feature and
+ * `feat_pos[i]` its position in the sampled order (both device int32[n_feat]).  For every
+ * (sampled position, frontier node) the best threshold under the order (score, left count,
+ * threshold) is written to the candidate table, `n_sampled` x nodes entries; positions not
+ * listed in `feat_pos` are left untouched (another device fills them). */
+int pb_depth_hist_score(const pb_train_state* st, int64_t depth, const int32_t* feat_rows,
+                        const int32_t* feat_pos, int64_t n_feat, int64_t n_sampled, void* stream);
+
+/* Device pointer and byte size of the candidate table of `depth` (for the cross-device
+ * exchange: entries are disjoint per device, so a SUM all-reduce over int32 words merges
+ * them; `pb_depth_clear_candidates` must run first when more than one device takes part). */
+int pb_candidates_buffer(const pb_train_state* st, int64_t depth, int64_t n_sampled,
+                         void** ptr, int64_t* bytes);
+int pb_depth_clear_candidates(const pb_train_state* st, int64_t depth, int64_t n_sampled, void* stream);
+
+/* Pick the winner of every frontier node (packboost/booster.py:1912-1981: in-block order
+ * score, left count, position; across blocks strictly greater on score, left count,
+ * feature id, threshold), assign BFS-compact child ids (packboost/booster.py:181-187),
+ * compute child leaf values in float64 (packboost/booster.py:545-546, 2103-2108), decide
+ * which children stay on the frontier (packboost/booster.py:794-796) and write the depth's
+ * decision log.  `sampled_features` is the device int32[n_sampled] list of global feature
+ * ids in sampled order. */
+int pb_depth_select(const pb_train_state* st, int64_t depth, const int32_t* sampled_features,
+                    int64_t n_sampled, void* stream);
+
+/* Route every frontier row to its child (packboost/booster.py:2172-2188: left when
+ * code <= threshold) and update `slot` / `leaf`.  Single-device form. */
+int pb_depth_partition(const pb_train_state* st, int64_t depth, void* stream);
+
+/* Feature-sharded form: each device sets the go-left bit of the rows whose winning feature
+ * it holds (`bits` is uint32[rows_padded/32], zero elsewhere); after a SUM/OR all-reduce
+ * of `bits` every device applies them. */
+int pb_depth_goleft_bits(const pb_train_state* st, int64_t depth, uint32_t* bits, void* stream);
+int pb_depth_apply_bits(const pb_train_state* st, int64_t depth, const uint32_t* bits, void* stream);
+
+/* End of a round: finish the leaf-delta table (pack aggregation, packboost/booster.py:
+ * 582-598: every one of the B identical trees adds its float32 leaf value, scaled by the
+ * float32 learning rate).  The predictions themselves are updated by the next
+ * pb_round_begin or by pb_apply_leaf_delta. */
+int pb_round_end(const pb_train_state* st, void* stream);
+int pb_apply_leaf_delta(const pb_train_state* st, void* stream);
+
+/* Device address and size of the round's decision log (copy it to the host after
+ * pb_round_end; layout: pb_round_log below). */
+int pb_round_log_buffer(const pb_train_state* st, void** ptr, int64_t* bytes);
+
+typedef struct pb_winner {
+    int32_t feature;      /* global feature id, -1: node not split */
+    int32_t threshold;    /* bin id: rows with code <= threshold go left */
+    float score;
+    int32_t tree_node;    /* id of the split node */
+    int64_t left_count;
+    int64_t total_count;
+    int64_t left_gq;      /* exact fixed-point sums */
+    int64_t total_gq;
+    int32_t left_id;      /* child ids (BFS-compact) */
+    int32_t right_id;
+    double left_value;    /* float64 leaf values of the children */
+    double right_value;
+    float left_grad;      /* float32 sums as used for the leaf values */
+    float total_grad;
+} pb_winner;
+
+typedef struct pb_round_log_header {
+    double root_value;
+    float scale;          /* gq = rint(g * scale) */
+    float max_abs_grad;
+    int64_t root_gq;
+    int32_t n_ctx[PB_MAX_DEPTH + 1]; /* frontier nodes per depth; winners of depth d start at (1<<d)-1 */
+    int32_t n_tree_nodes;
+    int32_t reserved[2];
+} pb_round_log_header;
+/* The log is a pb_round_log_header followed by (1 << max_depth) - 1 pb_winner records. */
+
+/* ---- kernel-level entry points (used directly by the parity tests and the benchmark) ---- */
+
+/* Histogram pass alone (packboost/booster.py:933-977, counts and gradient sums; the
+ * hessian of the squared loss is 1, so its histogram is the count).  Output layout
+ * `[n_feat][node_stride][n_eras][max_bins]`. `n_nodes` frontier slots are accumulated. */
+int pb_hist_build(const pb_train_state* st, const int32_t* feat_rows, int64_t n_feat,
+                  int64_t n_nodes, int64_t node_stride, uint32_t* cnt, int64_t* gsum, void* stream);
+
+/* ---- prediction ----------------------------------------------------------------------- */
+
+/* Ensemble over row-major packed codes (see pb_pack_rows):
+ * out[row] = fold over trees in order of out + weight * leaf(tree, row), in float32 without
+ * contraction — the CPU route of PackBoost.predict (packboost/booster.py:709-712) with
+ * Tree routing (packboost/booster.py:131-169).  Trees are concatenated node arrays;
+ * `tree_offsets[t]` is the first node of tree t, children are tree-relative.
+ * `repeat[t]` (may be NULL = 1) adds tree t that many times in a row (identical trees of a
+ * pack are stored once).  The accumulation starts from `init[row]` (NULL: from 0), which
+ * lets a caller extend earlier predictions by the trees added since; `out` is overwritten
+ * and may alias `init`. */
+int pb_predict_rows(const uint8_t* codes, int64_t n_rows, int64_t pitch_row, int64_t code_bits,
+                    const int32_t* feature, const int32_t* threshold, const int32_t* left,
+                    const int32_t* right, const float* value, const uint8_t* is_leaf,
+                    const int32_t* tree_offsets, const int32_t* repeat, int64_t n_trees,
+                    float weight, float* out, const float* init, void* stream);
+
+/* Single tree over feature-major uint8 codes `bins[F][N]`: the argument list of
+ * predict_bins_cuda (packboost/backends/cuda/frontier_cuda.cu:853-861). */
+int pb_predict_bins_fm(const uint8_t* bins, int64_t n_features, int64_t n_rows,
+                       const int32_t* feature, const int32_t* threshold, const int32_t* left,
+                       const int32_t* right, const float* value, const uint8_t* is_leaf,
+                       int64_t n_nodes, float* out, void* stream);
+
+/* One pack over feature-major uint8 codes, out[row] = tree_weight * sum over trees of the
+ * leaf value: the argument list of predict_pack_cuda
+ * (packboost/backends/cuda/frontier_cuda.cu:989-999); children are absolute node ids. */
+int pb_predict_pack_fm(const uint8_t* bins, int64_t n_features, int64_t n_rows,
+                       const int32_t* feature, const int32_t* threshold, const int32_t* left_abs,
+                       const int32_t* right_abs, const float* value, const uint8_t* is_leaf,
+                       const int32_t* offsets, int64_t n_trees, float tree_weight,
+                       float* out, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* PACKBOOST_B200_H */

@@ -1,0 +1,662 @@
+"""PackBoost host orchestration for the B200 backend.
+
+The public surface follows the reference booster (``packboost/booster.py``):
+``PackBoost(config).fit(X, y, era, num_rounds=..., feature_names=...,
+eval_sets=..., round_callback=...)``, ``predict``, ``predict_packwise``,
+``trees`` and ``round_metrics``, with ``Tree`` / ``TreeNode`` / ``TreeBuilder``
+as the model containers.  What changed is everything below the round loop:
+
+* the feature matrix lives on the device as feature-major packed bin codes with
+  rows ordered by era;
+* frontier bookkeeping is a per-row ``slot`` / ``leaf`` map on the device, not
+  Python lists of row-index tensors;
+* histograms, DES scores, winner selection, child numbering, leaf values,
+  partition and the prediction update are CUDA kernels reached through the C
+  ABI (``include/packboost_b200.h``); the host only draws the per-depth feature
+  subset, launches the phases and reads one small decision log per round.
+
+All ``pack_size`` trees of a round are identical in the reference (it has no
+per-tree randomness and de-duplicates identical frontier nodes,
+``packboost/booster.py:1670-1682``); this implementation grows the tree once and
+records it ``pack_size`` times, keeping the summed (not averaged) pack update of
+``packboost/booster.py:582-597``.
+
+With ``torch.distributed`` initialised (one process per GPU) the features are
+sharded ``feature % world_size == rank``; each depth exchanges the candidate
+table and a go-left bitmask with two all-reduces.
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+import logging
+import json
+import math
+import os
+from dataclasses import dataclass, field
+from time import perf_counter
+from typing import Callable, Iterable, List, Sequence, Tuple
+
+import numpy as np
+import torch
+
+from . import backends as B
+from .config import PackBoostConfig
+from .sharding import feature_map, local_part
+from .data import (BinningResult, PackedMatrix, PackedRows, code_bits_for, detect_prebinned, pack_feature_major,
+                   pack_row_major, quantile_edges)
+
+# ------------------------------ tree containers ------------------------------
+
+
+@dataclass(slots=True)
+class TreeNode:
+    feature: int = -1
+    threshold: int = 0
+    left: int = -1
+    right: int = -1
+    value: float = 0.0
+    is_leaf: bool = True
+
+
+@dataclass(slots=True)
+class Tree:
+    nodes: List[TreeNode]
+    _arrays: dict | None = field(init=False, repr=False, default=None)
+
+    def arrays(self) -> dict[str, np.ndarray]:
+        if self._arrays is None:
+            self._arrays = {
+                "feature": np.asarray([n.feature for n in self.nodes], dtype=np.int32),
+                "threshold": np.asarray([n.threshold for n in self.nodes], dtype=np.int32),
+                "left": np.asarray([n.left for n in self.nodes], dtype=np.int32),
+                "right": np.asarray([n.right for n in self.nodes], dtype=np.int32),
+                "value": np.asarray([n.value for n in self.nodes], dtype=np.float32),
+                "is_leaf": np.asarray([n.is_leaf for n in self.nodes], dtype=np.uint8),
+            }
+        return self._arrays
+
+    def predict_bins(self, bins: torch.Tensor) -> torch.Tensor:
+        """Leaf value per row for integer-binned features ``[N, F]``
+        (``packboost/booster.py:66-128``).  Always routed on the GPU; the result is
+        returned on the input's device."""
+        n = bins.shape[0]
+        if n == 0:
+            return torch.empty(0, dtype=torch.float32, device=bins.device)
+        dev = torch.device("cuda", torch.cuda.current_device())
+        a = self.arrays()
+        fm = bins.to(device=dev, dtype=torch.uint8).t().contiguous()
+        t = {k: torch.from_numpy(v).to(dev) for k, v in a.items()}
+        out = B.predict_bins_cuda(fm, t["feature"], t["threshold"], t["left"], t["right"], t["value"], t["is_leaf"])
+        return out.to(bins.device)
+
+
+class TreeBuilder:
+    """BFS-compact node numbering (``packboost/booster.py:172-190``)."""
+
+    def __init__(self) -> None:
+        self.nodes: List[TreeNode] = [TreeNode()]
+
+    def set_leaf(self, node_id: int, value: float) -> None:
+        n = self.nodes[node_id]
+        n.value = float(value)
+        n.is_leaf = True
+        n.feature = -1
+        n.threshold = 0
+        n.left = -1
+        n.right = -1
+
+    def split(self, node_id: int, feature: int, threshold: int) -> Tuple[int, int]:
+        n = self.nodes[node_id]
+        n.feature = int(feature)
+        n.threshold = int(threshold)
+        n.is_leaf = False
+        l = len(self.nodes)
+        n.left = l
+        n.right = l + 1
+        self.nodes.append(TreeNode())
+        self.nodes.append(TreeNode())
+        return l, l + 1
+
+    def build(self) -> Tree:
+        return Tree(nodes=self.nodes)
+
+
+# ------------------------------ decision log ------------------------------
+
+_WINNER_DT = np.dtype({
+    "names": ["feature", "threshold", "score", "tree_node", "left_count", "total_count", "left_gq", "total_gq",
+              "left_id", "right_id", "left_value", "right_value", "left_grad", "total_grad"],
+    "formats": ["<i4", "<i4", "<f4", "<i4", "<i8", "<i8", "<i8", "<i8", "<i4", "<i4", "<f8", "<f8", "<f4", "<f4"],
+    "offsets": [0, 4, 8, 12, 16, 24, 32, 40, 48, 52, 56, 64, 72, 76],
+    "itemsize": 80,
+})
+_HEADER_DT = np.dtype({
+    "names": ["root_value", "scale", "max_abs_grad", "root_gq", "n_ctx", "n_tree_nodes"],
+    "formats": ["<f8", "<f4", "<f4", "<i8", ("<i4", (B.PB_MAX_DEPTH + 1,)), "<i4"],
+    "offsets": [0, 8, 12, 16, 24, 24 + 4 * (B.PB_MAX_DEPTH + 1)],
+    "itemsize": 88,
+})
+
+
+def even_cut_ids(num_bins: int, k: int) -> np.ndarray:
+    """Evenly spaced threshold ids (``packboost/booster.py:1006-1010``)."""
+    k = max(1, min(k, max(1, num_bins - 1)))
+    idx = torch.round(torch.linspace(0, num_bins - 2, k)).to(torch.int64)
+    return torch.unique(idx, sorted=True).clamp_(0, num_bins - 2).numpy().astype(np.int32)
+
+
+def _era_correlation_np(era_ids: np.ndarray, target: np.ndarray, preds: np.ndarray) -> float:
+    """Mean per-era Pearson correlation (``packboost/booster.py:909-929``)."""
+    if era_ids.shape[0] == 0:
+        return float("nan")
+    cors: list[float] = []
+    for era in np.unique(era_ids):
+        m = era_ids == era
+        y = target[m]
+        p = preds[m]
+        if y.size < 2:
+            continue
+        sy = y.std(ddof=0)
+        sp = p.std(ddof=0)
+        if sy <= 1e-12 or sp <= 1e-12:
+            continue
+        corr = float(((y - y.mean()) * (p - p.mean())).mean()) / (sy * sp)
+        if math.isfinite(corr):
+            cors.append(corr)
+    return float(np.mean(cors)) if cors else float("nan")
+
+
+# ------------------------------ device training state ------------------------------
+
+
+class _DeviceTrainer:
+    """Owns the device buffers of one fit and launches the round phases."""
+
+    def __init__(self, cfg: PackBoostConfig, matrix: PackedMatrix, y_sorted: np.ndarray, era_offsets: np.ndarray,
+                 n_features_total: int, feat_local: np.ndarray, rank: int, world: int,
+                 workspace_bytes: int | None = None):
+        self.cfg = cfg
+        self.lib = B.lib()
+        self.dev = matrix.codes.device
+        self.rank, self.world = rank, world
+        self.matrix = matrix
+        n = matrix.n_rows
+        npad = matrix.rows_padded
+        self.n_rows = n
+        self.F = n_features_total
+        self.E = int(era_offsets.shape[0] - 1)
+        nb = int(cfg.max_bins)
+        k_user = int(cfg.k_cuts)
+        if 0 < k_user < nb - 1:
+            if cfg.cut_selection == "mass":
+                raise RuntimeError(
+                    "k_cuts with cut_selection='mass' is not supported: the reference torch frontier raises on it")
+            thr = even_cut_ids(nb, k_user)
+        else:
+            thr = np.arange(nb - 1, dtype=np.int32)
+        self.thr_ids = torch.from_numpy(thr).to(self.dev)
+        self.era_offsets = torch.from_numpy(np.ascontiguousarray(era_offsets, dtype=np.int32)).to(self.dev)
+        self.feat_local = torch.from_numpy(np.ascontiguousarray(feat_local, dtype=np.int32)).to(self.dev)
+        self.y = torch.from_numpy(np.ascontiguousarray(y_sorted, dtype=np.float32)).to(self.dev)
+        self.preds = torch.zeros(n, dtype=torch.float32, device=self.dev)
+        self.gq = torch.zeros(npad, dtype=torch.int32, device=self.dev)
+        self.slot = torch.full((npad,), -1, dtype=torch.int16, device=self.dev)  # 0xFFFF: no slot
+        self.leaf = torch.zeros(npad, dtype=torch.int16, device=self.dev)
+        self.bits = torch.zeros(npad // 32, dtype=torch.int32, device=self.dev) if world > 1 else None
+        self.ctl = torch.zeros(int(self.lib.pb_ctl_bytes()), dtype=torch.uint8, device=self.dev)
+
+        st = B.TrainState()
+        st.n_rows = n
+        st.n_features_total = n_features_total
+        st.n_features_local = matrix.n_features_local
+        st.n_eras = self.E
+        st.max_bins = nb
+        st.code_bits = matrix.code_bits
+        st.pitch = matrix.pitch
+        st.max_depth = int(cfg.max_depth)
+        st.pack_size = int(cfg.pack_size)
+        st.min_samples_leaf = int(cfg.min_samples_leaf)
+        st.n_thresholds = int(thr.shape[0])
+        st.feature_block_size = int(cfg.feature_block_size)
+        st.lambda_l2 = float(cfg.lambda_l2)
+        st.lambda_dro = float(cfg.lambda_dro)
+        st.direction_weight = float(cfg.direction_weight)
+        st.era_alpha = float(cfg.era_alpha)
+        st.learning_rate = float(cfg.learning_rate)
+        st.codes = matrix.codes.data_ptr()
+        st.era_offsets = self.era_offsets.data_ptr()
+        st.thr_ids = self.thr_ids.data_ptr()
+        st.feat_local = self.feat_local.data_ptr()
+        st.y = self.y.data_ptr()
+        st.preds = self.preds.data_ptr()
+        st.gq = self.gq.data_ptr()
+        st.slot = self.slot.data_ptr()
+        st.leaf = self.leaf.data_ptr()
+        st.ctl = self.ctl.data_ptr()
+        self.st = st
+
+        # workspace: candidate table + as many features of histogram as fit the budget
+        k_sampled = self.n_sampled()
+        stride = 1 << (int(cfg.max_depth) - 1)
+        per_feat = stride * self.E * nb * 12
+        local_sampled = (k_sampled + world - 1) // world + 1
+        want = 24 * self.F * stride + per_feat * min(local_sampled, max(matrix.n_features_local, 1)) + (1 << 20)
+        min_bytes = int(self.lib.pb_workspace_min_bytes(C.byref(st)))
+        if workspace_bytes is None:
+            free, _total = torch.cuda.mem_get_info(self.dev)
+            cap = int(os.getenv("PACKBOOST_WORKSPACE_BYTES", str(min(8 << 30, int(free * 0.6)))))
+            workspace_bytes = max(min_bytes, min(want, cap))
+        self.workspace = torch.empty(int(workspace_bytes), dtype=torch.uint8, device=self.dev)
+        st.workspace = self.workspace.data_ptr()
+        st.workspace_bytes = int(workspace_bytes)
+        eo = np.ascontiguousarray(era_offsets, dtype=np.int32)
+        B.check(self.lib.pb_train_prepare(C.byref(st), eo.ctypes.data))
+
+        # pinned staging for the per-round feature lists and the decision log
+        D = int(cfg.max_depth)
+        self.D = D
+        ptr, nbytes = C.c_void_p(), C.c_int64()
+        B.check(self.lib.pb_round_log_buffer(C.byref(st), C.byref(ptr), C.byref(nbytes)))
+        self.log_bytes = int(nbytes.value)
+        off = ptr.value - self.ctl.data_ptr()
+        self.log_dev = self.ctl[off: off + self.log_bytes]
+        self.log_host = torch.empty(self.log_bytes, dtype=torch.uint8).pin_memory()
+        self.feat_host = torch.empty((D, 3, max(k_sampled, 1)), dtype=torch.int32).pin_memory()
+        self.feat_dev = torch.empty((D, 3, max(k_sampled, 1)), dtype=torch.int32, device=self.dev)
+        self.rounds_done = 0
+        self.pending_delta = False
+
+    def n_sampled(self) -> int:
+        frac = float(self.cfg.layer_feature_fraction)
+        k = max(1, int(round(frac * self.F)))
+        return min(k, self.F)
+
+    # -- one round ---------------------------------------------------------
+    def run_round(self, subsets: list[np.ndarray]) -> None:
+        """Enqueue every phase of one round; ``subsets[d]`` is the sampled feature list of depth d."""
+        lib, st = self.lib, C.byref(self.st)
+        stream = torch.cuda.current_stream().cuda_stream
+        D = self.D
+        k = subsets[0].shape[0]
+        fh = self.feat_host
+        n_local = []
+        for d in range(D):
+            s = subsets[d]
+            fh[d, 0, :k] = torch.from_numpy(s)
+            rows, pos = local_part(s, self.rank, self.world)
+            n_local.append(int(pos.shape[0]))
+            fh[d, 1, : pos.shape[0]] = torch.from_numpy(rows)
+            fh[d, 2, : pos.shape[0]] = torch.from_numpy(pos)
+        self.feat_dev.copy_(fh, non_blocking=True)
+        B.check(lib.pb_round_begin(st, 1 if self.pending_delta else 0, stream))
+        for d in range(D):
+            sampled = self.feat_dev[d, 0].data_ptr()
+            rows = self.feat_dev[d, 1].data_ptr()
+            pos = self.feat_dev[d, 2].data_ptr()
+            if self.world > 1:
+                B.check(lib.pb_depth_clear_candidates(st, d, k, stream))
+            B.check(lib.pb_depth_hist_score(st, d, rows, pos, n_local[d], k, stream))
+            if self.world > 1:
+                self._allreduce_candidates(d, k)
+            B.check(lib.pb_depth_select(st, d, sampled, k, stream))
+            if self.world > 1:
+                B.check(lib.pb_depth_goleft_bits(st, d, self.bits.data_ptr(), stream))
+                torch.distributed.all_reduce(self.bits, op=torch.distributed.ReduceOp.SUM)
+                B.check(lib.pb_depth_apply_bits(st, d, self.bits.data_ptr(), stream))
+            else:
+                B.check(lib.pb_depth_partition(st, d, stream))
+        B.check(lib.pb_round_end(st, stream))
+        self.pending_delta = True
+        self.log_host.copy_(self.log_dev, non_blocking=True)
+        self.rounds_done += 1
+
+    def _allreduce_candidates(self, depth: int, k: int) -> None:
+        ptr, nbytes = C.c_void_p(), C.c_int64()
+        B.check(self.lib.pb_candidates_buffer(C.byref(self.st), depth, k, C.byref(ptr), C.byref(nbytes)))
+        off = ptr.value - self.workspace.data_ptr()
+        view = self.workspace[off: off + int(nbytes.value)].view(torch.int32)
+        torch.distributed.all_reduce(view, op=torch.distributed.ReduceOp.SUM)
+
+    def flush_predictions(self) -> None:
+        """Apply the last round's leaf deltas to ``preds`` now (metrics, end of fit)."""
+        if self.pending_delta:
+            B.check(self.lib.pb_apply_leaf_delta(C.byref(self.st), torch.cuda.current_stream().cuda_stream))
+            self.pending_delta = False
+
+    def read_log(self) -> tuple[np.ndarray, np.ndarray]:
+        torch.cuda.current_stream().synchronize()
+        raw = self.log_host.numpy()
+        head = raw[:88].view(_HEADER_DT)[0]
+        winners = raw[88:].view(_WINNER_DT)
+        return head, winners
+
+
+def _tree_from_log(head, winners, max_depth: int) -> tuple[Tree, list[int]]:
+    """Replay the device's decisions into a ``Tree`` (``packboost/booster.py:527-563``)."""
+    tb = TreeBuilder()
+    tb.set_leaf(0, float(head["root_value"]))
+    n_ctx = [int(v) for v in head["n_ctx"][: max_depth + 1]]
+    for d in range(max_depth):
+        if n_ctx[d] == 0:
+            break
+        base = (1 << d) - 1
+        for w in winners[base: base + n_ctx[d]]:
+            nid = int(w["tree_node"])
+            if int(w["feature"]) < 0:
+                tb.set_leaf(nid, float(w["left_value"]))
+                continue
+            l, r = tb.split(nid, int(w["feature"]), int(w["threshold"]))
+            if l != int(w["left_id"]) or r != int(w["right_id"]):
+                raise RuntimeError("device and host child numbering disagree")
+            tb.set_leaf(l, float(w["left_value"]))
+            tb.set_leaf(r, float(w["right_value"]))
+    if len(tb.nodes) != int(head["n_tree_nodes"]):
+        raise RuntimeError("device and host tree sizes disagree")
+    return tb.build(), n_ctx
+
+
+# ------------------------------ the booster ------------------------------
+
+
+class PackBoost:
+    """Pack-parallel gradient booster with DES scoring on the B200 backend."""
+
+    def __init__(self, config: PackBoostConfig) -> None:
+        self.config = config
+        if torch.device(config.device).type != "cuda":
+            raise RuntimeError("packboost_b200 has no CPU path: PackBoostConfig.device must be 'cuda'")
+        if not B.cuda_available():
+            raise RuntimeError("packboost_b200: libpackboost_b200.so is not built or no sm_100 device is visible")
+        self._device = torch.device("cuda", torch.cuda.current_device())
+        self._rng = torch.Generator(device="cpu")
+        if config.random_state is not None:
+            self._rng.manual_seed(int(config.random_state))
+        mode = (os.getenv("PACKBOOST_HIST_MODE") or config.histogram_mode).lower()
+        if mode not in {"rebuild", "subtract", "auto"}:
+            raise ValueError(f"Unsupported histogram_mode: {mode}")
+        self._histogram_mode = mode
+        self._logger = logging.getLogger(__name__)
+        self._depth_logs: list[dict[str, object]] = []
+        self._binner: BinningResult | None = None
+        self._trees: list[Tree] = []
+        self._distinct: list[tuple[Tree, int]] = []  # (tree, repeat) per round
+        self._era_unique: np.ndarray | None = None
+        self._feature_names: list[str] | None = None
+        self._tree_weight: float | None = None
+        self._trained_pack_size: int | None = None
+        self._round_metrics: list[dict[str, float]] = []
+        self._use_native_cuda = True
+        self._cuda_backend = B
+        self._forest_cache: dict | None = None
+        self._train_preds: np.ndarray | None = None
+        self._trainer: _DeviceTrainer | None = None
+        self._row_order: np.ndarray | None = None
+
+    # Public -------------------------------------------------------------
+
+    @property
+    def trees(self) -> Sequence[Tree]:
+        return self._trees
+
+    @property
+    def round_metrics(self) -> Sequence[dict[str, float]]:
+        return self._round_metrics
+
+    def fit(
+        self,
+        X: np.ndarray,
+        y: np.ndarray,
+        era: Iterable[int] | None,
+        *,
+        num_rounds: int,
+        feature_names: Sequence[str] | None = None,
+        eval_sets: Sequence[tuple[str, np.ndarray, np.ndarray, Iterable[int] | None]] | None = None,
+        round_callback: Callable[[int, dict[str, float]], None] | None = None,
+    ) -> "PackBoost":
+        """Squared-loss boosting with pack-synchronous growth and DES (``packboost/booster.py:375-656``)."""
+        cfg = self.config
+        X_np = X.detach().cpu().numpy() if isinstance(X, torch.Tensor) else np.asarray(X)
+        y_np = np.asarray(y, dtype=np.float32)
+        if y_np.ndim != 1:
+            raise ValueError("y must be 1-D")
+        N, F = X_np.shape
+        if N != y_np.shape[0]:
+            raise ValueError("X and y row mismatch")
+        wide = os.getenv("PACKBOOST_ALLOW_WIDE_BINS") == "1"
+        if cfg.max_bins > 128 and not wide:
+            raise ValueError("max_bins must be ≤ 128 when using int8 bin storage")
+        if cfg.max_bins > 256:
+            raise ValueError("max_bins must be ≤ 256")
+        if era is None:
+            era_encoded = np.zeros(N, dtype=np.int16)
+            uniq = np.array([0], dtype=np.int16)
+        else:
+            era_np = np.asarray(era, dtype=np.int16)
+            if era_np.shape[0] != N:
+                raise ValueError("era must align with X rows")
+            uniq, inv = np.unique(era_np, return_inverse=True)
+            era_encoded = inv.astype(np.int16)
+        self._era_unique = uniq
+        E = int(uniq.shape[0])
+        self._feature_names = list(feature_names) if feature_names is not None else [f"f{i}" for i in range(F)]
+
+        # rows ordered by (era, row); identity when eras are already contiguous and ascending
+        if N > 1 and np.all(era_encoded[1:] >= era_encoded[:-1]):
+            order = None
+            era_sorted = era_encoded
+        else:
+            order = np.argsort(era_encoded, kind="stable")
+            era_sorted = era_encoded[order]
+        counts = np.bincount(era_sorted.astype(np.int64), minlength=E)
+        era_offsets = np.concatenate([[0], np.cumsum(counts)]).astype(np.int32)
+
+        # binning (packboost/data.py:61-93)
+        if bool(cfg.prebinned) and not detect_prebinned(X_np, cfg.max_bins):
+            raise ValueError("prebinned=True requires X to contain integer bins within [0, max_bins).")
+        if bool(cfg.prebinned) or detect_prebinned(X_np, cfg.max_bins):
+            edges = None
+            self._binner = BinningResult(bins=None, bin_edges=None, prebinned=True)
+            X_src = X_np if X_np.dtype in (np.uint8, np.int8) else X_np.astype(np.uint8)
+            X_src = X_src.view(np.uint8)
+        else:
+            X_src = X_np.astype(np.float32, copy=False)
+            edges = quantile_edges(X_src, cfg.max_bins)
+            self._binner = BinningResult(bins=None, bin_edges=edges, prebinned=False)
+
+        rank, world = 0, 1
+        if torch.distributed.is_available() and torch.distributed.is_initialized():
+            rank, world = torch.distributed.get_rank(), torch.distributed.get_world_size()
+        feat_local = feature_map(F, rank, world)
+        n_local = int((feat_local >= 0).sum())
+        matrix = pack_feature_major(X_src, edges, cfg.max_bins, row_order=order,
+                                    feature_map=feat_local if world > 1 else None, n_features_local=n_local)
+        y_sorted = y_np if order is None else y_np[order]
+        trainer = _DeviceTrainer(cfg, matrix, y_sorted, era_offsets, F, feat_local, rank, world)
+        self._trainer = trainer
+        self._row_order = order
+
+        self._depth_logs = []
+        self._round_metrics = []
+        self._trees = []
+        self._distinct = []
+        self._forest_cache = None
+        self._tree_weight = float(cfg.learning_rate)
+        self._trained_pack_size = int(cfg.pack_size)
+
+        eval_states = self._prepare_eval_sets(eval_sets)
+        want_metrics = (round_callback is not None) or bool(eval_states) or os.getenv("PACKBOOST_TRAIN_METRICS") == "1"
+        try:
+            eval_every = int(os.getenv("PACKBOOST_EVAL_EVERY", "1"))
+        except Exception:
+            eval_every = 1
+
+        k = trainer.n_sampled()
+        D = int(cfg.max_depth)
+        for round_idx in range(num_rounds):
+            t0 = perf_counter()
+            # one draw per depth, speculating that every depth has active nodes; the generator is
+            # rewound below when the device reports an empty frontier (packboost/booster.py:516-519)
+            states, subsets = [], []
+            for _ in range(D):
+                states.append(self._rng.get_state())
+                subsets.append(torch.randperm(F, generator=self._rng)[:k].numpy().astype(np.int32))
+            trainer.run_round(subsets)
+            head, winners = trainer.read_log()
+            tree, n_ctx = _tree_from_log(head, winners, D)
+            for d in range(D):
+                if n_ctx[d] == 0:
+                    self._rng.set_state(states[d])
+                    break
+                self._depth_logs.append(self._depth_log(d, n_ctx[d], k))
+            self._distinct.append((tree, int(cfg.pack_size)))
+            self._trees.extend([tree] * int(cfg.pack_size))
+
+            metrics: dict[str, float] = {"round": round_idx + 1}
+            if want_metrics:
+                trainer.flush_predictions()
+                preds_sorted = trainer.preds.cpu().numpy()
+                metrics["train_corr"] = _era_correlation_np(era_sorted, y_sorted, preds_sorted)
+            else:
+                metrics["train_corr"] = float("nan")
+            if eval_states and eval_every > 0 and (((round_idx + 1) % eval_every == 0) or round_idx + 1 == num_rounds):
+                self._update_eval_sets(eval_states)
+            dt = perf_counter() - t0
+            metrics["trees_per_second"] = (cfg.pack_size / dt) if dt > 0 else float("inf")
+            metrics["round_seconds"] = dt
+            for stt in eval_states:
+                metrics[f"{stt['name']}_corr"] = _era_correlation_np(stt["era"], stt["y"], stt["preds"].cpu().numpy())
+            self._round_metrics.append(metrics)
+            if round_callback is not None:
+                round_callback(round_idx + 1, metrics)
+
+        trainer.flush_predictions()
+        torch.cuda.current_stream().synchronize()
+        return self
+
+    def train_predictions(self) -> np.ndarray:
+        """Predictions of the training rows as maintained during ``fit`` (original row order)."""
+        if self._trainer is None:
+            raise RuntimeError("Model must be fitted first")
+        self._trainer.flush_predictions()
+        p = self._trainer.preds.cpu().numpy()
+        if self._row_order is None:
+            return p
+        out = np.empty_like(p)
+        out[self._row_order] = p
+        return out
+
+    def _depth_log(self, depth: int, n_nodes: int, k: int) -> dict[str, object]:
+        blk = int(self.config.feature_block_size)
+        blk = k if (blk <= 0 or blk > k) else blk
+        return {
+            "nodes_processed": n_nodes, "nodes_skipped": 0, "rows_total": 0,
+            "feature_blocks": (k + blk - 1) // blk, "bincount_calls": 0,
+            "hist_ms": 0.0, "scan_ms": 0.0, "score_ms": 0.0, "partition_ms": 0.0,
+            "nodes_subtract_ok": 0, "nodes_rebuild": n_nodes, "nodes_subtract_fallback": 0,
+            "nodes_collapsed": n_nodes * (int(self.config.pack_size) - 1), "feature_block_size": blk,
+            "depth": depth, "feature_subset_size": k, "pack_size": int(self.config.pack_size),
+            "layer_feature_fraction": float(self.config.layer_feature_fraction),
+            "histogram_mode": self._histogram_mode, "seed": self.config.random_state,
+            "torch_threads": torch.get_num_threads(),
+        }
+
+    # -- evaluation sets -----------------------------------------------------
+    def _prepare_eval_sets(self, eval_sets):
+        states = []
+        if not eval_sets:
+            return states
+        for name, X_eval, y_eval, era_eval in eval_sets:
+            if y_eval is None:
+                raise ValueError(f"eval set '{name}' requires y values for correlation logging")
+            Xe = np.asarray(X_eval)
+            rows = self._pack_rows(Xe)
+            era_e = np.zeros(Xe.shape[0], dtype=np.int16) if era_eval is None else np.asarray(era_eval, dtype=np.int16)
+            if era_e.shape[0] != Xe.shape[0]:
+                raise ValueError(f"eval set '{name}' era ids must align with X rows")
+            states.append({"name": name, "rows": rows, "y": np.asarray(y_eval, dtype=np.float32), "era": era_e,
+                           "preds": torch.zeros(Xe.shape[0], dtype=torch.float32, device=self._device), "done": 0})
+        return states
+
+    def _update_eval_sets(self, states) -> None:
+        # predictions accumulate in tree order, so adding only the new rounds reproduces a
+        # from-scratch evaluation bit for bit
+        for stt in states:
+            new = self._distinct[stt["done"]:]
+            if not new:
+                continue
+            forest = self._pack_forest(new)
+            stt["preds"] = self._predict_packed(stt["rows"], forest, init=stt["preds"])
+            stt["done"] = len(self._distinct)
+
+    # -- prediction -------------------------------------------------------------
+    def _pack_rows(self, X: np.ndarray) -> PackedRows:
+        if self._binner is None:
+            raise RuntimeError("Model must be fitted before predict()")
+        X_np = X.detach().cpu().numpy() if isinstance(X, torch.Tensor) else np.asarray(X)
+        if self._binner.bin_edges is None:
+            if not detect_prebinned(X_np, self.config.max_bins):
+                raise ValueError("Input must already be prebinned when no edges are provided")
+            src = X_np if X_np.dtype in (np.uint8, np.int8) else X_np.astype(np.uint8)
+            return pack_row_major(src.view(np.uint8), None, self.config.max_bins)
+        return pack_row_major(X_np.astype(np.float32, copy=False), self._binner.bin_edges, self.config.max_bins)
+
+    def _pack_forest(self, distinct: Sequence[tuple[Tree, int]]) -> dict[str, torch.Tensor]:
+        arrs = [t.arrays() for t, _ in distinct]
+        offs = np.zeros(len(arrs) + 1, dtype=np.int32)
+        np.cumsum([a["feature"].shape[0] for a in arrs], out=offs[1:])
+        cat = {k: np.concatenate([a[k] for a in arrs]) for k in ("feature", "threshold", "left", "right", "value", "is_leaf")}
+        out = {k: torch.from_numpy(v).to(self._device) for k, v in cat.items()}
+        out["offsets"] = torch.from_numpy(offs).to(self._device)
+        out["repeat"] = torch.tensor([r for _, r in distinct], dtype=torch.int32, device=self._device)
+        out["n_trees"] = len(arrs)
+        return out
+
+    def _predict_packed(self, rows: PackedRows, forest: dict, init: torch.Tensor | None = None) -> torch.Tensor:
+        out = torch.empty(rows.n_rows, dtype=torch.float32, device=self._device)
+        if rows.n_rows == 0:
+            return out
+        f = forest
+        B.check(B.lib().pb_predict_rows(
+            rows.codes.data_ptr(), rows.n_rows, rows.pitch_row, rows.code_bits, f["feature"].data_ptr(),
+            f["threshold"].data_ptr(), f["left"].data_ptr(), f["right"].data_ptr(), f["value"].data_ptr(),
+            f["is_leaf"].data_ptr(), f["offsets"].data_ptr(), f["repeat"].data_ptr(), f["n_trees"],
+            float(self._tree_weight), out.data_ptr(), B._ptr(init) if init is not None else 0,
+            torch.cuda.current_stream().cuda_stream))
+        return out
+
+    def predict(self, X: np.ndarray) -> np.ndarray:
+        """``pred = sum over trees of tree_weight * tree(X)`` accumulated in tree order, float32
+        (``packboost/booster.py:658-712``)."""
+        if self._binner is None:
+            raise RuntimeError("Model must be fitted before predict()")
+        rows = self._pack_rows(X)
+        if not self._trees:
+            return np.zeros(rows.n_rows, dtype=np.float32)
+        if self._tree_weight is None:
+            raise RuntimeError("Missing _tree_weight; call fit() first.")
+        if self._trained_pack_size is not None and int(self.config.pack_size) != self._trained_pack_size:
+            raise RuntimeError("pack_size differs from training; keep it constant.")
+        if self._forest_cache is None or self._forest_cache["n_distinct"] != len(self._distinct):
+            self._forest_cache = self._pack_forest(self._distinct)
+            self._forest_cache["n_distinct"] = len(self._distinct)
+        return self._predict_packed(rows, self._forest_cache).cpu().numpy()
+
+    def predict_packwise(self, X: np.ndarray, block_size_trees: int = 8) -> np.ndarray:
+        if block_size_trees <= 0:
+            raise ValueError("block_size_trees must be positive")
+        if self._binner is None:
+            raise RuntimeError("Model must be fitted before predict_packwise()")
+        return self.predict(X)
+
+    def set_forest(self, trees: Sequence[Tree], tree_weight: float, *, bin_edges: np.ndarray | None = None,
+                   repeats: Sequence[int] | None = None) -> "PackBoost":
+        """Install an externally built ensemble (inference-only use)."""
+        reps = list(repeats) if repeats is not None else [1] * len(trees)
+        self._distinct = list(zip(trees, reps))
+        self._trees = [t for t, r in self._distinct for _ in range(r)]
+        self._tree_weight = float(tree_weight)
+        self._trained_pack_size = int(self.config.pack_size)
+        self._binner = BinningResult(bins=None, bin_edges=bin_edges, prebinned=bin_edges is None)
+        self._forest_cache = None
+        return self

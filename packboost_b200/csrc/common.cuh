@@ -1,0 +1,167 @@
+// Internal declarations shared by the kernels of libpackboost_b200.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+#include <string.h>
+
+#include "../../include/packboost_b200.h"
+
+namespace pb {
+
+// ---- error reporting --------------------------------------------------------------------
+
+void set_error(const char* fmt, ...);
+int fail_arg(const char* fmt, ...);
+int fail_cuda(cudaError_t e, const char* what);
+
+#define PB_CUDA_TRY(expr)                                   \
+    do {                                                    \
+        cudaError_t _e = (expr);                            \
+        if (_e != cudaSuccess) return pb::fail_cuda(_e, #expr); \
+    } while (0)
+
+#define PB_LAUNCH_CHECK(what)                               \
+    do {                                                    \
+        cudaError_t _e = cudaGetLastError();                \
+        if (_e != cudaSuccess) return pb::fail_cuda(_e, what); \
+    } while (0)
+
+#define PB_REQUIRE(cond, ...)                               \
+    do {                                                    \
+        if (!(cond)) return pb::fail_arg(__VA_ARGS__);      \
+    } while (0)
+
+// ---- constants --------------------------------------------------------------------------
+
+constexpr int kMaxDepth = PB_MAX_DEPTH;
+constexpr int kMaxCtx = 1 << (PB_MAX_DEPTH - 1);        // frontier nodes at the deepest level
+constexpr int kMaxTreeNodes = (1 << (PB_MAX_DEPTH + 1)); // 2^(D+1) - 1 rounded up
+constexpr int kMaxWinners = (1 << PB_MAX_DEPTH);         // sum over depths of frontier sizes (+1)
+constexpr uint16_t kSlotNone = 0xFFFFu;
+constexpr int kSingleTileRows = 32768;  // an era up to this size is accumulated by one CTA per feature group
+constexpr int kSplitTileRows = 16384;   // larger eras are cut into tiles of this many rows
+constexpr int kGqBits = 30;             // |gq| <= 2^30
+
+// ---- device-side tables -----------------------------------------------------------------
+
+// Best threshold of one (sampled feature, frontier node) pair.
+struct Cand {
+    float score;
+    int32_t k;            // index into thr_ids, -1: empty entry
+    uint32_t left_count;
+    uint32_t flags;       // bit 0: a globally valid threshold of this feature scored NaN
+    int64_t left_gq;
+};
+static_assert(sizeof(Cand) == 24, "Cand layout");
+
+struct FrontierNode {
+    int32_t tree_node;
+    int32_t count;
+    int64_t gq;
+};
+
+struct PartEntry {
+    int32_t feature;      // global id, -1: node keeps its rows (no split)
+    int32_t threshold;
+    uint16_t slot_left, slot_right;
+    uint16_t leaf_left, leaf_right;
+};
+static_assert(sizeof(PartEntry) == 16, "PartEntry layout");
+
+struct CtlHead {
+    uint32_t max_abs_bits;
+    float scale;
+    float inv_scale;
+    int32_t n_tree_nodes;
+    int64_t root_gq;
+    int32_t n_ctx[kMaxDepth + 2];
+    int32_t any_dir[kMaxDepth + 2];
+};
+
+// Addresses of the sub-tables inside the caller's control block.
+struct Ctl {
+    CtlHead* head;
+    FrontierNode* frontier[2];  // indexed by depth parity
+    PartEntry* part;
+    pb_round_log_header* log_head;
+    pb_winner* winners;
+    double* node_value;
+    float* delta;
+};
+
+constexpr size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+constexpr size_t kOffHead = 0;
+constexpr size_t kOffFrontier0 = align_up(sizeof(CtlHead), 256);
+constexpr size_t kOffFrontier1 = kOffFrontier0 + align_up(sizeof(FrontierNode) * kMaxCtx, 256);
+constexpr size_t kOffPart = kOffFrontier1 + align_up(sizeof(FrontierNode) * kMaxCtx, 256);
+constexpr size_t kOffLog = kOffPart + align_up(sizeof(PartEntry) * kMaxCtx, 256);
+constexpr size_t kLogBytes = sizeof(pb_round_log_header) + sizeof(pb_winner) * kMaxWinners;
+constexpr size_t kOffNodeValue = kOffLog + align_up(kLogBytes, 256);
+constexpr size_t kOffDelta = kOffNodeValue + align_up(sizeof(double) * kMaxTreeNodes, 256);
+constexpr size_t kCtlBytes = kOffDelta + align_up(sizeof(float) * kMaxTreeNodes, 256);
+
+inline __host__ __device__ Ctl ctl_view(void* base) {
+    char* p = static_cast<char*>(base);
+    Ctl c;
+    c.head = reinterpret_cast<CtlHead*>(p + kOffHead);
+    c.frontier[0] = reinterpret_cast<FrontierNode*>(p + kOffFrontier0);
+    c.frontier[1] = reinterpret_cast<FrontierNode*>(p + kOffFrontier1);
+    c.part = reinterpret_cast<PartEntry*>(p + kOffPart);
+    c.log_head = reinterpret_cast<pb_round_log_header*>(p + kOffLog);
+    c.winners = reinterpret_cast<pb_winner*>(p + kOffLog + sizeof(pb_round_log_header));
+    c.node_value = reinterpret_cast<double*>(p + kOffNodeValue);
+    c.delta = reinterpret_cast<float*>(p + kOffDelta);
+    return c;
+}
+
+inline int64_t rows_padded(int64_t n) { return (n + 255) / 256 * 256; }
+
+// ---- histogram launch (hist.cu) -----------------------------------------------------------
+
+struct HistLaunch {
+    const uint8_t* codes;
+    int64_t pitch;
+    int code_bits;
+    const int32_t* feat_rows;  // device: local feature row per histogram feature
+    int n_feat;
+    const int32_t* gq;
+    const uint16_t* slot;
+    const int32_t* era_offsets;
+    int n_eras;
+    int max_bins;
+    int max_era_rows;
+    const int32_t* n_nodes_ptr;  // device count of frontier nodes, or nullptr
+    int n_nodes;                 // upper bound (grid sizing) and value when n_nodes_ptr == nullptr
+    int node_stride;
+    uint32_t* cnt;
+    int64_t* gsum;
+};
+int launch_hist(const HistLaunch& h, cudaStream_t stream);
+
+// ---- scorer launch (score.cu) -------------------------------------------------------------
+
+struct ScoreLaunch {
+    const uint32_t* cnt;
+    const int64_t* gsum;
+    int n_feat;                  // features in this histogram block
+    const int32_t* feat_pos;     // device: sampled position of each histogram feature
+    int node_stride;
+    int n_nodes_max;
+    const int32_t* n_nodes_ptr;
+    const FrontierNode* frontier;
+    const int32_t* any_dir_ptr;
+    const float* inv_scale_ptr;
+    int n_eras;
+    int max_bins;
+    int n_thr;
+    const int32_t* thr_ids;
+    float lambda_l2, lambda_dro, direction_weight, era_alpha;
+    int min_samples_leaf;
+    Cand* cand;                  // [n_sampled][node_stride]
+};
+int launch_score(const ScoreLaunch& s, cudaStream_t stream);
+
+}  // namespace pb

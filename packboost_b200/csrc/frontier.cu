@@ -1,0 +1,626 @@
+// Round bookkeeping that stays on the device: gradient update and quantisation, winner
+// selection with the reference's tie-break, child numbering, leaf values, the row -> node
+// map update and the leaf-delta table for the prediction update.
+
+#include "common.cuh"
+
+namespace pb {
+
+namespace {
+
+constexpr int kRowThreads = 256;
+
+__device__ __forceinline__ float scale_from_max(float max_abs, float* inv) {
+    // power of two with max_abs * scale < 2^30
+    if (!(max_abs > 0.f) || !isfinite(max_abs)) {
+        *inv = 1.f;
+        return 1.f;
+    }
+    int ex;
+    frexpf(max_abs, &ex);  // max_abs = m * 2^ex, m in [0.5, 1)
+    int sh = kGqBits - ex;
+    sh = max(-100, min(100, sh));
+    *inv = ldexpf(1.f, -sh);
+    return ldexpf(1.f, sh);
+}
+
+__global__ void round_reset_kernel(Ctl c) {
+    if (threadIdx.x == 0 && blockIdx.x == 0) {
+        c.head->max_abs_bits = 0u;
+        c.head->root_gq = 0;
+        c.head->n_tree_nodes = 1;
+        for (int i = 0; i < kMaxDepth + 2; ++i) {
+            c.head->n_ctx[i] = 0;
+            c.head->any_dir[i] = 0;
+        }
+    }
+}
+
+// preds += delta[leaf] (optional), track max |preds - y|
+__global__ void __launch_bounds__(kRowThreads) preds_absmax_kernel(
+    float* __restrict__ preds, const float* __restrict__ y, const uint16_t* __restrict__ leaf,
+    const float* __restrict__ delta, int64_t n, int apply, CtlHead* head) {
+    float m = 0.f;
+    for (int64_t r = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; r < n; r += (int64_t)gridDim.x * blockDim.x) {
+        float p = preds[r];
+        if (apply) {
+            p = __fadd_rn(p, delta[leaf[r]]);
+            preds[r] = p;
+        }
+        const float g = __fsub_rn(p, y[r]);
+        m = fmaxf(m, fabsf(g));
+    }
+    for (int d = 16; d > 0; d >>= 1) m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, d));
+    __shared__ float wm[kRowThreads / 32];
+    if ((threadIdx.x & 31) == 0) wm[threadIdx.x >> 5] = m;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int i = 1; i < kRowThreads / 32; ++i) m = fmaxf(m, wm[i]);
+        atomicMax(&head->max_abs_bits, __float_as_uint(m));  // non-negative floats order like their bits
+    }
+}
+
+// gq = rint((preds - y) * scale); rows back to the root; sum of gq
+__global__ void __launch_bounds__(kRowThreads) quantise_kernel(
+    const float* __restrict__ preds, const float* __restrict__ y, int32_t* __restrict__ gq,
+    uint16_t* __restrict__ slot, uint16_t* __restrict__ leaf, int64_t n, int64_t n_pad, CtlHead* head) {
+    float inv;
+    const float scale = scale_from_max(__uint_as_float(head->max_abs_bits), &inv);
+    long long acc = 0;
+    for (int64_t r = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; r < n_pad; r += (int64_t)gridDim.x * blockDim.x) {
+        if (r < n) {
+            const float g = __fsub_rn(preds[r], y[r]);
+            const int q = __float2int_rn(__fmul_rn(g, scale));
+            gq[r] = q;
+            slot[r] = 0;
+            acc += q;
+        } else {
+            gq[r] = 0;
+            slot[r] = kSlotNone;
+        }
+        leaf[r] = 0;
+    }
+    for (int d = 16; d > 0; d >>= 1) acc += __shfl_xor_sync(0xFFFFFFFFu, acc, d);
+    __shared__ long long ws[kRowThreads / 32];
+    if ((threadIdx.x & 31) == 0) ws[threadIdx.x >> 5] = acc;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int i = 1; i < kRowThreads / 32; ++i) acc += ws[i];
+        atomicAdd(reinterpret_cast<unsigned long long*>(&head->root_gq), (unsigned long long)acc);
+    }
+}
+
+__global__ void root_kernel(Ctl c, int64_t n, int min_leaf, double lambda) {
+    if (threadIdx.x != 0 || blockIdx.x != 0) return;
+    float inv;
+    const float scale = scale_from_max(__uint_as_float(c.head->max_abs_bits), &inv);
+    c.head->scale = scale;
+    c.head->inv_scale = inv;
+    const long long g = c.head->root_gq;
+    FrontierNode fn;
+    fn.tree_node = 0;
+    fn.count = (int32_t)n;
+    fn.gq = g;
+    c.frontier[0][0] = fn;
+    c.head->n_ctx[0] = (n >= 2 * (int64_t)min_leaf) ? 1 : 0;
+    c.head->any_dir[0] = (g != 0) ? 1 : 0;
+    const float g32 = __fmul_rn(__ll2float_rn(g), inv);
+    const double v = (n > 0) ? (-(double)g32 / ((double)(float)n + lambda)) : 0.0;
+    c.node_value[0] = v;
+    pb_round_log_header* h = c.log_head;
+    h->root_value = v;
+    h->scale = scale;
+    h->max_abs_grad = __uint_as_float(c.head->max_abs_bits);
+    h->root_gq = g;
+    for (int i = 0; i <= kMaxDepth; ++i) h->n_ctx[i] = 0;
+    h->n_ctx[0] = c.head->n_ctx[0];
+    h->n_tree_nodes = 1;
+}
+
+// ---- winner selection --------------------------------------------------------------------
+
+struct SelectArgs {
+    Ctl c;
+    int depth;
+    int max_depth;
+    const Cand* cand;
+    int node_stride;
+    const int32_t* sampled;  // global feature ids in sampled order
+    int n_sampled;
+    int block_size;
+    const int32_t* thr_ids;
+    int min_leaf;
+    double lambda;
+};
+
+__global__ void __launch_bounds__(1024) select_kernel(SelectArgs a) {
+    Ctl& c = a.c;
+    const int n_ctx = c.head->n_ctx[a.depth];
+    if (n_ctx <= 0) return;
+    const FrontierNode* cur = c.frontier[a.depth & 1];
+    FrontierNode* nxt = c.frontier[(a.depth + 1) & 1];
+    pb_winner* win = c.winners + ((1 << a.depth) - 1);
+    const float inv = c.head->inv_scale;
+
+    // ---- per node: in-block winner, then cross-block merge ----
+    for (int n = threadIdx.x; n < n_ctx; n += blockDim.x) {
+        float best_s = -INFINITY;
+        long long best_c = -1, best_lg = 0;
+        int best_f = -1, best_t = -1;
+        for (int b0 = 0; b0 < a.n_sampled; b0 += a.block_size) {
+            const int b1 = min(a.n_sampled, b0 + a.block_size);
+            float bs = -INFINITY;
+            long long bc = -1, blg = 0;
+            int bp = -1, bk = -1;
+            bool has_nan = false;
+            for (int p = b0; p < b1; ++p) {
+                const Cand cd = a.cand[(size_t)p * a.node_stride + n];
+                if (cd.flags & 1u) has_nan = true;
+                if (cd.k < 0) continue;
+                if ((cd.score > bs) || (cd.score == bs && (long long)cd.left_count >= bc)) {
+                    bs = cd.score; bc = cd.left_count; blg = cd.left_gq; bp = p; bk = cd.k;
+                }
+            }
+            if (has_nan || bp < 0) continue;
+            const int feat = a.sampled[bp];
+            const int thr = a.thr_ids[bk];
+            const bool upd = (bs > best_s) ||
+                             (bs == best_s && ((bc > best_c) ||
+                                               (bc == best_c && ((feat > best_f) || (feat == best_f && thr > best_t)))));
+            if (upd) { best_s = bs; best_c = bc; best_lg = blg; best_f = feat; best_t = thr; }
+        }
+        const FrontierNode fn = cur[n];
+        pb_winner w;
+        w.feature = best_f;
+        w.threshold = best_t;
+        w.score = best_s;
+        w.tree_node = fn.tree_node;
+        w.left_count = (best_f >= 0) ? best_c : 0;
+        w.total_count = fn.count;
+        w.left_gq = (best_f >= 0) ? best_lg : 0;
+        w.total_gq = fn.gq;
+        w.left_id = -1;
+        w.right_id = -1;
+        const float tg32 = __fmul_rn(__ll2float_rn(fn.gq), inv);
+        const float lg32 = __fmul_rn(__ll2float_rn(w.left_gq), inv);
+        const float th32 = (float)fn.count;
+        const float lh32 = (float)w.left_count;
+        w.left_grad = lg32;
+        w.total_grad = tg32;
+        if (best_f >= 0) {
+            w.left_value = -(double)lg32 / ((double)lh32 + a.lambda);
+            const double rg = (double)tg32 - (double)lg32;
+            const double rh = (double)th32 - (double)lh32;
+            w.right_value = -rg / (rh + a.lambda);
+        } else {
+            // no usable candidate: the node stays a leaf with its Newton value
+            w.left_value = -(double)tg32 / ((double)th32 + a.lambda);
+            w.right_value = w.left_value;
+        }
+        win[n] = w;
+    }
+    __syncthreads();
+
+    // ---- sequential numbering of children and of the next frontier ----
+    if (threadIdx.x == 0) {
+        int next_id = c.head->n_tree_nodes;
+        int next_slot = 0;
+        int any_dir = 0;
+        const bool keep_frontier = (a.depth + 1) < a.max_depth;
+        for (int n = 0; n < n_ctx; ++n) {
+            pb_winner& w = win[n];
+            PartEntry pe;
+            pe.feature = w.feature;
+            pe.threshold = w.threshold;
+            pe.slot_left = pe.slot_right = kSlotNone;
+            pe.leaf_left = pe.leaf_right = (uint16_t)w.tree_node;
+            if (w.feature >= 0) {
+                w.left_id = next_id;
+                w.right_id = next_id + 1;
+                next_id += 2;
+                pe.leaf_left = (uint16_t)w.left_id;
+                pe.leaf_right = (uint16_t)w.right_id;
+                c.node_value[w.left_id] = w.left_value;
+                c.node_value[w.right_id] = w.right_value;
+                const long long lc = w.left_count, rc = w.total_count - w.left_count;
+                const long long lg = w.left_gq, rg = w.total_gq - w.left_gq;
+                if (keep_frontier && lc >= 2ll * a.min_leaf) {
+                    FrontierNode fn; fn.tree_node = w.left_id; fn.count = (int32_t)lc; fn.gq = lg;
+                    nxt[next_slot] = fn;
+                    pe.slot_left = (uint16_t)next_slot++;
+                    any_dir |= (lg != 0);
+                }
+                if (keep_frontier && rc >= 2ll * a.min_leaf) {
+                    FrontierNode fn; fn.tree_node = w.right_id; fn.count = (int32_t)rc; fn.gq = rg;
+                    nxt[next_slot] = fn;
+                    pe.slot_right = (uint16_t)next_slot++;
+                    any_dir |= (rg != 0);
+                }
+            } else {
+                c.node_value[w.tree_node] = w.left_value;
+            }
+            c.part[n] = pe;
+        }
+        c.head->n_tree_nodes = next_id;
+        c.head->n_ctx[a.depth + 1] = next_slot;
+        c.head->any_dir[a.depth + 1] = any_dir;
+        c.log_head->n_ctx[a.depth] = n_ctx;
+        if (a.depth + 1 <= kMaxDepth) c.log_head->n_ctx[a.depth + 1] = next_slot;
+        c.log_head->n_tree_nodes = next_id;
+    }
+}
+
+// ---- row -> node map ------------------------------------------------------------------------
+
+template <int BITS>
+__device__ __forceinline__ int load_code(const uint8_t* codes, int64_t pitch, int frow, int64_t r) {
+    if (BITS == 4) {
+        const uint8_t b = codes[(int64_t)frow * pitch + (r >> 1)];
+        return (b >> ((r & 1) * 4)) & 0xF;
+    }
+    return codes[(int64_t)frow * pitch + r];
+}
+
+struct PartArgs {
+    Ctl c;
+    int depth;
+    const uint8_t* codes;
+    int64_t pitch;
+    const int32_t* feat_local;
+    uint16_t* slot;
+    uint16_t* leaf;
+    int64_t n;
+    uint32_t* bits;        // goleft_bits output
+    const uint32_t* bits_in;  // apply_bits input
+};
+
+// mode 0: fused (decide + apply); mode 1: write go-left bits for locally held features;
+// mode 2: apply bits
+template <int BITS, int MODE>
+__global__ void __launch_bounds__(kRowThreads) partition_kernel(PartArgs a) {
+    extern __shared__ PartEntry tab[];
+    const int n_ctx = a.c.head->n_ctx[a.depth];
+    if (n_ctx <= 0) return;
+    for (int i = threadIdx.x; i < n_ctx; i += blockDim.x) tab[i] = a.c.part[i];
+    __syncthreads();
+    const int64_t n_round = (a.n + 31) / 32 * 32;
+    for (int64_t r = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; r < n_round; r += (int64_t)gridDim.x * blockDim.x) {
+        const int s = (r < a.n) ? a.slot[r] : kSlotNone;
+        bool left = false;
+        PartEntry pe;
+        pe.feature = -1;
+        if (s != kSlotNone && s < n_ctx) {
+            pe = tab[s];
+            if (pe.feature >= 0) {
+                if (MODE == 2) {
+                    left = (a.bits_in[r >> 5] >> (r & 31)) & 1u;
+                } else {
+                    const int frow = a.feat_local[pe.feature];
+                    if (frow >= 0) left = load_code<BITS>(a.codes, a.pitch, frow, r) <= pe.threshold;
+                }
+            }
+        }
+        if (MODE == 1) {
+            const unsigned m = __ballot_sync(0xFFFFFFFFu, left);
+            if ((threadIdx.x & 31) == 0) a.bits[r >> 5] = m;
+        } else if (s != kSlotNone) {
+            if (s < n_ctx && pe.feature >= 0) {
+                a.slot[r] = left ? pe.slot_left : pe.slot_right;
+                a.leaf[r] = left ? pe.leaf_left : pe.leaf_right;
+            } else {
+                a.slot[r] = kSlotNone;
+            }
+        }
+    }
+}
+
+__global__ void delta_kernel(Ctl c, int pack_size, float lr) {
+    const int n = c.head->n_tree_nodes;
+    for (int t = blockIdx.x * blockDim.x + threadIdx.x; t < n; t += gridDim.x * blockDim.x) {
+        const float v = (float)c.node_value[t];
+        float acc = 0.f;
+        for (int b = 0; b < pack_size; ++b) acc = __fadd_rn(acc, v);
+        c.delta[t] = __fmul_rn(lr, acc);
+    }
+}
+
+__global__ void __launch_bounds__(kRowThreads) apply_delta_kernel(float* preds, const uint16_t* leaf,
+                                                                  const float* delta, int64_t n) {
+    for (int64_t r = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; r < n; r += (int64_t)gridDim.x * blockDim.x)
+        preds[r] = __fadd_rn(preds[r], delta[leaf[r]]);
+}
+
+int row_grid(int64_t n) {
+    int64_t b = (n + kRowThreads - 1) / kRowThreads;
+    const int64_t cap = 148 * 16;
+    if (b > cap) b = cap;
+    if (b < 1) b = 1;
+    return (int)b;
+}
+
+}  // namespace
+
+// Candidate table of a depth lives at the start of the workspace: [n_sampled][node_stride].
+static inline int node_stride_of(int64_t depth) { return 1 << depth; }
+
+}  // namespace pb
+
+using namespace pb;
+
+static int check_state(const pb_train_state* st) {
+    PB_REQUIRE(st != nullptr, "state is null");
+    PB_REQUIRE(st->n_rows > 0 && st->n_rows < (1ll << 31) - 512, "n_rows=%lld out of range", (long long)st->n_rows);
+    PB_REQUIRE(st->code_bits == 4 || st->code_bits == 8, "code_bits must be 4 or 8");
+    PB_REQUIRE(st->max_bins >= 2 && st->max_bins <= 256, "max_bins=%lld outside [2,256]", (long long)st->max_bins);
+    PB_REQUIRE(st->code_bits == 8 || st->max_bins <= 16, "4-bit codes need max_bins <= 16");
+    PB_REQUIRE(st->max_depth >= 1 && st->max_depth <= PB_MAX_DEPTH, "max_depth=%lld outside [1,%d]",
+               (long long)st->max_depth, PB_MAX_DEPTH);
+    PB_REQUIRE(st->n_eras >= 1 && st->n_eras <= 32767, "n_eras=%lld outside [1,32767]", (long long)st->n_eras);
+    PB_REQUIRE(st->pitch % 128 == 0 && st->pitch * (st->code_bits == 4 ? 2 : 1) >= rows_padded(st->n_rows),
+               "pitch=%lld does not cover the padded rows", (long long)st->pitch);
+    PB_REQUIRE(st->n_thresholds >= 1 && st->n_thresholds < st->max_bins, "n_thresholds out of range");
+    PB_REQUIRE(st->codes && st->era_offsets && st->thr_ids && st->feat_local && st->y && st->preds && st->gq &&
+                   st->slot && st->leaf && st->ctl && st->workspace,
+               "a device buffer of the training state is null");
+    PB_REQUIRE(st->lambda_l2 > 0.0, "lambda_l2 must be positive");
+    PB_REQUIRE(((uintptr_t)st->codes % 16 == 0) && ((uintptr_t)st->gq % 16 == 0) && ((uintptr_t)st->slot % 16 == 0),
+               "codes, gq and slot must be 16-byte aligned");
+    return PB_OK;
+}
+
+extern "C" int64_t pb_ctl_bytes(void) { return (int64_t)kCtlBytes; }
+
+extern "C" int64_t pb_workspace_min_bytes(const pb_train_state* st) {
+    if (!st) return 0;
+    // candidate table at the deepest level for every feature + one feature of histogram
+    const int64_t stride = 1ll << (st->max_depth - 1);
+    const int64_t cand = (int64_t)sizeof(Cand) * st->n_features_total * stride;
+    const int64_t hist_one = stride * st->n_eras * st->max_bins * 12;
+    return align_up((size_t)cand, 256) + hist_one + 4096;
+}
+
+extern "C" int pb_train_prepare(pb_train_state* st, const int32_t* era_offsets_host) {
+    PB_REQUIRE(st && era_offsets_host, "null argument");
+    int64_t mx = 0;
+    PB_REQUIRE(era_offsets_host[0] == 0, "era_offsets[0] must be 0");
+    for (int64_t e = 0; e < st->n_eras; ++e) {
+        const int64_t len = (int64_t)era_offsets_host[e + 1] - era_offsets_host[e];
+        PB_REQUIRE(len >= 0, "era_offsets must be non-decreasing");
+        if (len > mx) mx = len;
+    }
+    PB_REQUIRE(era_offsets_host[st->n_eras] == st->n_rows, "era_offsets[E] must equal n_rows");
+    st->max_era_rows = mx;
+    st->hist_rows_per_tile = (mx <= kSingleTileRows) ? kSingleTileRows : kSplitTileRows;
+    int rc = check_state(st);
+    if (rc) return rc;
+    PB_REQUIRE(st->workspace_bytes >= pb_workspace_min_bytes(st), "workspace too small: %lld < %lld",
+               (long long)st->workspace_bytes, (long long)pb_workspace_min_bytes(st));
+    return PB_OK;
+}
+
+extern "C" int pb_round_begin(const pb_train_state* st, int64_t apply_previous, void* stream_) {
+    int rc = check_state(st);
+    if (rc) return rc;
+    cudaStream_t stream = (cudaStream_t)stream_;
+    Ctl c = ctl_view(st->ctl);
+    const int g = row_grid(st->n_rows);
+    round_reset_kernel<<<1, 32, 0, stream>>>(c);
+    preds_absmax_kernel<<<g, kRowThreads, 0, stream>>>(st->preds, st->y, st->leaf, c.delta, st->n_rows,
+                                                        apply_previous ? 1 : 0, c.head);
+    quantise_kernel<<<g, kRowThreads, 0, stream>>>(st->preds, st->y, st->gq, st->slot, st->leaf, st->n_rows,
+                                                    rows_padded(st->n_rows), c.head);
+    root_kernel<<<1, 32, 0, stream>>>(c, st->n_rows, (int)st->min_samples_leaf, st->lambda_l2);
+    PB_LAUNCH_CHECK("round_begin");
+    return PB_OK;
+}
+
+extern "C" int pb_candidates_buffer(const pb_train_state* st, int64_t depth, int64_t n_sampled, void** ptr,
+                                    int64_t* bytes) {
+    PB_REQUIRE(st && ptr && bytes, "null argument");
+    PB_REQUIRE(depth >= 0 && depth < st->max_depth, "depth out of range");
+    *ptr = st->workspace;
+    *bytes = (int64_t)sizeof(Cand) * n_sampled * node_stride_of(depth);
+    return PB_OK;
+}
+
+extern "C" int pb_depth_clear_candidates(const pb_train_state* st, int64_t depth, int64_t n_sampled, void* stream) {
+    void* p;
+    int64_t b;
+    int rc = pb_candidates_buffer(st, depth, n_sampled, &p, &b);
+    if (rc) return rc;
+    PB_CUDA_TRY(cudaMemsetAsync(p, 0, (size_t)b, (cudaStream_t)stream));
+    return PB_OK;
+}
+
+extern "C" int pb_depth_hist_score(const pb_train_state* st, int64_t depth, const int32_t* feat_rows,
+                                   const int32_t* feat_pos, int64_t n_feat, int64_t n_sampled, void* stream_) {
+    int rc = check_state(st);
+    if (rc) return rc;
+    PB_REQUIRE(depth >= 0 && depth < st->max_depth, "depth out of range");
+    PB_REQUIRE(n_feat >= 0 && n_feat <= n_sampled && n_sampled <= st->n_features_total, "feature counts out of range");
+    if (n_feat == 0) return PB_OK;
+    PB_REQUIRE(feat_rows && feat_pos, "null feature list");
+    cudaStream_t stream = (cudaStream_t)stream_;
+    Ctl c = ctl_view(st->ctl);
+    const int stride = node_stride_of(depth);
+    const size_t cand_bytes = align_up(sizeof(Cand) * (size_t)n_sampled * stride, 256);
+    PB_REQUIRE((int64_t)cand_bytes < st->workspace_bytes, "workspace too small for the candidate table");
+    char* ws = static_cast<char*>(st->workspace);
+    Cand* cand = reinterpret_cast<Cand*>(ws);
+    const size_t per_feat_cells = (size_t)stride * st->n_eras * st->max_bins;
+    const size_t per_feat_bytes = per_feat_cells * 12;
+    int64_t fb = (int64_t)((st->workspace_bytes - cand_bytes - 256) / per_feat_bytes);
+    PB_REQUIRE(fb >= 1, "workspace too small for one feature of histogram at depth %lld", (long long)depth);
+    if (fb > n_feat) fb = n_feat;
+    // gsum (int64) first, then cnt: both 8-byte aligned
+    int64_t* gsum = reinterpret_cast<int64_t*>(ws + cand_bytes);
+    uint32_t* cnt = reinterpret_cast<uint32_t*>(ws + cand_bytes + align_up((size_t)fb * per_feat_cells * 8, 256));
+    if ((char*)cnt + (size_t)fb * per_feat_cells * 4 > ws + st->workspace_bytes) fb -= 1;
+    PB_REQUIRE(fb >= 1, "workspace too small for one feature of histogram at depth %lld", (long long)depth);
+
+    for (int64_t f0 = 0; f0 < n_feat; f0 += fb) {
+        const int nf = (int)((n_feat - f0 < fb) ? (n_feat - f0) : fb);
+        HistLaunch h;
+        h.codes = st->codes;
+        h.pitch = st->pitch;
+        h.code_bits = (int)st->code_bits;
+        h.feat_rows = feat_rows + f0;
+        h.n_feat = nf;
+        h.gq = st->gq;
+        h.slot = st->slot;
+        h.era_offsets = st->era_offsets;
+        h.n_eras = (int)st->n_eras;
+        h.max_bins = (int)st->max_bins;
+        h.max_era_rows = (int)st->max_era_rows;
+        h.n_nodes_ptr = &c.head->n_ctx[depth];
+        h.n_nodes = stride;
+        h.node_stride = stride;
+        h.cnt = cnt;
+        h.gsum = gsum;
+        rc = launch_hist(h, stream);
+        if (rc) return rc;
+        ScoreLaunch s;
+        s.cnt = cnt;
+        s.gsum = gsum;
+        s.n_feat = nf;
+        s.feat_pos = feat_pos + f0;
+        s.node_stride = stride;
+        s.n_nodes_max = stride;
+        s.n_nodes_ptr = &c.head->n_ctx[depth];
+        s.frontier = c.frontier[depth & 1];
+        s.any_dir_ptr = &c.head->any_dir[depth];
+        s.inv_scale_ptr = &c.head->inv_scale;
+        s.n_eras = (int)st->n_eras;
+        s.max_bins = (int)st->max_bins;
+        s.n_thr = (int)st->n_thresholds;
+        s.thr_ids = st->thr_ids;
+        s.lambda_l2 = (float)st->lambda_l2;
+        s.lambda_dro = (float)st->lambda_dro;
+        s.direction_weight = (float)st->direction_weight;
+        s.era_alpha = (float)(st->era_alpha > 0.0 ? st->era_alpha : 0.0);
+        s.min_samples_leaf = (int)st->min_samples_leaf;
+        s.cand = cand;
+        rc = launch_score(s, stream);
+        if (rc) return rc;
+    }
+    return PB_OK;
+}
+
+extern "C" int pb_depth_select(const pb_train_state* st, int64_t depth, const int32_t* sampled_features,
+                               int64_t n_sampled, void* stream_) {
+    int rc = check_state(st);
+    if (rc) return rc;
+    PB_REQUIRE(depth >= 0 && depth < st->max_depth, "depth out of range");
+    PB_REQUIRE(sampled_features && n_sampled >= 1, "empty feature subset");
+    SelectArgs a;
+    a.c = ctl_view(st->ctl);
+    a.depth = (int)depth;
+    a.max_depth = (int)st->max_depth;
+    a.cand = reinterpret_cast<const Cand*>(st->workspace);
+    a.node_stride = node_stride_of(depth);
+    a.sampled = sampled_features;
+    a.n_sampled = (int)n_sampled;
+    int blk = (int)st->feature_block_size;
+    if (blk <= 0 || blk > n_sampled) blk = (int)n_sampled;
+    a.block_size = blk;
+    a.thr_ids = st->thr_ids;
+    a.min_leaf = (int)st->min_samples_leaf;
+    a.lambda = st->lambda_l2;
+    select_kernel<<<1, 1024, 0, (cudaStream_t)stream_>>>(a);
+    PB_LAUNCH_CHECK("select_kernel");
+    return PB_OK;
+}
+
+template <int MODE>
+static int launch_partition(const pb_train_state* st, int64_t depth, uint32_t* bits, const uint32_t* bits_in,
+                            void* stream_) {
+    int rc = check_state(st);
+    if (rc) return rc;
+    PB_REQUIRE(depth >= 0 && depth < st->max_depth, "depth out of range");
+    PartArgs a;
+    a.c = ctl_view(st->ctl);
+    a.depth = (int)depth;
+    a.codes = st->codes;
+    a.pitch = st->pitch;
+    a.feat_local = st->feat_local;
+    a.slot = st->slot;
+    a.leaf = st->leaf;
+    a.n = st->n_rows;
+    a.bits = bits;
+    a.bits_in = bits_in;
+    const size_t smem = sizeof(PartEntry) * (size_t)(1 << depth);
+    const int g = row_grid(st->n_rows);
+    cudaStream_t stream = (cudaStream_t)stream_;
+    if (st->code_bits == 4)
+        partition_kernel<4, MODE><<<g, kRowThreads, smem, stream>>>(a);
+    else
+        partition_kernel<8, MODE><<<g, kRowThreads, smem, stream>>>(a);
+    PB_LAUNCH_CHECK("partition_kernel");
+    return PB_OK;
+}
+
+extern "C" int pb_depth_partition(const pb_train_state* st, int64_t depth, void* stream) {
+    return launch_partition<0>(st, depth, nullptr, nullptr, stream);
+}
+
+extern "C" int pb_depth_goleft_bits(const pb_train_state* st, int64_t depth, uint32_t* bits, void* stream) {
+    PB_REQUIRE(bits, "bits is null");
+    return launch_partition<1>(st, depth, bits, nullptr, stream);
+}
+
+extern "C" int pb_depth_apply_bits(const pb_train_state* st, int64_t depth, const uint32_t* bits, void* stream) {
+    PB_REQUIRE(bits, "bits is null");
+    return launch_partition<2>(st, depth, nullptr, bits, stream);
+}
+
+extern "C" int pb_round_end(const pb_train_state* st, void* stream) {
+    int rc = check_state(st);
+    if (rc) return rc;
+    delta_kernel<<<8, 256, 0, (cudaStream_t)stream>>>(ctl_view(st->ctl), (int)st->pack_size, (float)st->learning_rate);
+    PB_LAUNCH_CHECK("delta_kernel");
+    return PB_OK;
+}
+
+extern "C" int pb_apply_leaf_delta(const pb_train_state* st, void* stream) {
+    int rc = check_state(st);
+    if (rc) return rc;
+    Ctl c = ctl_view(st->ctl);
+    apply_delta_kernel<<<row_grid(st->n_rows), kRowThreads, 0, (cudaStream_t)stream>>>(st->preds, st->leaf, c.delta,
+                                                                                      st->n_rows);
+    PB_LAUNCH_CHECK("apply_delta_kernel");
+    return PB_OK;
+}
+
+extern "C" int pb_round_log_buffer(const pb_train_state* st, void** ptr, int64_t* bytes) {
+    PB_REQUIRE(st && ptr && bytes && st->ctl, "null argument");
+    Ctl c = ctl_view(st->ctl);
+    *ptr = c.log_head;
+    *bytes = (int64_t)(sizeof(pb_round_log_header) + sizeof(pb_winner) * ((1ll << st->max_depth) - 1));
+    return PB_OK;
+}
+
+extern "C" int pb_hist_build(const pb_train_state* st, const int32_t* feat_rows, int64_t n_feat, int64_t n_nodes,
+                             int64_t node_stride, uint32_t* cnt, int64_t* gsum, void* stream) {
+    int rc = check_state(st);
+    if (rc) return rc;
+    PB_REQUIRE(feat_rows && cnt && gsum, "null argument");
+    PB_REQUIRE(n_nodes >= 1 && n_nodes <= node_stride && node_stride < 65535, "node counts out of range");
+    HistLaunch h;
+    h.codes = st->codes;
+    h.pitch = st->pitch;
+    h.code_bits = (int)st->code_bits;
+    h.feat_rows = feat_rows;
+    h.n_feat = (int)n_feat;
+    h.gq = st->gq;
+    h.slot = st->slot;
+    h.era_offsets = st->era_offsets;
+    h.n_eras = (int)st->n_eras;
+    h.max_bins = (int)st->max_bins;
+    h.max_era_rows = (int)st->max_era_rows;
+    h.n_nodes_ptr = nullptr;
+    h.n_nodes = (int)n_nodes;
+    h.node_stride = (int)node_stride;
+    h.cnt = cnt;
+    h.gsum = gsum;
+    return launch_hist(h, (cudaStream_t)stream);
+}

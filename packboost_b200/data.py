@@ -1,0 +1,224 @@
+"""Binning and bit-packing of features for the B200 backend.
+
+Host-facing names follow the reference's data utilities
+(``packboost/data.py``): ``BinningResult``, ``detect_prebinned``,
+``quantile_bin``, ``preprocess_features``, ``apply_bins``, ``build_era_index``.
+The code assignment (``searchsorted`` against the per-feature edges) and the
+packing into 4-bit / 8-bit lanes run on the device; the quantile edges
+themselves are order statistics interpolated in float64 by ``np.quantile``,
+exactly as the reference computes them, so that bin codes are bit-identical.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Iterable, Sequence
+
+import numpy as np
+import torch
+
+from . import backends as B
+
+
+@dataclass(slots=True)
+class BinningResult:
+    """Preprocessed training data (``packboost/data.py:12-18``).  ``bins`` is only
+    materialised on request; training keeps the packed device matrix instead."""
+
+    bins: np.ndarray | None
+    bin_edges: np.ndarray | None
+    prebinned: bool
+
+
+def ensure_numpy(array) -> np.ndarray:
+    if isinstance(array, np.ndarray):
+        return array
+    if isinstance(array, torch.Tensor):
+        return array.detach().cpu().numpy()
+    return np.asarray(array)
+
+
+def detect_prebinned(X: np.ndarray, max_bins: int) -> bool:
+    """Integer input whose values already are bin ids (``packboost/data.py:32-42``)."""
+    if not np.issubdtype(X.dtype, np.integer):
+        return False
+    if X.size and X.min() < 0:
+        return False
+    top = int(X.max()) if X.size else 0
+    if top >= max_bins:
+        return False
+    return top <= 127
+
+
+def quantile_edges(X: np.ndarray, max_bins: int) -> np.ndarray:
+    """``[max_bins-1, F]`` float32 edges at the interior quantiles (``packboost/data.py:49-50``)."""
+    q = np.linspace(0.0, 1.0, max_bins + 1, dtype=np.float64)[1:-1]
+    return np.quantile(X, q, axis=0, method="linear").astype(np.float32)
+
+
+def code_bits_for(max_bins: int) -> int:
+    return 4 if max_bins <= 16 else 8
+
+
+def _device() -> torch.device:
+    if not B.cuda_available():
+        raise RuntimeError("packboost_b200 needs its CUDA library and a B200-class device; there is no CPU path")
+    return torch.device("cuda", torch.cuda.current_device())
+
+
+_CHUNK_BYTES = 256 << 20
+
+
+def _row_chunks(n_rows: int, row_bytes: int) -> Iterable[tuple[int, int]]:
+    step = max(256, (_CHUNK_BYTES // max(row_bytes, 1)) // 256 * 256)
+    for a in range(0, n_rows, step):
+        yield a, min(n_rows, a + step)
+
+
+class PackedMatrix:
+    """Feature-major packed bin codes on the device (layout of ``pb_train_state.codes``)."""
+
+    def __init__(self, n_rows: int, n_features_local: int, code_bits: int, device: torch.device):
+        self.n_rows = int(n_rows)
+        self.rows_padded = (self.n_rows + 255) // 256 * 256
+        self.code_bits = int(code_bits)
+        self.pitch = (self.rows_padded * code_bits // 8 + 127) // 128 * 128
+        self.n_features_local = int(n_features_local)
+        self.codes = torch.zeros((max(self.n_features_local, 1), self.pitch), dtype=torch.uint8, device=device)
+
+    def unpack(self) -> torch.Tensor:
+        """``uint8 [F_local, n_rows]`` (tests and the legacy feature-major predictors)."""
+        if self.code_bits == 8:
+            return self.codes[: self.n_features_local, : self.n_rows].contiguous()
+        lo = self.codes & 0xF
+        hi = self.codes >> 4
+        full = torch.stack([lo, hi], dim=2).reshape(self.codes.shape[0], -1)
+        return full[: self.n_features_local, : self.n_rows].contiguous()
+
+
+def pack_feature_major(
+    X: np.ndarray,
+    edges: np.ndarray | None,
+    max_bins: int,
+    *,
+    row_order: np.ndarray | None = None,
+    feature_map: np.ndarray | None = None,
+    n_features_local: int | None = None,
+) -> PackedMatrix:
+    """Bin (when ``edges`` is given) and pack host data into a device ``PackedMatrix``.
+
+    ``row_order`` lists source rows in destination order (era-sorted rows);
+    ``feature_map[j]`` is the destination feature row of column ``j`` or -1.
+    """
+    dev = _device()
+    lib = B.lib()
+    n_rows, n_feat = X.shape
+    bits = code_bits_for(max_bins)
+    n_local = n_feat if n_features_local is None else n_features_local
+    pm = PackedMatrix(n_rows, n_local, bits, dev)
+    fmap_t = None
+    if feature_map is not None:
+        fmap_t = torch.from_numpy(np.ascontiguousarray(feature_map, dtype=np.int32)).to(dev)
+    is_f32 = edges is not None
+    edges_t = torch.from_numpy(np.ascontiguousarray(edges, dtype=np.float32)).to(dev) if is_f32 else None
+    stream = torch.cuda.current_stream().cuda_stream
+    src_dtype = np.float32 if is_f32 else np.uint8
+    for a, b in _row_chunks(n_rows, n_feat * (4 if is_f32 else 1)):
+        rows = X[a:b] if row_order is None else X[row_order[a:b]]
+        chunk = torch.from_numpy(np.ascontiguousarray(rows, dtype=src_dtype)).to(dev, non_blocking=False)
+        if is_f32:
+            B.check(lib.pb_bin_pack_f32(chunk.data_ptr(), b - a, n_feat, a, edges_t.data_ptr(), edges_t.shape[0],
+                                        max_bins, B._ptr(fmap_t), pm.codes.data_ptr(), pm.pitch, bits, stream))
+        else:
+            B.check(lib.pb_pack_codes_u8(chunk.data_ptr(), b - a, n_feat, a, B._ptr(fmap_t), pm.codes.data_ptr(),
+                                         pm.pitch, bits, stream))
+        torch.cuda.current_stream().synchronize()
+    return pm
+
+
+class PackedRows:
+    """Row-major packed codes on the device (input layout of ``pb_predict_rows``)."""
+
+    def __init__(self, n_rows: int, n_features: int, code_bits: int, device: torch.device):
+        self.n_rows = int(n_rows)
+        self.n_features = int(n_features)
+        self.code_bits = int(code_bits)
+        need = (n_features + 1) // 2 if code_bits == 4 else n_features
+        self.pitch_row = (need + 15) // 16 * 16
+        self.codes = torch.empty((max(self.n_rows, 1), self.pitch_row), dtype=torch.uint8, device=device)
+
+
+def pack_row_major(X: np.ndarray | torch.Tensor, edges: np.ndarray | None, max_bins: int) -> PackedRows:
+    """Bin (when ``edges`` is given) and pack rows for prediction.  ``X`` may already be a
+    device tensor (float32 or uint8)."""
+    dev = _device()
+    lib = B.lib()
+    bits = code_bits_for(max_bins)
+    is_f32 = edges is not None
+    n_rows, n_feat = X.shape
+    pr = PackedRows(n_rows, n_feat, bits, dev)
+    edges_t = torch.from_numpy(np.ascontiguousarray(edges, dtype=np.float32)).to(dev) if is_f32 else None
+    stream = torch.cuda.current_stream().cuda_stream
+    want = torch.float32 if is_f32 else torch.uint8
+    for a, b in _row_chunks(n_rows, n_feat * (4 if is_f32 else 1)):
+        if isinstance(X, torch.Tensor):
+            chunk = X[a:b].to(device=dev, dtype=want).contiguous()
+        else:
+            chunk = torch.from_numpy(np.ascontiguousarray(X[a:b], dtype=np.float32 if is_f32 else np.uint8)).to(dev)
+        out = pr.codes[a:b]
+        B.check(lib.pb_pack_rows(chunk.data_ptr(), 1 if is_f32 else 0, b - a, n_feat, B._ptr(edges_t),
+                                 edges_t.shape[0] if is_f32 else 0, max_bins, out.data_ptr(), pr.pitch_row, bits,
+                                 stream))
+        torch.cuda.current_stream().synchronize()
+    return pr
+
+
+# ---- reference-named host helpers ------------------------------------------------------------
+
+
+def quantile_bin(X: np.ndarray, max_bins: int) -> tuple[np.ndarray, np.ndarray]:
+    """Quantile-bin ``X`` column-wise (``packboost/data.py:45-58``): ``(int8 codes [N,F], edges)``."""
+    if max_bins > 128:
+        raise ValueError("PackBoost currently supports up to 128 bins (int8 storage)")
+    Xf = np.ascontiguousarray(X, dtype=np.float32)
+    edges = quantile_edges(Xf, max_bins)
+    pm = pack_feature_major(Xf, edges, max_bins)
+    bins = pm.unpack().t().contiguous().cpu().numpy().astype(np.int8)
+    return bins, edges
+
+
+def preprocess_features(X: np.ndarray, max_bins: int, *, assume_prebinned: bool = False) -> BinningResult:
+    """``packboost/data.py:61-93``; the returned ``bins`` are int8 ``[N, F]``."""
+    X_np = ensure_numpy(X)
+    if assume_prebinned and not detect_prebinned(X_np, max_bins):
+        raise ValueError("prebinned=True requires X to contain integer bins within [0, max_bins).")
+    if assume_prebinned or detect_prebinned(X_np, max_bins):
+        return BinningResult(bins=X_np.astype(np.int8, copy=False), bin_edges=None, prebinned=True)
+    bins, edges = quantile_bin(X_np.astype(np.float32, copy=False), max_bins=max_bins)
+    return BinningResult(bins=bins, bin_edges=edges, prebinned=False)
+
+
+def apply_bins(X: np.ndarray, bin_edges: np.ndarray | None, max_bins: int) -> np.ndarray:
+    """Bin ``X`` with stored edges (``packboost/data.py:96-111``) -> int8 ``[N, F]``."""
+    X_np = ensure_numpy(X)
+    if bin_edges is None:
+        if not detect_prebinned(X_np, max_bins):
+            raise ValueError("Input must already be prebinned when no edges are provided")
+        return X_np.astype(np.int8, copy=False)
+    Xf = np.ascontiguousarray(X_np, dtype=np.float32)
+    pm = pack_feature_major(Xf, bin_edges, max_bins)
+    return pm.unpack().t().contiguous().cpu().numpy().astype(np.int8)
+
+
+def build_era_index(era_ids: Iterable[int] | np.ndarray, num_eras: int | None) -> list[torch.Tensor]:
+    """Per-era ascending row-id tensors (``packboost/data.py:114-134``)."""
+    era_np = np.asarray(era_ids, dtype=np.int16)
+    if era_np.ndim != 1:
+        raise ValueError("era_ids must be 1D")
+    if num_eras is None:
+        num_eras = 1 if era_np.size == 0 else int(era_np.max()) + 1
+    order = np.argsort(era_np, kind="stable")
+    counts = np.bincount(era_np[era_np >= 0].astype(np.int64), minlength=int(num_eras))[: int(num_eras)]
+    offs = np.concatenate([[0], np.cumsum(counts)])
+    valid = order[era_np[order] >= 0]
+    return [torch.from_numpy(valid[offs[e]:offs[e + 1]].astype(np.int64)) for e in range(int(num_eras))]

@@ -1,0 +1,29 @@
+"""Feature sharding across the GPUs of one node (one process per GPU).
+
+Feature ``f`` lives on rank ``f % world`` at local row ``f // world``.  Every
+rank keeps the row state (targets, predictions, gradients, row -> node map)
+replicated and runs the same host control flow with the same seed, so the
+per-depth feature subsets agree without communication.
+"""
+
+from __future__ import annotations
+
+import numpy as np
+
+
+def feature_map(n_features: int, rank: int, world: int) -> np.ndarray:
+    """``int32 [F]``: local feature row of each global feature, -1 when another rank holds it."""
+    f = np.arange(n_features, dtype=np.int64)
+    if world <= 1:
+        return f.astype(np.int32)
+    return np.where(f % world == rank, f // world, -1).astype(np.int32)
+
+
+def local_part(subset: np.ndarray, rank: int, world: int) -> tuple[np.ndarray, np.ndarray]:
+    """For a sampled feature list: ``(local feature rows, positions in the sampled order)`` of the
+    features this rank holds, both int32, positions ascending."""
+    subset = np.asarray(subset)
+    if world <= 1:
+        return subset.astype(np.int32), np.arange(subset.shape[0], dtype=np.int32)
+    pos = np.nonzero(subset % world == rank)[0].astype(np.int32)
+    return (subset[pos] // world).astype(np.int32), pos

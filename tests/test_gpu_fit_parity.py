@@ -1,0 +1,124 @@
+"""End-to-end parity of the CUDA path with the reference (golden fixtures) and the oracle.
+
+Split structure (feature, threshold, children, leaf flags) must match exactly; leaf values and
+predictions within 1e-5 relative (see ``gpu_util.assert_values_close`` for the absolute term).
+"""
+
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import cases
+from gpu_util import assert_values_close, flatten_oracle, flatten_trees
+from oracle import packboost_oracle as po
+
+pytestmark = pytest.mark.gpu
+
+GOLD = os.path.dirname(os.path.abspath(cases.__file__))
+
+
+def _fit_gpu(X, y, era, cfg, rounds):
+    from packboost_b200 import PackBoost, PackBoostConfig
+    booster = PackBoost(PackBoostConfig(device="cuda", **cfg))
+    booster.fit(X, y, era, num_rounds=rounds)
+    return booster
+
+
+@pytest.mark.parametrize("name", list(cases.CASES))
+def test_fit_matches_reference_golden(name):
+    X, y, era, cfg, rounds, Xh = cases.CASES[name]()
+    gold = np.load(os.path.join(GOLD, f"{name}.npz"))
+    booster = _fit_gpu(X, y, era, cfg, rounds)
+    off, cols = flatten_trees(booster.trees)
+    np.testing.assert_array_equal(off, gold["tree_offsets"])
+    for k in ("feature", "threshold", "left", "right", "is_leaf"):
+        np.testing.assert_array_equal(cols[k], gold[k], err_msg=k)
+    # empty children (the -inf fall-through) carry -0/(0+lambda)-type values: excluded by is_leaf & finite
+    assert_values_close(cols["value"], gold["value"], gold["is_leaf"])
+    scale = np.abs(gold["pred_train_head"]).max() + 1e-12
+    np.testing.assert_allclose(booster.predict(X[:2048]), gold["pred_train_head"], rtol=1e-5, atol=1e-5 * scale)
+    np.testing.assert_allclose(booster.predict(Xh), gold["pred_holdout"], rtol=1e-5, atol=1e-5 * scale)
+    # the prediction state kept during training equals predict() on the training rows
+    np.testing.assert_allclose(booster.train_predictions()[:2048], booster.predict(X[:2048]), rtol=1e-5,
+                               atol=1e-5 * scale)
+
+
+@pytest.mark.parametrize("seed", [0, 1, 2])
+def test_fit_matches_oracle_fresh_seeds(seed):
+    rng = np.random.default_rng(seed)
+    n, f, e = 3000, 20, 12
+    X = rng.normal(size=(n, f)).astype(np.float32)
+    X[:, 3] = np.round(X[:, 3])            # heavy ties -> empty bins -> equal-score candidates
+    X[:, 7] = (X[:, 7] > 0).astype(np.float32)
+    y = (X[:, 0] * X[:, 1] + np.sin(X[:, 2]) + 0.3 * rng.standard_normal(n)).astype(np.float32)
+    era = rng.integers(0, e, size=n).astype(np.int16)
+    cfg = dict(pack_size=4, max_depth=5, learning_rate=0.05, lambda_l2=1.0, lambda_dro=0.5, min_samples_leaf=10,
+               max_bins=64, layer_feature_fraction=0.8, random_state=seed)
+    model = po.fit(X, y, era, po.OracleParams(**cfg), 5)
+    booster = _fit_gpu(X, y, era, cfg, 5)
+    off_o, cols_o = flatten_oracle(model.trees)
+    off_g, cols_g = flatten_trees(booster.trees)
+    np.testing.assert_array_equal(off_g, off_o)
+    for k in ("feature", "threshold", "left", "right", "is_leaf"):
+        np.testing.assert_array_equal(cols_g[k], cols_o[k], err_msg=k)
+    assert_values_close(cols_g["value"], cols_o["value"], cols_o["is_leaf"])
+    scale = np.abs(model.train_preds).max()
+    np.testing.assert_allclose(booster.train_predictions(), model.train_preds, rtol=1e-5, atol=1e-5 * scale)
+
+
+def test_fit_is_bitwise_deterministic():
+    X, y, era, cfg, rounds, Xh = cases.CASES["prebinned5"]()
+    a = _fit_gpu(X, y, era, cfg, rounds)
+    b = _fit_gpu(X, y, era, cfg, rounds)
+    _, ca = flatten_trees(a.trees)
+    _, cb = flatten_trees(b.trees)
+    for k in ca:
+        if k == "value":
+            np.testing.assert_array_equal(ca[k].view(np.int64), cb[k].view(np.int64))
+        else:
+            np.testing.assert_array_equal(ca[k], cb[k])
+    np.testing.assert_array_equal(a.train_predictions().view(np.int32), b.train_predictions().view(np.int32))
+
+
+def test_predict_is_bit_exact_given_the_same_trees():
+    """With identical trees the GPU ensemble sum reproduces the CPU route bit for bit."""
+    X, y, era, cfg, rounds, Xh = cases.CASES["config1"]()
+    booster = _fit_gpu(X, y, era, cfg, 3)
+    _, cols = flatten_trees(booster.trees)
+    off, _ = flatten_trees(booster.trees)
+    trees = []
+    for i in range(len(off) - 1):
+        sl = slice(off[i], off[i + 1])
+        trees.append({k: v[sl] for k, v in cols.items()})
+    codes = po.apply_bins(Xh, booster._binner.bin_edges, cfg["max_bins"])
+    want = po.predict_codes(trees, codes, float(booster._tree_weight))
+    got = booster.predict(Xh)
+    np.testing.assert_array_equal(got.view(np.int32), want.view(np.int32))
+
+
+def test_inference_stand_in_bit_exact():
+    from packboost_b200 import PackBoost, PackBoostConfig
+    from packboost_b200.booster import Tree, TreeNode
+    from packboost_b200.workloads import heap_ensemble_to_trees
+    w = cases.inference_case()
+    tds = heap_ensemble_to_trees(w.extra["feature"], w.extra["threshold"], w.extra["leaf"])
+    trees = [Tree(nodes=[TreeNode(int(f), int(t), int(l), int(r), float(v), bool(il))
+                         for f, t, l, r, v, il in zip(d["feature"], d["threshold"], d["left"], d["right"], d["value"], d["is_leaf"])])
+             for d in tds]
+    b = PackBoost(PackBoostConfig(device="cuda", pack_size=w.config["pack_size"], max_bins=5, prebinned=True))
+    b.set_forest(trees, 1.0)
+    gold = np.load(os.path.join(GOLD, "inference_small.npz"))["pred"]
+    np.testing.assert_array_equal(b.predict(w.X).view(np.int32), gold.view(np.int32))
+
+
+def test_errors_are_loud():
+    from packboost_b200 import PackBoost, PackBoostConfig
+    with pytest.raises(RuntimeError):
+        PackBoost(PackBoostConfig(device="cpu"))
+    b = PackBoost(PackBoostConfig(device="cuda", max_bins=200))
+    with pytest.raises(ValueError):
+        b.fit(np.zeros((10, 2), np.float32), np.zeros(10, np.float32), None, num_rounds=1)
+    with pytest.raises(RuntimeError):
+        PackBoost(PackBoostConfig(device="cuda")).predict(np.zeros((4, 2), np.float32))

@@ -1,0 +1,158 @@
+"""Kernel-level parity through the C ABI: binning/packing, histograms, legacy predictors."""
+
+import ctypes as C
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import packboost_oracle as po
+
+pytestmark = pytest.mark.gpu
+
+
+def _dev():
+    return torch.device("cuda", 0)
+
+
+@pytest.mark.parametrize("max_bins", [5, 16, 64, 128])
+def test_bin_pack_matches_searchsorted(max_bins):
+    from packboost_b200.data import pack_feature_major, pack_row_major, quantile_edges
+    rng = np.random.default_rng(max_bins)
+    X = rng.normal(size=(1537, 37)).astype(np.float32)
+    X[::7, 3] = np.nan
+    X[:, 5] = np.round(X[:, 5])
+    edges = quantile_edges(np.nan_to_num(X), max_bins)
+    want = po.bin_codes(X, edges, max_bins).astype(np.uint8)
+    pm = pack_feature_major(X, edges, max_bins)
+    np.testing.assert_array_equal(pm.unpack().cpu().numpy(), want.T)
+    pr = pack_row_major(X, edges, max_bins)
+    raw = pr.codes.cpu().numpy()
+    if pr.code_bits == 4:
+        got = np.stack([raw & 0xF, raw >> 4], axis=2).reshape(raw.shape[0], -1)[:, : X.shape[1]]
+    else:
+        got = raw[:, : X.shape[1]]
+    np.testing.assert_array_equal(got, want)
+
+
+def _hist_case(n, f, e, nb, n_nodes, seed, big_era=False):
+    from packboost_b200 import backends as B
+    from packboost_b200.data import pack_feature_major
+    rng = np.random.default_rng(seed)
+    codes = rng.integers(0, nb, size=(n, f), dtype=np.uint8)
+    if big_era:
+        cuts = np.sort(rng.choice(np.arange(1, n), size=e - 1, replace=False))
+        cuts[0] = max(cuts[0], 40000) if n > 50000 else cuts[0]
+        cuts = np.sort(cuts)
+    else:
+        cuts = np.sort(rng.choice(np.arange(1, n), size=e - 1, replace=False))
+    era_off = np.concatenate([[0], cuts, [n]]).astype(np.int32)
+    pm = pack_feature_major(codes, None, nb)
+    npad = pm.rows_padded
+    gq = np.zeros(npad, np.int32)
+    gq[:n] = rng.integers(-(1 << 30), 1 << 30, size=n)
+    slot = np.full(npad, 0xFFFF, np.uint16)
+    slot[:n] = rng.integers(0, n_nodes + 1, size=n)
+    slot[:n][slot[:n] == n_nodes] = 0xFFFF      # some rows sit in finished leaves
+    dev = _dev()
+    t = dict(gq=torch.from_numpy(gq).to(dev), slot=torch.from_numpy(slot.view(np.int16)).to(dev),
+             era=torch.from_numpy(era_off).to(dev))
+    st = B.TrainState()
+    st.n_rows, st.n_features_total, st.n_features_local, st.n_eras = n, f, f, e
+    st.max_bins, st.code_bits, st.pitch = nb, pm.code_bits, pm.pitch
+    st.max_depth, st.pack_size, st.min_samples_leaf, st.n_thresholds, st.feature_block_size = 6, 1, 1, nb - 1, 32
+    st.lambda_l2 = 1.0
+    dummy = torch.zeros(max(npad, 4096), dtype=torch.float32, device=dev)
+    ids = torch.arange(max(f, nb), dtype=torch.int32, device=dev)
+    st.codes, st.era_offsets, st.thr_ids, st.feat_local = pm.codes.data_ptr(), t["era"].data_ptr(), ids.data_ptr(), ids.data_ptr()
+    st.y = st.preds = dummy.data_ptr()
+    st.gq, st.slot, st.leaf = t["gq"].data_ptr(), t["slot"].data_ptr(), t["slot"].data_ptr()
+    ctl = torch.zeros(int(B.lib().pb_ctl_bytes()), dtype=torch.uint8, device=dev)
+    ws = torch.zeros(int(B.lib().pb_workspace_min_bytes(C.byref(st))) + 1024, dtype=torch.uint8, device=dev)
+    st.ctl, st.workspace, st.workspace_bytes = ctl.data_ptr(), ws.data_ptr(), ws.numel()
+    B.check(B.lib().pb_train_prepare(C.byref(st), era_off.ctypes.data))
+    feat = rng.permutation(f)[: max(1, f // 2)].astype(np.int32)
+    feat_t = torch.from_numpy(feat).to(dev)
+    cnt = torch.full((feat.shape[0], n_nodes, e, nb), -1, dtype=torch.int32, device=dev)
+    gs = torch.full((feat.shape[0], n_nodes, e, nb), -1, dtype=torch.int64, device=dev)
+    B.check(B.lib().pb_hist_build(C.byref(st), feat_t.data_ptr(), feat.shape[0], n_nodes, n_nodes, cnt.data_ptr(),
+                                  gs.data_ptr(), torch.cuda.current_stream().cuda_stream))
+    torch.cuda.synchronize()
+    # numpy reference (exact integers)
+    era_of = np.repeat(np.arange(e), np.diff(era_off))
+    live = slot[:n] != 0xFFFF
+    want_c = np.zeros((feat.shape[0], n_nodes, e, nb), np.int64)
+    want_g = np.zeros_like(want_c)
+    for i, fid in enumerate(feat):
+        key = (slot[:n][live].astype(np.int64) * e + era_of[live]) * nb + codes[live, fid]
+        want_c[i] = np.bincount(key, minlength=n_nodes * e * nb).reshape(n_nodes, e, nb)
+        pos = np.bincount(key, weights=np.maximum(gq[:n][live], 0).astype(np.float64), minlength=n_nodes * e * nb)
+        # float64 bincount is not exact at this magnitude; accumulate exactly instead
+        acc = np.zeros(n_nodes * e * nb, np.int64)
+        np.add.at(acc, key, gq[:n][live].astype(np.int64))
+        want_g[i] = acc.reshape(n_nodes, e, nb)
+    np.testing.assert_array_equal(cnt.cpu().numpy().astype(np.int64), want_c)
+    np.testing.assert_array_equal(gs.cpu().numpy(), want_g)
+
+
+@pytest.mark.parametrize("n,f,e,nb,nodes", [
+    (5000, 12, 7, 5, 1), (5000, 12, 7, 5, 32), (4097, 9, 3, 16, 4), (6000, 10, 5, 128, 8),
+    (3001, 6, 4, 200, 3), (20000, 5, 2, 64, 300), (1000, 3, 1, 2, 1),
+])
+def test_histogram_exact(n, f, e, nb, nodes):
+    _hist_case(n, f, e, nb, nodes, seed=n + nb)
+
+
+def test_histogram_exact_when_an_era_spans_several_tiles():
+    _hist_case(120_000, 6, 3, 5, 4, seed=5, big_era=True)
+    _hist_case(90_000, 4, 1, 32, 2, seed=6)
+
+
+def test_legacy_predictors_match_oracle_router():
+    from packboost_b200 import backends as B
+    rng = np.random.default_rng(3)
+    n, f = 3000, 40
+    codes = rng.integers(0, 16, size=(n, f), dtype=np.uint8)
+    # three random (not complete) trees with BFS-compact numbering
+    trees = []
+    for t in range(3):
+        tr = po.OracleTree()
+        frontier = [0]
+        for depth in range(4):
+            nxt = []
+            for nid in frontier:
+                if rng.random() < 0.8:
+                    l, r = tr.split(nid, int(rng.integers(0, f)), int(rng.integers(0, 15)))
+                    tr.set_leaf(l, float(rng.normal()))
+                    tr.set_leaf(r, float(rng.normal()))
+                    nxt += [l, r]
+            frontier = nxt
+        trees.append(tr.arrays())
+    dev = _dev()
+    fm = torch.from_numpy(np.ascontiguousarray(codes.T)).to(dev)
+    for tr in trees:
+        got = B.predict_bins_cuda(fm, *(torch.from_numpy(tr[k].astype(np.int32)).to(dev) for k in ("feature", "threshold", "left", "right")),
+                                  torch.from_numpy(tr["value"].astype(np.float32)).to(dev),
+                                  torch.from_numpy(tr["is_leaf"].astype(np.uint8)).to(dev))
+        np.testing.assert_array_equal(got.cpu().numpy().view(np.int32), po.route_tree(tr, codes.astype(np.int8)).view(np.int32))
+    # pack: absolute child ids, out = w * sum of leaves
+    off = np.cumsum([0] + [t["feature"].shape[0] for t in trees]).astype(np.int32)
+    cat = {k: np.concatenate([t[k] for t in trees]) for k in trees[0]}
+    la = np.concatenate([np.where(t["left"] >= 0, t["left"] + o, -1) for t, o in zip(trees, off[:-1])]).astype(np.int32)
+    ra = np.concatenate([np.where(t["right"] >= 0, t["right"] + o, -1) for t, o in zip(trees, off[:-1])]).astype(np.int32)
+    got = B.predict_pack_cuda(fm, torch.from_numpy(cat["feature"]).to(dev), torch.from_numpy(cat["threshold"]).to(dev),
+                              torch.from_numpy(la).to(dev), torch.from_numpy(ra).to(dev),
+                              torch.from_numpy(cat["value"].astype(np.float32)).to(dev),
+                              torch.from_numpy(cat["is_leaf"].astype(np.uint8)).to(dev), torch.from_numpy(off).to(dev), 0.25)
+    want = np.zeros(n, np.float32)
+    for tr in trees:
+        want = want + po.route_tree(tr, codes.astype(np.int8))
+    np.testing.assert_allclose(got.cpu().numpy(), np.float32(0.25) * want, rtol=1e-6, atol=1e-7)
+
+
+def test_superseded_frontier_calls_say_so():
+    from packboost_b200 import backends as B
+    assert B.cuda_available() and not B.cpu_available()
+    for fn in (B.find_best_splits_batched_cuda, B.partition_frontier_cuda, B.find_best_splits_batched):
+        with pytest.raises(RuntimeError):
+            fn()
