@@ -59,6 +59,17 @@ int pb_abi_version(void);
  * probed by packboost/backends/__init__.py:101-119). */
 int pb_device_count(void);
 
+/* Instrumentation (the reference times its phases with perf_counter buckets,
+ * packboost/booster.py:220-270, and a cudaEvent pair around its kernel,
+ * packboost/backends/cuda/frontier_cuda.cu:670-710).  While enabled, every launch of a kernel
+ * family is bracketed by two events on its stream.  After synchronising, pb_profile_collect
+ * returns per family (0 histogram, 1 scorer, 2 select, 3 partition, 4 round begin/end) the
+ * summed milliseconds and the number of bracketed launches, and clears the record.
+ * pb_launch_count is the number of kernels this library launched since it was loaded. */
+int pb_profile_enable(int on);
+int pb_profile_collect(double* ms_by_kind /* [5] */, int64_t* launches_by_kind /* [5] */);
+int64_t pb_launch_count(void);
+
 /* ---- binning and packing (packboost/data.py:45-58, 96-111) ---------------------------- */
 
 /* Bin a row-major float32 chunk `x[n_chunk][n_features]` with per-feature edges

@@ -65,6 +65,9 @@ _PROTOS: dict[str, tuple[Any, list[Any]]] = {
     "pb_last_error": (C.c_char_p, []),
     "pb_abi_version": (C.c_int, []),
     "pb_device_count": (C.c_int, []),
+    "pb_profile_enable": (C.c_int, [C.c_int]),
+    "pb_profile_collect": (C.c_int, [vp, vp]),
+    "pb_launch_count": (i64, []),
     "pb_bin_pack_f32": (C.c_int, [vp, i64, i64, i64, vp, i64, i64, vp, vp, i64, i64, vp]),
     "pb_pack_codes_u8": (C.c_int, [vp, i64, i64, i64, vp, vp, i64, i64, vp]),
     "pb_pack_rows": (C.c_int, [vp, i64, i64, i64, vp, i64, i64, vp, i64, i64, vp]),

@@ -28,6 +28,13 @@ int fail_cuda(cudaError_t e, const char* what);
         if (_e != cudaSuccess) return pb::fail_cuda(_e, what); \
     } while (0)
 
+// ---- optional in-stream timing of the kernel families and a launch counter -----------------
+
+enum ProfKind { kProfHist = 0, kProfScore = 1, kProfSelect = 2, kProfPartition = 3, kProfRound = 4, kProfKinds = 5 };
+void prof_begin(int kind, cudaStream_t stream);
+void prof_end(int kind, cudaStream_t stream);
+void count_launch(int n);
+
 #define PB_REQUIRE(cond, ...)                               \
     do {                                                    \
         if (!(cond)) return pb::fail_arg(__VA_ARGS__);      \

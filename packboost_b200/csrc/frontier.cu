@@ -404,12 +404,15 @@ extern "C" int pb_round_begin(const pb_train_state* st, int64_t apply_previous, 
     cudaStream_t stream = (cudaStream_t)stream_;
     Ctl c = ctl_view(st->ctl);
     const int g = row_grid(st->n_rows);
+    prof_begin(kProfRound, stream);
     round_reset_kernel<<<1, 32, 0, stream>>>(c);
     preds_absmax_kernel<<<g, kRowThreads, 0, stream>>>(st->preds, st->y, st->leaf, c.delta, st->n_rows,
                                                         apply_previous ? 1 : 0, c.head);
     quantise_kernel<<<g, kRowThreads, 0, stream>>>(st->preds, st->y, st->gq, st->slot, st->leaf, st->n_rows,
                                                     rows_padded(st->n_rows), c.head);
     root_kernel<<<1, 32, 0, stream>>>(c, st->n_rows, (int)st->min_samples_leaf, st->lambda_l2);
+    prof_end(kProfRound, stream);
+    count_launch(4);
     PB_LAUNCH_CHECK("round_begin");
     return PB_OK;
 }
@@ -526,7 +529,10 @@ extern "C" int pb_depth_select(const pb_train_state* st, int64_t depth, const in
     a.thr_ids = st->thr_ids;
     a.min_leaf = (int)st->min_samples_leaf;
     a.lambda = st->lambda_l2;
+    prof_begin(kProfSelect, (cudaStream_t)stream_);
     select_kernel<<<1, 1024, 0, (cudaStream_t)stream_>>>(a);
+    prof_end(kProfSelect, (cudaStream_t)stream_);
+    count_launch(1);
     PB_LAUNCH_CHECK("select_kernel");
     return PB_OK;
 }
@@ -551,10 +557,13 @@ static int launch_partition(const pb_train_state* st, int64_t depth, uint32_t* b
     const size_t smem = sizeof(PartEntry) * (size_t)(1 << depth);
     const int g = row_grid(st->n_rows);
     cudaStream_t stream = (cudaStream_t)stream_;
+    prof_begin(kProfPartition, stream);
     if (st->code_bits == 4)
         partition_kernel<4, MODE><<<g, kRowThreads, smem, stream>>>(a);
     else
         partition_kernel<8, MODE><<<g, kRowThreads, smem, stream>>>(a);
+    prof_end(kProfPartition, stream);
+    count_launch(1);
     PB_LAUNCH_CHECK("partition_kernel");
     return PB_OK;
 }
@@ -577,6 +586,7 @@ extern "C" int pb_round_end(const pb_train_state* st, void* stream) {
     int rc = check_state(st);
     if (rc) return rc;
     delta_kernel<<<8, 256, 0, (cudaStream_t)stream>>>(ctl_view(st->ctl), (int)st->pack_size, (float)st->learning_rate);
+    count_launch(1);
     PB_LAUNCH_CHECK("delta_kernel");
     return PB_OK;
 }
@@ -587,6 +597,7 @@ extern "C" int pb_apply_leaf_delta(const pb_train_state* st, void* stream) {
     Ctl c = ctl_view(st->ctl);
     apply_delta_kernel<<<row_grid(st->n_rows), kRowThreads, 0, (cudaStream_t)stream>>>(st->preds, st->leaf, c.delta,
                                                                                       st->n_rows);
+    count_launch(1);
     PB_LAUNCH_CHECK("apply_delta_kernel");
     return PB_OK;
 }

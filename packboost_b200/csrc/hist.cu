@@ -210,6 +210,7 @@ int launch_hist(const HistLaunch& h, cudaStream_t stream) {
     }
     dim3 grid((unsigned)(h.n_eras * a.tiles_per_era), (unsigned)((h.n_feat + group - 1) / group), (unsigned)chunks);
     if (grid.y > 65535u || grid.z > 65535u) return fail_arg("histogram grid too large");
+    prof_begin(kProfHist, stream);
     if (h.code_bits == 4) {
         if (smem > 48 * 1024)
             PB_CUDA_TRY(cudaFuncSetAttribute(hist_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
@@ -219,6 +220,8 @@ int launch_hist(const HistLaunch& h, cudaStream_t stream) {
             PB_CUDA_TRY(cudaFuncSetAttribute(hist_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         hist_kernel<8><<<grid, kHistThreads, smem, stream>>>(a);
     }
+    prof_end(kProfHist, stream);
+    count_launch(1);
     PB_LAUNCH_CHECK("hist_kernel");
     return PB_OK;
 }

@@ -140,6 +140,7 @@ int pack_fm(const PackArgs& a, int code_bits, cudaStream_t stream) {
         pack_fm_kernel<4><<<grid, block, smem, stream>>>(a);
     else
         pack_fm_kernel<8><<<grid, block, smem, stream>>>(a);
+    count_launch(1);
     PB_LAUNCH_CHECK("pack_fm_kernel");
     return PB_OK;
 }
@@ -198,6 +199,7 @@ extern "C" int pb_pack_rows(const void* x, int64_t x_is_f32, int64_t n_rows, int
         pack_rows_kernel<4><<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(a);
     else
         pack_rows_kernel<8><<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(a);
+    count_launch(1);
     PB_LAUNCH_CHECK("pack_rows_kernel");
     return PB_OK;
 }

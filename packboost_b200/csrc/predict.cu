@@ -145,6 +145,7 @@ extern "C" int pb_predict_rows(const uint8_t* codes, int64_t n_rows, int64_t pit
             PB_CUDA_TRY(cudaFuncSetAttribute(predict_rows_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         predict_rows_kernel<8><<<grid, 128, smem, stream>>>(a);
     }
+    count_launch(1);
     PB_LAUNCH_CHECK("predict_rows_kernel");
     return PB_OK;
 }
@@ -164,6 +165,7 @@ extern "C" int pb_predict_bins_fm(const uint8_t* bins, int64_t n_features, int64
     if (n_rows <= 0) return PB_OK;
     predict_bins_fm_kernel<<<row_blocks(n_rows), 256, 0, (cudaStream_t)stream>>>(bins, n_rows, feature, threshold, left,
                                                                                 right, value, is_leaf, out);
+    count_launch(1);
     PB_LAUNCH_CHECK("predict_bins_fm_kernel");
     return PB_OK;
 }
@@ -178,6 +180,7 @@ extern "C" int pb_predict_pack_fm(const uint8_t* bins, int64_t n_features, int64
     if (n_rows <= 0) return PB_OK;
     predict_pack_fm_kernel<<<row_blocks(n_rows), 256, 0, (cudaStream_t)stream>>>(
         bins, n_rows, feature, threshold, left_abs, right_abs, value, is_leaf, offsets, (int)n_trees, tree_weight, out);
+    count_launch(1);
     PB_LAUNCH_CHECK("predict_pack_fm_kernel");
     return PB_OK;
 }

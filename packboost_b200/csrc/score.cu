@@ -246,7 +246,10 @@ int launch_score(const ScoreLaunch& s, cudaStream_t stream) {
     if (smem > 48 * 1024)
         PB_CUDA_TRY(cudaFuncSetAttribute(score_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     dim3 grid((unsigned)s.n_feat, (unsigned)((s.n_nodes_max + npc - 1) / npc));
+    prof_begin(kProfScore, stream);
     score_kernel<<<grid, kScoreThreads, smem, stream>>>(a);
+    prof_end(kProfScore, stream);
+    count_launch(1);
     PB_LAUNCH_CHECK("score_kernel");
     return PB_OK;
 }

@@ -49,3 +49,42 @@ def assert_values_close(got, want, is_leaf, scale=None):
     finite = np.isfinite(want) & (np.abs(want) < 1e30)
     s = np.abs(want[finite]).max() if scale is None and finite.any() else (scale or 1.0)
     np.testing.assert_allclose(got[finite], want[finite], rtol=1e-5, atol=1e-5 * s)
+
+
+def leaf_index(tree, codes):
+    """Index of the leaf node each row lands in (same routing rule as the oracle)."""
+    n = codes.shape[0]
+    node = np.zeros(n, dtype=np.int64)
+    live = np.arange(n)
+    while live.size:
+        cur = node[live]
+        keep = ~tree["is_leaf"][cur]
+        live, cur = live[keep], cur[keep]
+        if live.size == 0:
+            break
+        go_left = codes[live, tree["feature"][cur]] <= tree["threshold"][cur]
+        node[live] = np.where(go_left, tree["left"][cur], tree["right"][cur])
+    return node
+
+
+def populated_leaves(off, cols, codes_train):
+    """Boolean mask over all nodes: leaf reached by at least one training row.  A child that
+    received no rows (possible after the reference's -inf fall-through split) has the value
+    -eps/(0+lambda) with eps the float32 summation noise of the CPU path; such values are not
+    comparable and are excluded from value checks."""
+    mask = np.zeros(cols["feature"].shape[0], dtype=bool)
+    for i in range(len(off) - 1):
+        sl = slice(off[i], off[i + 1])
+        tree = {k: v[sl] for k, v in cols.items()}
+        hit = np.unique(leaf_index(tree, codes_train))
+        mask[off[i] + hit] = True
+    return mask
+
+
+def rows_avoiding_empty_leaves(off, cols, populated, codes):
+    ok = np.ones(codes.shape[0], dtype=bool)
+    for i in range(len(off) - 1):
+        sl = slice(off[i], off[i + 1])
+        tree = {k: v[sl] for k, v in cols.items()}
+        ok &= populated[off[i] + leaf_index(tree, codes)]
+    return ok
