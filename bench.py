@@ -1,0 +1,314 @@
+#!/usr/bin/env python
+"""Benchmark: boosting rounds/s and histogram-kernel HBM GB/s on the era-heavy wide workload.
+
+    python bench.py --gpus N --steps K --warmup W [--impl reference] [--scale S]
+
+One "step" is one boosting round (pack of 32 identical trees, depth 6, 10 % of the 2 376
+features sampled per depth, 574 eras) over a seeded synthetic stand-in for the 2.7 M-row
+five-level table.  With N > 1 (launched by torchrun, one rank per GPU) the features are
+sharded over the ranks and the same data set is trained, i.e. strong scaling.
+
+Own arm: `value` is rounds/s with the packed matrix resident in HBM, timed with CUDA events
+around exactly K rounds (barrier + synchronize on both sides, max over ranks); `e2e` is
+rounds/s of the public `PackBoost.fit` call on HOST buffers for K rounds, including binning,
+packing and the host->device copy of the matrix and the device->host read of each round's
+decision log.  `roofline` is the histogram kernel: algorithmic bytes of its launches divided
+by their event-timed duration inside the timed region.  `cpu_baseline` (N=1 only) and
+`--impl reference` time the CPU port of the reference's torch frontier (oracle/) on a bounded
+era-subsample of the same workload on this box's host cores.
+"""
+
+from __future__ import annotations
+
+import argparse
+import ctypes as C
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+N_ROWS, N_FEAT, N_ERAS = 2_700_000, 2376, 574
+CFG = dict(pack_size=32, max_depth=6, learning_rate=0.4 / 32, lambda_l2=1e-6, lambda_dro=0.5,
+           min_samples_leaf=20, max_bins=5, layer_feature_fraction=0.1, prebinned=True, random_state=42)
+METRIC = "boosting_rounds_per_sec"
+UNIT = "rounds/s"
+
+
+def workload_name(n_rows, n_feat, n_eras):
+    return (f"config3 era-heavy wide: {n_rows} rows x {n_feat} uint8 features in {{0..4}} (4-bit packed), "
+            f"{n_eras} eras, pack_size=32, max_depth=6, feature fraction 0.1, lambda_dro=0.5, lr=0.4/32")
+
+
+# ---------------------------------------------------------------------------------------------
+# synthetic data (seeded, generated on the device; same shape and value distribution as
+# packboost_b200.workloads.config3)
+# ---------------------------------------------------------------------------------------------
+
+def make_device_data(n_rows, n_feat, n_eras, device, seed=3):
+    import torch
+    g = torch.Generator(device=device)
+    g.manual_seed(seed)
+    X = torch.empty((n_rows, n_feat), dtype=torch.uint8, device=device)
+    step = 1 << 18
+    for a in range(0, n_rows, step):
+        b = min(n_rows, a + step)
+        X[a:b] = torch.randint(0, 5, (b - a, n_feat), generator=g, device=device, dtype=torch.uint8)
+    era = (torch.arange(n_rows, device=device, dtype=torch.int64) * n_eras // n_rows)
+    sel = torch.randperm(n_feat, generator=g, device=device)[:50]
+    w = 0.02 + 0.02 * torch.randn((n_eras, 50), generator=g, device=device)
+    latent = ((X[:, sel].float() - 2.0) * w[era]).sum(1)
+    latent = latent + torch.randn(n_rows, generator=g, device=device) * (latent.std() / 0.02)
+    ranks = torch.argsort(torch.argsort(latent))
+    y = (torch.floor(ranks.float() * 5.0 / n_rows).clamp_(0, 4) * 0.25).float()
+    return X, y, era.to(torch.int16)
+
+
+# ---------------------------------------------------------------------------------------------
+# clocks
+# ---------------------------------------------------------------------------------------------
+
+class ClockSampler:
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.samples = []
+        self._stop = threading.Event()
+        self._t = threading.Thread(target=self._run, daemon=True)
+
+    def _run(self):
+        while not self._stop.is_set():
+            try:
+                out = subprocess.run(["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.FIELDS}",
+                                      "--format=csv,noheader,nounits"], capture_output=True, text=True, timeout=5).stdout
+                parts = [p.strip() for p in out.strip().split(",")]
+                if len(parts) >= 6:
+                    self.samples.append(parts)
+            except Exception:
+                pass
+            self._stop.wait(0.2)
+
+    def start(self):
+        self._t.start()
+
+    def stop(self):
+        self._stop.set()
+        self._t.join(timeout=6)
+        sm = [int(float(s[0])) for s in self.samples if s[0].replace(".", "").isdigit()]
+        mx = [int(float(s[1])) for s in self.samples if s[1].replace(".", "").isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(s[2 + i].lower().startswith("active") for s in self.samples)]
+        return {"sm_mhz": int(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": reasons, "samples": len(self.samples)}
+
+
+# ---------------------------------------------------------------------------------------------
+# CPU port of the reference on a bounded era-subsample
+# ---------------------------------------------------------------------------------------------
+
+def cpu_port_rounds_per_sec(n_rows, n_feat, n_eras, sample_eras, rounds, warmup):
+    """Time the oracle's fit on the first `sample_eras` eras of a host-generated table of the same
+    shape; histogram and scoring cost are linear in the number of whole eras, so rounds/s of
+    the full workload is the sample's rounds/s times sample_eras / n_eras."""
+    import torch
+    from oracle import packboost_oracle as po
+    from packboost_b200 import workloads
+    torch.set_num_threads(os.cpu_count() or 1)
+    rows_per_era = n_rows // n_eras
+    w = workloads.config3(seed=3, n_rows=rows_per_era * sample_eras, n_features=n_feat, n_eras=sample_eras)
+    p = po.OracleParams(**CFG)
+    model = po.fit(w.X, w.y, w.era, p, warmup + rounds)
+    secs = float(np.sum(model.round_seconds[warmup:]))
+    sample_rps = rounds / secs
+    return sample_rps * sample_eras / n_eras, secs, w.X.shape[0]
+
+
+def pick_sample_eras(steps, warmup, n_eras, budget_s=90.0, per_era_round_s=0.2):
+    e = int(budget_s / max(1, steps + warmup) / per_era_round_s)
+    return max(2, min(e, 24, n_eras))
+
+
+# ---------------------------------------------------------------------------------------------
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="packboost_b200", choices=["packboost_b200", "reference"])
+    ap.add_argument("--scale", type=float, default=1.0, help="row/era scale of the workload (profiling captures use < 1)")
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-cpu", action="store_true")
+    args = ap.parse_args()
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    n_eras = max(2, int(round(N_ERAS * args.scale)))
+    n_rows = int(N_ROWS * args.scale) // n_eras * n_eras
+    n_feat = N_FEAT
+    config = {"workload": workload_name(n_rows, n_feat, n_eras), "parallelism": f"feature-sharded x{world}",
+              "l2": "inputs larger than L2 (packed matrix 3.2 GB at full size); no flush needed",
+              "scale": args.scale}
+
+    if args.impl == "reference":
+        if rank != 0:
+            return
+        cores = os.cpu_count() or 1
+        se = pick_sample_eras(args.steps, args.warmup, n_eras)
+        rps, secs, srows = cpu_port_rounds_per_sec(n_rows, n_feat, n_eras, se, args.steps, args.warmup)
+        sample = (f"CPU port of the reference torch frontier (oracle/): {args.steps} timed rounds on the first {se} of "
+                  f"{n_eras} eras ({srows} rows x {n_feat} features), rounds/s scaled by {se}/{n_eras}")
+        line = {"impl": "reference", "metric": METRIC, "value": rps, "unit": UNIT, "n_gpus": args.gpus,
+                "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1000.0 / rps, "higher_is_better": True,
+                "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": config,
+                "cpu_baseline": {"value": rps, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
+                "e2e": {"value": rps, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+        print(json.dumps(line))
+        return
+
+    import torch
+    import torch.distributed as dist
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    from packboost_b200 import PackBoost, PackBoostConfig
+    from packboost_b200 import backends as B
+    lib = B.lib()
+
+    X, y, era = make_device_data(n_rows, n_feat, n_eras, dev)
+    y_host = y.cpu().numpy()
+    era_host = era.cpu().numpy()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- device-resident leg ------------------------------------------------------------------
+    booster = PackBoost(PackBoostConfig(device="cuda", **CFG))
+    booster._start(X, y_host, era_host)
+    trainer = booster._trainer
+    total = args.warmup + args.steps
+    for r in range(args.warmup):
+        booster._boost_one_round(r, total)
+    barrier()
+    launches0 = int(lib.pb_launch_count())
+    lib.pb_profile_enable(1)
+    ms5 = (C.c_double * 5)()
+    n5 = (C.c_int64 * 5)()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    k_local_sum = 0
+    hist_bytes = 0.0
+    code_bytes = 0.5
+    F_s = trainer.n_sampled()
+    barrier()
+    ev0.record()
+    for r in range(args.warmup, total):
+        booster._boost_one_round(r, total)
+        n_ctx = booster._last_n_ctx
+        # algorithmic bytes of this round's histogram launches (this rank's features only)
+        f_loc = F_s / world
+        for d in range(CFG["max_depth"]):
+            if n_ctx[d] == 0:
+                break
+            hist_bytes += (n_rows * f_loc * code_bytes + n_rows * (4 + 2) + (n_eras + 1) * 4
+                           + n_ctx[d] * f_loc * n_eras * CFG["max_bins"] * 12)
+    ev1.record()
+    barrier()
+    ms = ev0.elapsed_time(ev1)
+    clocks = sampler.stop() if rank == 0 else None
+    lib.pb_profile_enable(0)
+    B.check(lib.pb_profile_collect(ms5, n5))
+    launches = int(lib.pb_launch_count()) - launches0
+    t = torch.tensor([ms], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.item())
+    value = args.steps / (ms / 1000.0)
+    hist_ms, hist_launches = float(ms5[0]), int(n5[0])
+    achieved = hist_bytes / (hist_ms / 1000.0) / 1e9 if hist_ms > 0 else 0.0
+    peaks_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(peaks_path):
+        peak = float(json.load(open(peaks_path))["hbm_gbs"])
+        peak_src = "measured (MEASURED_PEAKS.json hbm_gbs)"
+    else:
+        peak, peak_src = 6650.0, "fallback"
+    phases = {"hist_ms_per_step": hist_ms / args.steps, "score_ms_per_step": float(ms5[1]) / args.steps,
+              "select_ms_per_step": float(ms5[2]) / args.steps, "partition_ms_per_step": float(ms5[3]) / args.steps,
+              "round_begin_ms_per_step": float(ms5[4]) / args.steps}
+    train_corr = None
+    del booster, trainer
+    torch.cuda.empty_cache()
+
+    # ---- end-to-end leg: public fit() on host buffers --------------------------------------------
+    e2e = None
+    if not args.no_e2e:
+        X_host = torch.empty((n_rows, n_feat), dtype=torch.uint8).pin_memory()
+        X_host.copy_(X)
+        del X
+        torch.cuda.empty_cache()
+        Xh = X_host.numpy()
+        barrier()
+        t0 = time.perf_counter()
+        b2 = PackBoost(PackBoostConfig(device="cuda", **CFG))
+        b2.fit(Xh, y_host, era_host, num_rounds=args.steps)
+        p = b2.train_predictions()          # device -> host read of the result
+        barrier()
+        wall = time.perf_counter() - t0
+        tt = torch.tensor([wall], dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        wall = float(tt.item())
+        lists_bytes = CFG["max_depth"] * 3 * F_s * 4
+        h2d = (n_rows * n_feat + n_rows * 4 + (n_eras + 1) * 4) / args.steps + lists_bytes
+        d2h = b2._trainer.log_bytes + n_rows * 4 / args.steps
+        e2e = {"value": args.steps / wall, "unit": UNIT, "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h),
+               "note": "whole PackBoost.fit on host arrays: packing + one-time matrix upload amortised over the "
+                       "timed rounds, per-round feature lists up and decision log down, final predictions down",
+               "seconds": wall}
+        from packboost_b200.booster import _era_correlation_np
+        train_corr = _era_correlation_np(era_host, y_host, p)
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    cpu_baseline = None
+    if world == 1 and not args.no_cpu:
+        se = 8
+        rps, secs, srows = cpu_port_rounds_per_sec(n_rows, n_feat, n_eras, min(se, n_eras), 3, 1)
+        cpu_baseline = {"value": rps, "unit": UNIT, "cores": os.cpu_count() or 1, "kind": "port",
+                        "sample": f"3 timed rounds (1 warm-up) of the oracle on the first {min(se, n_eras)} of {n_eras} eras "
+                                  f"({srows} rows x {n_feat} features), {secs:.1f} s; rounds/s scaled by eras"}
+
+    line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "int64", "data": "synthetic", "config": config,
+            "roofline": {"bound": "hbm", "kernel": "hist_kernel<4>", "achieved": achieved, "peak": peak, "unit": "GB/s",
+                         "frac": achieved / peak, "traffic": None, "peak_source": peak_src,
+                         "launches": hist_launches, "avg_launch_ms": hist_ms / max(hist_launches, 1),
+                         "algorithmic_bytes_per_launch": hist_bytes / max(hist_launches, 1)},
+            "cpu_baseline": cpu_baseline, "e2e": e2e, "gpu_launches": launches, "clocks": clocks, "phases": phases,
+            "train_corr_after_e2e": train_corr}
+    print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -21,7 +21,9 @@
  *              <= 16): two rows per byte, even row in the low nibble.  `pitch` is a
  *              multiple of 128 and covers `rows_padded = roundup(n_rows, 256)` rows.
  *  gq          int32 fixed-point gradient per row, `gq = rint(g * scale)` with `scale` a
- *              power of two chosen per round so that `max|gq| <= 2^30`.
+ *              power of two chosen per round so that `max|gq| <= 2^gq_bits`; gq_bits is 30
+ *              when no era tile exceeds 2047 rows, 27 up to 4095 rows and 24 up to 8160 rows
+ *              (the histogram kernel accumulates a tile in 32-bit shared-memory words).
  *  slot        uint16 frontier slot of the row at the current depth (index into the list of
  *              active nodes) or 0xFFFF when the row sits in a finished leaf.
  *  leaf        uint16 id of the tree node the row currently sits in (BFS-compact ids: a
@@ -136,7 +138,10 @@ typedef struct pb_train_state {
     /* tiling of the rows computed by pb_train_prepare (host side, read-only afterwards) */
     int64_t max_era_rows;
     int64_t hist_rows_per_tile;
-    int64_t reserved[6];
+    int64_t gq_bits;             /* |gq| <= 2^gq_bits */
+    int64_t count_bits;          /* CB: rows of a histogram tile < 2^CB */
+    int64_t lo_bits;             /* LB = 32 - 2*CB: low gradient bits kept beside the count */
+    int64_t reserved[3];
 } pb_train_state;
 
 /* sizeof(pb_train_state), so that a binding can verify its mirror of the struct. */

@@ -57,7 +57,8 @@ class TrainState(C.Structure):
         ("codes", vp), ("era_offsets", vp), ("thr_ids", vp), ("feat_local", vp), ("y", vp),
         ("preds", vp), ("gq", vp), ("slot", vp), ("leaf", vp), ("ctl", vp), ("workspace", vp),
         ("workspace_bytes", i64),
-        ("max_era_rows", i64), ("hist_rows_per_tile", i64), ("reserved", i64 * 6),
+        ("max_era_rows", i64), ("hist_rows_per_tile", i64), ("gq_bits", i64), ("count_bits", i64),
+        ("lo_bits", i64), ("reserved", i64 * 3),
     ]
 
 

@@ -392,6 +392,9 @@ class PackBoost:
         self._train_preds: np.ndarray | None = None
         self._trainer: _DeviceTrainer | None = None
         self._row_order: np.ndarray | None = None
+        self._fit_ctx: dict | None = None
+        self._eval_states: list = []
+        self._last_n_ctx: list[int] = []
 
     # Public -------------------------------------------------------------
 
@@ -415,9 +418,21 @@ class PackBoost:
         round_callback: Callable[[int, dict[str, float]], None] | None = None,
     ) -> "PackBoost":
         """Squared-loss boosting with pack-synchronous growth and DES (``packboost/booster.py:375-656``)."""
+        self._start(X, y, era, feature_names=feature_names, eval_sets=eval_sets)
+        for round_idx in range(num_rounds):
+            metrics = self._boost_one_round(round_idx, num_rounds, round_callback is not None)
+            if round_callback is not None:
+                round_callback(round_idx + 1, metrics)
+        self._finish()
+        return self
+
+    # -- fit, step by step (the benchmark times _boost_one_round) -------------
+    def _start(self, X, y, era, *, feature_names=None, eval_sets=None) -> None:
+        """Validate, bin, pack and upload the data; allocate the device state."""
         cfg = self.config
-        X_np = X.detach().cpu().numpy() if isinstance(X, torch.Tensor) else np.asarray(X)
-        y_np = np.asarray(y, dtype=np.float32)
+        on_device = isinstance(X, torch.Tensor) and X.is_cuda
+        X_np = X if on_device else (X.detach().cpu().numpy() if isinstance(X, torch.Tensor) else np.asarray(X))
+        y_np = np.asarray(y.detach().cpu().numpy() if isinstance(y, torch.Tensor) else y, dtype=np.float32)
         if y_np.ndim != 1:
             raise ValueError("y must be 1-D")
         N, F = X_np.shape
@@ -442,7 +457,7 @@ class PackBoost:
         self._feature_names = list(feature_names) if feature_names is not None else [f"f{i}" for i in range(F)]
 
         # rows ordered by (era, row); identity when eras are already contiguous and ascending
-        if N > 1 and np.all(era_encoded[1:] >= era_encoded[:-1]):
+        if N <= 1 or np.all(era_encoded[1:] >= era_encoded[:-1]):
             order = None
             era_sorted = era_encoded
         else:
@@ -452,16 +467,27 @@ class PackBoost:
         era_offsets = np.concatenate([[0], np.cumsum(counts)]).astype(np.int32)
 
         # binning (packboost/data.py:61-93)
-        if bool(cfg.prebinned) and not detect_prebinned(X_np, cfg.max_bins):
+        if on_device:
+            is_binned = X_np.dtype in (torch.uint8, torch.int8) and int(X_np.max()) < cfg.max_bins
+        else:
+            is_binned = detect_prebinned(X_np, cfg.max_bins)
+        if bool(cfg.prebinned) and not is_binned:
             raise ValueError("prebinned=True requires X to contain integer bins within [0, max_bins).")
-        if bool(cfg.prebinned) or detect_prebinned(X_np, cfg.max_bins):
+        if is_binned:
             edges = None
             self._binner = BinningResult(bins=None, bin_edges=None, prebinned=True)
-            X_src = X_np if X_np.dtype in (np.uint8, np.int8) else X_np.astype(np.uint8)
-            X_src = X_src.view(np.uint8)
+            if on_device:
+                X_src = X_np.view(torch.uint8)
+            else:
+                X_src = X_np if X_np.dtype in (np.uint8, np.int8) else X_np.astype(np.uint8)
+                X_src = X_src.view(np.uint8)
         else:
-            X_src = X_np.astype(np.float32, copy=False)
-            edges = quantile_edges(X_src, cfg.max_bins)
+            if on_device:
+                X_src = X_np.to(torch.float32)
+                edges = quantile_edges(X_src.cpu().numpy(), cfg.max_bins)
+            else:
+                X_src = X_np.astype(np.float32, copy=False)
+                edges = quantile_edges(X_src, cfg.max_bins)
             self._binner = BinningResult(bins=None, bin_edges=edges, prebinned=False)
 
         rank, world = 0, 1
@@ -472,9 +498,9 @@ class PackBoost:
         matrix = pack_feature_major(X_src, edges, cfg.max_bins, row_order=order,
                                     feature_map=feat_local if world > 1 else None, n_features_local=n_local)
         y_sorted = y_np if order is None else y_np[order]
-        trainer = _DeviceTrainer(cfg, matrix, y_sorted, era_offsets, F, feat_local, rank, world)
-        self._trainer = trainer
+        self._trainer = _DeviceTrainer(cfg, matrix, y_sorted, era_offsets, F, feat_local, rank, world)
         self._row_order = order
+        self._fit_ctx = {"era_sorted": era_sorted, "y_sorted": y_sorted, "F": F}
 
         self._depth_logs = []
         self._round_metrics = []
@@ -483,56 +509,56 @@ class PackBoost:
         self._forest_cache = None
         self._tree_weight = float(cfg.learning_rate)
         self._trained_pack_size = int(cfg.pack_size)
+        self._eval_states = self._prepare_eval_sets(eval_sets)
 
-        eval_states = self._prepare_eval_sets(eval_sets)
-        want_metrics = (round_callback is not None) or bool(eval_states) or os.getenv("PACKBOOST_TRAIN_METRICS") == "1"
+    def _boost_one_round(self, round_idx: int, num_rounds: int, want_callback: bool = False) -> dict[str, float]:
+        """One boosting round (``packboost/booster.py:494-655``)."""
+        cfg, trainer, ctx = self.config, self._trainer, self._fit_ctx
+        F, D, k = ctx["F"], int(cfg.max_depth), trainer.n_sampled()
+        t0 = perf_counter()
+        # one draw per depth, speculating that every depth has active nodes; the generator is
+        # rewound below when the device reports an empty frontier (packboost/booster.py:516-519)
+        states, subsets = [], []
+        for _ in range(D):
+            states.append(self._rng.get_state())
+            subsets.append(torch.randperm(F, generator=self._rng)[:k].numpy().astype(np.int32))
+        trainer.run_round(subsets)
+        head, winners = trainer.read_log()
+        tree, n_ctx = _tree_from_log(head, winners, D)
+        self._last_n_ctx = n_ctx
+        for d in range(D):
+            if n_ctx[d] == 0:
+                self._rng.set_state(states[d])
+                break
+            self._depth_logs.append(self._depth_log(d, n_ctx[d], k))
+        self._distinct.append((tree, int(cfg.pack_size)))
+        self._trees.extend([tree] * int(cfg.pack_size))
+
+        eval_states = self._eval_states
+        want_metrics = want_callback or bool(eval_states) or os.getenv("PACKBOOST_TRAIN_METRICS") == "1"
+        metrics: dict[str, float] = {"round": round_idx + 1}
+        if want_metrics:
+            trainer.flush_predictions()
+            metrics["train_corr"] = _era_correlation_np(ctx["era_sorted"], ctx["y_sorted"], trainer.preds.cpu().numpy())
+        else:
+            metrics["train_corr"] = float("nan")
         try:
             eval_every = int(os.getenv("PACKBOOST_EVAL_EVERY", "1"))
         except Exception:
             eval_every = 1
+        if eval_states and eval_every > 0 and (((round_idx + 1) % eval_every == 0) or round_idx + 1 == num_rounds):
+            self._update_eval_sets(eval_states)
+        dt = perf_counter() - t0
+        metrics["trees_per_second"] = (cfg.pack_size / dt) if dt > 0 else float("inf")
+        metrics["round_seconds"] = dt
+        for stt in eval_states:
+            metrics[f"{stt['name']}_corr"] = _era_correlation_np(stt["era"], stt["y"], stt["preds"].cpu().numpy())
+        self._round_metrics.append(metrics)
+        return metrics
 
-        k = trainer.n_sampled()
-        D = int(cfg.max_depth)
-        for round_idx in range(num_rounds):
-            t0 = perf_counter()
-            # one draw per depth, speculating that every depth has active nodes; the generator is
-            # rewound below when the device reports an empty frontier (packboost/booster.py:516-519)
-            states, subsets = [], []
-            for _ in range(D):
-                states.append(self._rng.get_state())
-                subsets.append(torch.randperm(F, generator=self._rng)[:k].numpy().astype(np.int32))
-            trainer.run_round(subsets)
-            head, winners = trainer.read_log()
-            tree, n_ctx = _tree_from_log(head, winners, D)
-            for d in range(D):
-                if n_ctx[d] == 0:
-                    self._rng.set_state(states[d])
-                    break
-                self._depth_logs.append(self._depth_log(d, n_ctx[d], k))
-            self._distinct.append((tree, int(cfg.pack_size)))
-            self._trees.extend([tree] * int(cfg.pack_size))
-
-            metrics: dict[str, float] = {"round": round_idx + 1}
-            if want_metrics:
-                trainer.flush_predictions()
-                preds_sorted = trainer.preds.cpu().numpy()
-                metrics["train_corr"] = _era_correlation_np(era_sorted, y_sorted, preds_sorted)
-            else:
-                metrics["train_corr"] = float("nan")
-            if eval_states and eval_every > 0 and (((round_idx + 1) % eval_every == 0) or round_idx + 1 == num_rounds):
-                self._update_eval_sets(eval_states)
-            dt = perf_counter() - t0
-            metrics["trees_per_second"] = (cfg.pack_size / dt) if dt > 0 else float("inf")
-            metrics["round_seconds"] = dt
-            for stt in eval_states:
-                metrics[f"{stt['name']}_corr"] = _era_correlation_np(stt["era"], stt["y"], stt["preds"].cpu().numpy())
-            self._round_metrics.append(metrics)
-            if round_callback is not None:
-                round_callback(round_idx + 1, metrics)
-
-        trainer.flush_predictions()
+    def _finish(self) -> None:
+        self._trainer.flush_predictions()
         torch.cuda.current_stream().synchronize()
-        return self
 
     def train_predictions(self) -> np.ndarray:
         """Predictions of the training rows as maintained during ``fit`` (original row order)."""

@@ -47,9 +47,8 @@ constexpr int kMaxCtx = 1 << (PB_MAX_DEPTH - 1);        // frontier nodes at the
 constexpr int kMaxTreeNodes = (1 << (PB_MAX_DEPTH + 1)); // 2^(D+1) - 1 rounded up
 constexpr int kMaxWinners = (1 << PB_MAX_DEPTH);         // sum over depths of frontier sizes (+1)
 constexpr uint16_t kSlotNone = 0xFFFFu;
-constexpr int kSingleTileRows = 32768;  // an era up to this size is accumulated by one CTA per feature group
-constexpr int kSplitTileRows = 16384;   // larger eras are cut into tiles of this many rows
-constexpr int kGqBits = 30;             // |gq| <= 2^30
+constexpr int kTileRowsMax = 8160;      // rows one histogram CTA accumulates (255 chunks of 32 rows)
+constexpr int kGqBitsMax = 30;          // |gq| <= 2^30 at most; fewer bits when tiles are large
 
 // ---- device-side tables -----------------------------------------------------------------
 
@@ -143,6 +142,8 @@ struct HistLaunch {
     const int32_t* n_nodes_ptr;  // device count of frontier nodes, or nullptr
     int n_nodes;                 // upper bound (grid sizing) and value when n_nodes_ptr == nullptr
     int node_stride;
+    int count_bits;              // CB: tile rows < 2^CB
+    int lo_bits;                 // LB = 32 - 2*CB
     uint32_t* cnt;
     int64_t* gsum;
 };

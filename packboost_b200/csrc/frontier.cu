@@ -10,15 +10,15 @@ namespace {
 
 constexpr int kRowThreads = 256;
 
-__device__ __forceinline__ float scale_from_max(float max_abs, float* inv) {
-    // power of two with max_abs * scale < 2^30
+__device__ __forceinline__ float scale_from_max(float max_abs, int gq_bits, float* inv) {
+    // power of two with max_abs * scale < 2^gq_bits
     if (!(max_abs > 0.f) || !isfinite(max_abs)) {
         *inv = 1.f;
         return 1.f;
     }
     int ex;
     frexpf(max_abs, &ex);  // max_abs = m * 2^ex, m in [0.5, 1)
-    int sh = kGqBits - ex;
+    int sh = gq_bits - ex;
     sh = max(-100, min(100, sh));
     *inv = ldexpf(1.f, -sh);
     return ldexpf(1.f, sh);
@@ -63,9 +63,9 @@ __global__ void __launch_bounds__(kRowThreads) preds_absmax_kernel(
 // gq = rint((preds - y) * scale); rows back to the root; sum of gq
 __global__ void __launch_bounds__(kRowThreads) quantise_kernel(
     const float* __restrict__ preds, const float* __restrict__ y, int32_t* __restrict__ gq,
-    uint16_t* __restrict__ slot, uint16_t* __restrict__ leaf, int64_t n, int64_t n_pad, CtlHead* head) {
+    uint16_t* __restrict__ slot, uint16_t* __restrict__ leaf, int64_t n, int64_t n_pad, CtlHead* head, int gq_bits) {
     float inv;
-    const float scale = scale_from_max(__uint_as_float(head->max_abs_bits), &inv);
+    const float scale = scale_from_max(__uint_as_float(head->max_abs_bits), gq_bits, &inv);
     long long acc = 0;
     for (int64_t r = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; r < n_pad; r += (int64_t)gridDim.x * blockDim.x) {
         if (r < n) {
@@ -90,10 +90,10 @@ __global__ void __launch_bounds__(kRowThreads) quantise_kernel(
     }
 }
 
-__global__ void root_kernel(Ctl c, int64_t n, int min_leaf, double lambda) {
+__global__ void root_kernel(Ctl c, int64_t n, int min_leaf, double lambda, int gq_bits) {
     if (threadIdx.x != 0 || blockIdx.x != 0) return;
     float inv;
-    const float scale = scale_from_max(__uint_as_float(c.head->max_abs_bits), &inv);
+    const float scale = scale_from_max(__uint_as_float(c.head->max_abs_bits), gq_bits, &inv);
     c.head->scale = scale;
     c.head->inv_scale = inv;
     const long long g = c.head->root_gq;
@@ -133,121 +133,193 @@ struct SelectArgs {
     double lambda;
 };
 
+// Candidate order inside a feature block: higher score, then larger left count, then the later
+// position (exact float equality decides ties, as in the tensor code this replaces).
+struct BlockBest {
+    float s;
+    long long c;
+    long long lg;
+    int p;
+    int k;
+};
+
+__device__ __forceinline__ bool block_better(const BlockBest& x, const BlockBest& y) {
+    // true when x beats y
+    if (x.p < 0) return false;
+    if (y.p < 0) return true;
+    if (x.s != y.s) return x.s > y.s;
+    if (x.c != y.c) return x.c > y.c;
+    return x.p > y.p;
+}
+
 __global__ void __launch_bounds__(1024) select_kernel(SelectArgs a) {
     Ctl& c = a.c;
+    __shared__ int s_flag[kMaxCtx];   // bit 0: split, bit 1: left child stays active, bit 2: right child
+    __shared__ int s_ids[kMaxCtx];    // exclusive count of splits before the node
+    __shared__ int s_slots[kMaxCtx];  // exclusive count of active children before the node
+    __shared__ int s_any_dir;
     const int n_ctx = c.head->n_ctx[a.depth];
     if (n_ctx <= 0) return;
     const FrontierNode* cur = c.frontier[a.depth & 1];
     FrontierNode* nxt = c.frontier[(a.depth + 1) & 1];
     pb_winner* win = c.winners + ((1 << a.depth) - 1);
     const float inv = c.head->inv_scale;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
+    const bool keep_frontier = (a.depth + 1) < a.max_depth;
+    if (threadIdx.x == 0) s_any_dir = 0;
 
-    // ---- per node: in-block winner, then cross-block merge ----
-    for (int n = threadIdx.x; n < n_ctx; n += blockDim.x) {
+    // ---- A. one warp per node: in-block winner (lanes stride the block), cross-block merge ----
+    for (int n = warp; n < n_ctx; n += n_warps) {
         float best_s = -INFINITY;
         long long best_c = -1, best_lg = 0;
         int best_f = -1, best_t = -1;
         for (int b0 = 0; b0 < a.n_sampled; b0 += a.block_size) {
             const int b1 = min(a.n_sampled, b0 + a.block_size);
-            float bs = -INFINITY;
-            long long bc = -1, blg = 0;
-            int bp = -1, bk = -1;
+            BlockBest mine{-INFINITY, -1, 0, -1, -1};
             bool has_nan = false;
-            for (int p = b0; p < b1; ++p) {
+            for (int p = b0 + lane; p < b1; p += 32) {
                 const Cand cd = a.cand[(size_t)p * a.node_stride + n];
                 if (cd.flags & 1u) has_nan = true;
                 if (cd.k < 0) continue;
-                if ((cd.score > bs) || (cd.score == bs && (long long)cd.left_count >= bc)) {
-                    bs = cd.score; bc = cd.left_count; blg = cd.left_gq; bp = p; bk = cd.k;
-                }
+                const BlockBest x{cd.score, (long long)cd.left_count, cd.left_gq, p, cd.k};
+                if (block_better(x, mine)) mine = x;
             }
-            if (has_nan || bp < 0) continue;
-            const int feat = a.sampled[bp];
-            const int thr = a.thr_ids[bk];
-            const bool upd = (bs > best_s) ||
-                             (bs == best_s && ((bc > best_c) ||
-                                               (bc == best_c && ((feat > best_f) || (feat == best_f && thr > best_t)))));
-            if (upd) { best_s = bs; best_c = bc; best_lg = blg; best_f = feat; best_t = thr; }
+            has_nan = __any_sync(0xFFFFFFFFu, has_nan);
+            for (int d = 16; d > 0; d >>= 1) {
+                BlockBest o;
+                o.s = __shfl_xor_sync(0xFFFFFFFFu, mine.s, d);
+                o.c = __shfl_xor_sync(0xFFFFFFFFu, mine.c, d);
+                o.lg = __shfl_xor_sync(0xFFFFFFFFu, mine.lg, d);
+                o.p = __shfl_xor_sync(0xFFFFFFFFu, mine.p, d);
+                o.k = __shfl_xor_sync(0xFFFFFFFFu, mine.k, d);
+                if (block_better(o, mine)) mine = o;
+            }
+            if (has_nan || mine.p < 0) continue;
+            const int feat = a.sampled[mine.p];
+            const int thr = a.thr_ids[mine.k];
+            const bool upd = (mine.s > best_s) ||
+                             (mine.s == best_s && ((mine.c > best_c) ||
+                                                   (mine.c == best_c && ((feat > best_f) || (feat == best_f && thr > best_t)))));
+            if (upd) { best_s = mine.s; best_c = mine.c; best_lg = mine.lg; best_f = feat; best_t = thr; }
         }
-        const FrontierNode fn = cur[n];
-        pb_winner w;
-        w.feature = best_f;
-        w.threshold = best_t;
-        w.score = best_s;
-        w.tree_node = fn.tree_node;
-        w.left_count = (best_f >= 0) ? best_c : 0;
-        w.total_count = fn.count;
-        w.left_gq = (best_f >= 0) ? best_lg : 0;
-        w.total_gq = fn.gq;
-        w.left_id = -1;
-        w.right_id = -1;
-        const float tg32 = __fmul_rn(__ll2float_rn(fn.gq), inv);
-        const float lg32 = __fmul_rn(__ll2float_rn(w.left_gq), inv);
-        const float th32 = (float)fn.count;
-        const float lh32 = (float)w.left_count;
-        w.left_grad = lg32;
-        w.total_grad = tg32;
-        if (best_f >= 0) {
-            w.left_value = -(double)lg32 / ((double)lh32 + a.lambda);
-            const double rg = (double)tg32 - (double)lg32;
-            const double rh = (double)th32 - (double)lh32;
-            w.right_value = -rg / (rh + a.lambda);
-        } else {
-            // no usable candidate: the node stays a leaf with its Newton value
-            w.left_value = -(double)tg32 / ((double)th32 + a.lambda);
-            w.right_value = w.left_value;
+        if (lane == 0) {
+            const FrontierNode fn = cur[n];
+            pb_winner w;
+            w.feature = best_f;
+            w.threshold = best_t;
+            w.score = best_s;
+            w.tree_node = fn.tree_node;
+            w.left_count = (best_f >= 0) ? best_c : 0;
+            w.total_count = fn.count;
+            w.left_gq = (best_f >= 0) ? best_lg : 0;
+            w.total_gq = fn.gq;
+            w.left_id = -1;
+            w.right_id = -1;
+            const float tg32 = __fmul_rn(__ll2float_rn(fn.gq), inv);
+            const float lg32 = __fmul_rn(__ll2float_rn(w.left_gq), inv);
+            const float th32 = (float)fn.count;
+            const float lh32 = (float)w.left_count;
+            w.left_grad = lg32;
+            w.total_grad = tg32;
+            int flag = 0;
+            if (best_f >= 0) {
+                w.left_value = -(double)lg32 / ((double)lh32 + a.lambda);
+                const double rg = (double)tg32 - (double)lg32;
+                const double rh = (double)th32 - (double)lh32;
+                w.right_value = -rg / (rh + a.lambda);
+                flag = 1;
+                if (keep_frontier && w.left_count >= 2ll * a.min_leaf) flag |= 2;
+                if (keep_frontier && (w.total_count - w.left_count) >= 2ll * a.min_leaf) flag |= 4;
+            } else {
+                // no usable candidate: the node stays a leaf with its Newton value
+                w.left_value = -(double)tg32 / ((double)th32 + a.lambda);
+                w.right_value = w.left_value;
+            }
+            win[n] = w;
+            s_flag[n] = flag;
         }
-        win[n] = w;
     }
     __syncthreads();
 
-    // ---- sequential numbering of children and of the next frontier ----
-    if (threadIdx.x == 0) {
-        int next_id = c.head->n_tree_nodes;
-        int next_slot = 0;
-        int any_dir = 0;
-        const bool keep_frontier = (a.depth + 1) < a.max_depth;
-        for (int n = 0; n < n_ctx; ++n) {
-            pb_winner& w = win[n];
-            PartEntry pe;
-            pe.feature = w.feature;
-            pe.threshold = w.threshold;
-            pe.slot_left = pe.slot_right = kSlotNone;
-            pe.leaf_left = pe.leaf_right = (uint16_t)w.tree_node;
-            if (w.feature >= 0) {
-                w.left_id = next_id;
-                w.right_id = next_id + 1;
-                next_id += 2;
-                pe.leaf_left = (uint16_t)w.left_id;
-                pe.leaf_right = (uint16_t)w.right_id;
-                c.node_value[w.left_id] = w.left_value;
-                c.node_value[w.right_id] = w.right_value;
-                const long long lc = w.left_count, rc = w.total_count - w.left_count;
-                const long long lg = w.left_gq, rg = w.total_gq - w.left_gq;
-                if (keep_frontier && lc >= 2ll * a.min_leaf) {
-                    FrontierNode fn; fn.tree_node = w.left_id; fn.count = (int32_t)lc; fn.gq = lg;
-                    nxt[next_slot] = fn;
-                    pe.slot_left = (uint16_t)next_slot++;
-                    any_dir |= (lg != 0);
-                }
-                if (keep_frontier && rc >= 2ll * a.min_leaf) {
-                    FrontierNode fn; fn.tree_node = w.right_id; fn.count = (int32_t)rc; fn.gq = rg;
-                    nxt[next_slot] = fn;
-                    pe.slot_right = (uint16_t)next_slot++;
-                    any_dir |= (rg != 0);
-                }
-            } else {
-                c.node_value[w.tree_node] = w.left_value;
+    // ---- B. warp 0: exclusive prefix counts of splits and of active children ----
+    if (warp == 0) {
+        int carry_id = 0, carry_slot = 0;
+        for (int base = 0; base < n_ctx; base += 32) {
+            const int n = base + lane;
+            const int fl = (n < n_ctx) ? s_flag[n] : 0;
+            int v_id = fl & 1;
+            int v_slot = ((fl >> 1) & 1) + ((fl >> 2) & 1);
+            const int own_id = v_id, own_slot = v_slot;
+            for (int d = 1; d < 32; d <<= 1) {
+                const int t1 = __shfl_up_sync(0xFFFFFFFFu, v_id, d);
+                const int t2 = __shfl_up_sync(0xFFFFFFFFu, v_slot, d);
+                if (lane >= d) { v_id += t1; v_slot += t2; }
             }
-            c.part[n] = pe;
+            if (n < n_ctx) {
+                s_ids[n] = carry_id + v_id - own_id;
+                s_slots[n] = carry_slot + v_slot - own_slot;
+            }
+            carry_id += __shfl_sync(0xFFFFFFFFu, v_id, 31);
+            carry_slot += __shfl_sync(0xFFFFFFFFu, v_slot, 31);
         }
-        c.head->n_tree_nodes = next_id;
-        c.head->n_ctx[a.depth + 1] = next_slot;
-        c.head->any_dir[a.depth + 1] = any_dir;
-        c.log_head->n_ctx[a.depth] = n_ctx;
-        if (a.depth + 1 <= kMaxDepth) c.log_head->n_ctx[a.depth + 1] = next_slot;
-        c.log_head->n_tree_nodes = next_id;
+        if (lane == 0) {
+            const int next_id = c.head->n_tree_nodes + 2 * carry_id;
+            c.head->n_tree_nodes = next_id;
+            c.head->n_ctx[a.depth + 1] = carry_slot;
+            c.log_head->n_ctx[a.depth] = n_ctx;
+            if (a.depth + 1 <= kMaxDepth) c.log_head->n_ctx[a.depth + 1] = carry_slot;
+            c.log_head->n_tree_nodes = next_id;
+        }
     }
+    __syncthreads();
+    // (n_tree_nodes was advanced above; recover the value it had before this depth)
+    int total_splits = 0;
+    {
+        const int last = n_ctx - 1;
+        total_splits = s_ids[last] + (s_flag[last] & 1);
+    }
+    const int first_id = c.head->n_tree_nodes - 2 * total_splits;
+
+    // ---- C. one thread per node: child ids, next frontier, partition table ----
+    int any_dir = 0;
+    for (int n = threadIdx.x; n < n_ctx; n += blockDim.x) {
+        pb_winner& w = win[n];
+        const int fl = s_flag[n];
+        PartEntry pe;
+        pe.feature = w.feature;
+        pe.threshold = w.threshold;
+        pe.slot_left = pe.slot_right = kSlotNone;
+        pe.leaf_left = pe.leaf_right = (uint16_t)w.tree_node;
+        if (fl & 1) {
+            const int lid = first_id + 2 * s_ids[n];
+            w.left_id = lid;
+            w.right_id = lid + 1;
+            pe.leaf_left = (uint16_t)lid;
+            pe.leaf_right = (uint16_t)(lid + 1);
+            c.node_value[lid] = w.left_value;
+            c.node_value[lid + 1] = w.right_value;
+            int slot = s_slots[n];
+            if (fl & 2) {
+                FrontierNode fn; fn.tree_node = lid; fn.count = (int32_t)w.left_count; fn.gq = w.left_gq;
+                nxt[slot] = fn;
+                pe.slot_left = (uint16_t)slot++;
+                any_dir |= (w.left_gq != 0);
+            }
+            if (fl & 4) {
+                FrontierNode fn; fn.tree_node = lid + 1; fn.count = (int32_t)(w.total_count - w.left_count);
+                fn.gq = w.total_gq - w.left_gq;
+                nxt[slot] = fn;
+                pe.slot_right = (uint16_t)slot;
+                any_dir |= (fn.gq != 0);
+            }
+        } else {
+            c.node_value[w.tree_node] = w.left_value;
+        }
+        c.part[n] = pe;
+    }
+    if (any_dir) atomicOr(&s_any_dir, 1);
+    __syncthreads();
+    if (threadIdx.x == 0) c.head->any_dir[a.depth + 1] = s_any_dir;
 }
 
 // ---- row -> node map ------------------------------------------------------------------------
@@ -363,6 +435,9 @@ static int check_state(const pb_train_state* st) {
                    st->slot && st->leaf && st->ctl && st->workspace,
                "a device buffer of the training state is null");
     PB_REQUIRE(st->lambda_l2 > 0.0, "lambda_l2 must be positive");
+    PB_REQUIRE(st->count_bits >= 1 && st->count_bits <= 13 && st->lo_bits == 32 - 2 * st->count_bits &&
+                   st->gq_bits >= st->lo_bits && st->gq_bits <= kGqBitsMax && st->gq_bits <= 63 - 3 * st->count_bits,
+               "accumulator widths are not set: call pb_train_prepare first");
     PB_REQUIRE(((uintptr_t)st->codes % 16 == 0) && ((uintptr_t)st->gq % 16 == 0) && ((uintptr_t)st->slot % 16 == 0),
                "codes, gq and slot must be 16-byte aligned");
     return PB_OK;
@@ -390,7 +465,14 @@ extern "C" int pb_train_prepare(pb_train_state* st, const int32_t* era_offsets_h
     }
     PB_REQUIRE(era_offsets_host[st->n_eras] == st->n_rows, "era_offsets[E] must equal n_rows");
     st->max_era_rows = mx;
-    st->hist_rows_per_tile = (mx <= kSingleTileRows) ? kSingleTileRows : kSplitTileRows;
+    st->hist_rows_per_tile = kTileRowsMax;
+    // widths of the 32-bit shared-memory accumulators of the histogram kernel
+    const int64_t tile = (mx < kTileRowsMax) ? mx : kTileRowsMax;
+    int cb = 1;
+    while ((1ll << cb) <= tile) ++cb;  // tile < 2^cb
+    st->count_bits = cb;
+    st->lo_bits = 32 - 2 * cb;
+    st->gq_bits = (63 - 3 * cb < kGqBitsMax) ? (63 - 3 * cb) : kGqBitsMax;
     int rc = check_state(st);
     if (rc) return rc;
     PB_REQUIRE(st->workspace_bytes >= pb_workspace_min_bytes(st), "workspace too small: %lld < %lld",
@@ -409,8 +491,8 @@ extern "C" int pb_round_begin(const pb_train_state* st, int64_t apply_previous, 
     preds_absmax_kernel<<<g, kRowThreads, 0, stream>>>(st->preds, st->y, st->leaf, c.delta, st->n_rows,
                                                         apply_previous ? 1 : 0, c.head);
     quantise_kernel<<<g, kRowThreads, 0, stream>>>(st->preds, st->y, st->gq, st->slot, st->leaf, st->n_rows,
-                                                    rows_padded(st->n_rows), c.head);
-    root_kernel<<<1, 32, 0, stream>>>(c, st->n_rows, (int)st->min_samples_leaf, st->lambda_l2);
+                                                    rows_padded(st->n_rows), c.head, (int)st->gq_bits);
+    root_kernel<<<1, 32, 0, stream>>>(c, st->n_rows, (int)st->min_samples_leaf, st->lambda_l2, (int)st->gq_bits);
     prof_end(kProfRound, stream);
     count_launch(4);
     PB_LAUNCH_CHECK("round_begin");
@@ -478,6 +560,8 @@ extern "C" int pb_depth_hist_score(const pb_train_state* st, int64_t depth, cons
         h.n_nodes_ptr = &c.head->n_ctx[depth];
         h.n_nodes = stride;
         h.node_stride = stride;
+        h.count_bits = (int)st->count_bits;
+        h.lo_bits = (int)st->lo_bits;
         h.cnt = cnt;
         h.gsum = gsum;
         rc = launch_hist(h, stream);
@@ -631,6 +715,8 @@ extern "C" int pb_hist_build(const pb_train_state* st, const int32_t* feat_rows,
     h.n_nodes_ptr = nullptr;
     h.n_nodes = (int)n_nodes;
     h.node_stride = (int)node_stride;
+    h.count_bits = (int)st->count_bits;
+    h.lo_bits = (int)st->lo_bits;
     h.cnt = cnt;
     h.gsum = gsum;
     return launch_hist(h, (cudaStream_t)stream);

@@ -1,19 +1,23 @@
 // Per-(feature, node, era, bin) histograms of counts and fixed-point gradient sums.
 //
-// Rows are ordered by era, so an era is a contiguous row range.  One CTA accumulates one row
-// tile of one era for a small group of features in shared memory and then writes (or, when an
-// era is cut into several tiles, atomically adds) its cells to the global histogram.  Because
-// every cell is an integer, the result does not depend on the order of the additions.
+// Rows are ordered by era, so an era is a contiguous row range.  One CTA owns one row tile of
+// one era (at most kTileRowsMax rows) and a contiguous range of the sampled features.  Every
+// thread owns one 16-byte chunk of codes per feature (32 rows of 4-bit codes, 16 rows of 8-bit
+// codes); the slot and gradient of those rows are loaded once and stay in registers while the
+// thread walks the CTA's features, prefetching the next feature's chunk while it accumulates
+// the current one.  Features are accumulated in groups in shared memory and each group is
+// written (or, when an era is cut into several tiles, atomically added) to the global
+// histogram.  Every cell is an integer, so the result does not depend on the order of the
+// additions.
 //
-// Shared-memory cell: one 64-bit word holding (gq_sum << 16) + count.  A tile has fewer than
-// 65536 rows, so the count never carries into the gradient field, and |gq| <= 2^30 keeps the
-// gradient field inside 48 bits.  One 64-bit shared atomic per (row, feature) updates both.
-// When the number of cells per feature is small the cells are replicated per lane group
-// ("copies") so that lanes of a warp rarely hit the same address.
-//
-// Global loads: a thread owns 32 consecutive rows (4-bit codes: one 128-bit load per feature)
-// or 16 consecutive rows (8-bit codes).  The slot and gradient of those rows are loaded once
-// with 128-bit loads and kept in registers while the thread walks the features of the group.
+// Shared-memory cell: two 32-bit words updated with one native 32-bit shared atomic each
+// (64-bit shared atomics are an order of magnitude slower on this part):
+//   A = (sum of lo) << CB | count        lo = gq & (2^LB - 1)
+//   B = sum of hi                        hi = gq >> LB (arithmetic)
+// With fewer than 2^CB rows per tile, LB = 32 - 2*CB and |gq| <= 2^(63 - 3*CB) (capped at
+// 2^30) neither word can overflow; pb_train_prepare derives CB/LB and the gradient scale from
+// the largest tile.  When a feature has few cells they are replicated ("copies") so that the
+// lanes of a warp rarely hit the same address.
 
 #include "common.cuh"
 
@@ -21,9 +25,8 @@ namespace pb {
 
 namespace {
 
-constexpr int kHistThreads = 256;
-constexpr int kMaxGroup = 8;            // features per CTA
-constexpr int kSmemCellBudget = 24576;  // 192 KB of 64-bit cells
+constexpr int kMaxGroup = 8;            // features accumulated together in shared memory
+constexpr int kSmemCellBudget = 24576;  // 192 KB of 2-word cells
 
 struct HistKernelArgs {
     const uint8_t* codes;
@@ -41,17 +44,21 @@ struct HistKernelArgs {
     int n_nodes;
     int node_stride;
     int nodes_per_chunk;
-    int group;       // features per CTA
+    int feats_per_cta;
+    int group;       // features per shared-memory pass
     int copies;      // power of two, <= 32
     int use_atomics; // 1: several tiles per era -> global atomics onto a zeroed histogram
+    int count_bits;  // CB
+    int lo_bits;     // LB
     uint32_t* cnt;
     int64_t* gsum;
 };
 
-template <int BITS>
-__global__ void __launch_bounds__(kHistThreads) hist_kernel(HistKernelArgs a) {
-    constexpr int RPI = (BITS == 4) ? 32 : 16;  // rows per thread iteration (16 bytes of codes)
-    extern __shared__ unsigned long long cells[];
+template <int BITS, int THREADS>
+__global__ void __launch_bounds__(THREADS) hist_kernel(HistKernelArgs a) {
+    constexpr int RPI = (BITS == 4) ? 32 : 16;  // rows per thread (16 bytes of codes)
+    extern __shared__ uint32_t cells[];         // [group][cells_per_feat][copies][2]
+    __shared__ int s_frow[256];
 
     const int n_nodes = a.n_nodes_ptr ? min(*a.n_nodes_ptr, a.n_nodes) : a.n_nodes;
     const int node_lo = blockIdx.z * a.nodes_per_chunk;
@@ -65,90 +72,123 @@ __global__ void __launch_bounds__(kHistThreads) hist_kernel(HistKernelArgs a) {
     const int r1 = min(era_end, r0 + a.tile_rows);
     if (r0 >= r1 && a.use_atomics) return;  // (without atomics an empty tile still writes its zeros)
 
-    const int f0 = blockIdx.y * a.group;
-    const int nf = min(a.group, a.n_feat - f0);
+    const int fa = blockIdx.y * a.feats_per_cta;
+    const int fb = min(a.n_feat, fa + a.feats_per_cta);
+    for (int i = threadIdx.x; i < fb - fa; i += blockDim.x) s_frow[i] = a.feat_rows[fa + i];
+
     const int nb = a.max_bins;
     const int cells_per_feat = (node_hi - node_lo) * nb;
     const int copies = a.copies;
-    const int total_cells = nf * cells_per_feat * copies;
-    for (int i = threadIdx.x; i < total_cells; i += kHistThreads) cells[i] = 0ull;
-    __syncthreads();
-
     const int lane_copy = threadIdx.x & (copies - 1);
-    const int c0 = r0 / RPI;
-    const int c1 = (r1 + RPI - 1) / RPI;
+    const int CB = a.count_bits, LB = a.lo_bits;
+    const uint32_t lo_mask = (1u << LB) - 1u;
 
-    for (int c = c0 + threadIdx.x; c < c1; c += kHistThreads) {
+    // ---- row state of this thread's chunk, kept in registers for the whole CTA ----
+    const int c = r0 / RPI + threadIdx.x;
+    const bool has = (r0 < r1) && (c * RPI < r1);
+    int32_t g[RPI];
+    uint32_t cb2[RPI / 2];  // two 16-bit cell bases per word; 0xFFFF: row not accumulated here
+    if (has) {
         const int row_base = c * RPI;
-        // slot (uint16) and gq (int32) of RPI rows
-        int32_t g[RPI];
-        int cellbase[RPI];  // (slot - node_lo) * nb, or -1 when the row is not accumulated here
-        {
-            const uint4* sp = reinterpret_cast<const uint4*>(a.slot + row_base);
-            const int4* gp = reinterpret_cast<const int4*>(a.gq + row_base);
+        const uint4* sp = reinterpret_cast<const uint4*>(a.slot + row_base);
+        const int4* gp = reinterpret_cast<const int4*>(a.gq + row_base);
 #pragma unroll
-            for (int q = 0; q < RPI / 8; ++q) {
-                const uint4 sv = __ldg(sp + q);
-                const uint32_t w[4] = {sv.x, sv.y, sv.z, sv.w};
+        for (int q = 0; q < RPI / 8; ++q) {
+            const uint4 sv = __ldg(sp + q);
+            const uint32_t w[4] = {sv.x, sv.y, sv.z, sv.w};
 #pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                    const int s = (w[j >> 1] >> ((j & 1) * 16)) & 0xFFFF;
-                    const int r = row_base + q * 8 + j;
+            for (int j = 0; j < 4; ++j) {
+                uint32_t packed = 0;
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    const int s = (w[j] >> (h * 16)) & 0xFFFF;
+                    const int r = row_base + q * 8 + j * 2 + h;
                     const bool ok = (r >= r0) & (r < r1) & (s >= node_lo) & (s < node_hi);
-                    cellbase[q * 8 + j] = ok ? (s - node_lo) * nb : -1;
+                    packed |= (ok ? (uint32_t)((s - node_lo) * nb) : 0xFFFFu) << (h * 16);
                 }
-            }
-#pragma unroll
-            for (int q = 0; q < RPI / 4; ++q) {
-                const int4 gv = __ldg(gp + q);
-                g[q * 4 + 0] = gv.x;
-                g[q * 4 + 1] = gv.y;
-                g[q * 4 + 2] = gv.z;
-                g[q * 4 + 3] = gv.w;
+                cb2[q * 4 + j] = packed;
             }
         }
-        for (int fi = 0; fi < nf; ++fi) {
-            const int frow = __ldg(a.feat_rows + f0 + fi);
-            const uint4 cv = __ldg(reinterpret_cast<const uint4*>(a.codes + (int64_t)frow * a.pitch) + c);
-            const uint32_t w[4] = {cv.x, cv.y, cv.z, cv.w};
-            unsigned long long* fc = cells + (size_t)fi * cells_per_feat * copies + lane_copy;
 #pragma unroll
-            for (int j = 0; j < RPI; ++j) {
-                int code;
-                if (BITS == 4) {
-                    code = (w[j >> 3] >> ((j & 7) * 4)) & 0xF;
-                } else {
-                    code = (w[j >> 2] >> ((j & 3) * 8)) & 0xFF;
-                }
-                if (cellbase[j] >= 0) {
-                    const long long v = ((long long)g[j] << 16) + 1ll;
-                    atomicAdd(fc + (size_t)(cellbase[j] + code) * copies, (unsigned long long)v);
-                }
-            }
+        for (int q = 0; q < RPI / 4; ++q) {
+            const int4 gv = __ldg(gp + q);
+            g[q * 4 + 0] = gv.x;
+            g[q * 4 + 1] = gv.y;
+            g[q * 4 + 2] = gv.z;
+            g[q * 4 + 3] = gv.w;
         }
+    } else {
+#pragma unroll
+        for (int j = 0; j < RPI / 2; ++j) cb2[j] = 0xFFFFFFFFu;
+#pragma unroll
+        for (int j = 0; j < RPI; ++j) g[j] = 0;
     }
-    __syncthreads();
+    __syncthreads();  // s_frow
 
-    // flush: fold the copies, split the packed word, write [feature][node][era][bin]
-    const int out_cells = nf * cells_per_feat;
-    for (int i = threadIdx.x; i < out_cells; i += kHistThreads) {
-        const int fi = i / cells_per_feat;
-        const int rem = i - fi * cells_per_feat;
-        const int node = node_lo + rem / nb;
-        const int bin = rem - (rem / nb) * nb;
-        long long acc = 0;
-        const unsigned long long* src = cells + (size_t)i * copies;
-        for (int k = 0; k < copies; ++k) acc += (long long)src[k];
-        const uint32_t count = (uint32_t)(acc & 0xFFFF);
-        const long long gs = (acc - (long long)count) >> 16;
-        const size_t o = (((size_t)(f0 + fi) * a.node_stride + node) * a.n_eras + era) * nb + bin;
-        if (a.use_atomics) {
-            if (count) atomicAdd(a.cnt + o, count);
-            if (gs) atomicAdd(reinterpret_cast<unsigned long long*>(a.gsum + o), (unsigned long long)gs);
-        } else {
-            a.cnt[o] = count;
-            a.gsum[o] = gs;
+    uint4 cur = make_uint4(0, 0, 0, 0);
+    if (has && fa < fb) cur = __ldg(reinterpret_cast<const uint4*>(a.codes + (int64_t)s_frow[0] * a.pitch) + c);
+
+    for (int g0 = fa; g0 < fb; g0 += a.group) {
+        const int nf = min(a.group, fb - g0);
+        const int total_words = nf * cells_per_feat * copies * 2;
+        for (int i = threadIdx.x; i < total_words; i += blockDim.x) cells[i] = 0u;
+        __syncthreads();
+
+        for (int fi = 0; fi < nf; ++fi) {
+            uint4 nxt = make_uint4(0, 0, 0, 0);
+            const int fnext = g0 + fi + 1;
+            if (has && fnext < fb)
+                nxt = __ldg(reinterpret_cast<const uint4*>(a.codes + (int64_t)s_frow[fnext - fa] * a.pitch) + c);
+            if (has) {
+                const uint32_t w[4] = {cur.x, cur.y, cur.z, cur.w};
+                uint32_t* fc = cells + ((size_t)fi * cells_per_feat * copies + lane_copy) * 2;
+#pragma unroll
+                for (int j = 0; j < RPI; ++j) {
+                    int code;
+                    if (BITS == 4) {
+                        code = (w[j >> 3] >> ((j & 7) * 4)) & 0xF;
+                    } else {
+                        code = (w[j >> 2] >> ((j & 3) * 8)) & 0xFF;
+                    }
+                    const uint32_t base = (cb2[j >> 1] >> ((j & 1) * 16)) & 0xFFFFu;
+                    if (base != 0xFFFFu) {
+                        uint32_t* cell = fc + (size_t)(base + code) * copies * 2;
+                        atomicAdd(cell, (((uint32_t)g[j] & lo_mask) << CB) + 1u);
+                        atomicAdd(reinterpret_cast<int*>(cell) + 1, g[j] >> LB);
+                    }
+                }
+            }
+            cur = nxt;
         }
+        __syncthreads();
+
+        // flush: fold the copies, rebuild count and gradient sum, write [feature][node][era][bin]
+        const int out_cells = nf * cells_per_feat;
+        for (int i = threadIdx.x; i < out_cells; i += blockDim.x) {
+            const int fi = i / cells_per_feat;
+            const int rem = i - fi * cells_per_feat;
+            const int node = node_lo + rem / nb;
+            const int bin = rem - (rem / nb) * nb;
+            const uint32_t* src = cells + (size_t)i * copies * 2;
+            uint32_t count = 0;
+            long long lo_sum = 0, hi_sum = 0;
+            for (int k = 0; k < copies; ++k) {
+                const uint32_t A = src[2 * k];
+                count += A & ((1u << CB) - 1u);
+                lo_sum += (long long)(A >> CB);
+                hi_sum += (long long)(int32_t)src[2 * k + 1];
+            }
+            const long long gs = hi_sum * (1ll << LB) + lo_sum;
+            const size_t o = (((size_t)(g0 + fi) * a.node_stride + node) * a.n_eras + era) * nb + bin;
+            if (a.use_atomics) {
+                if (count) atomicAdd(a.cnt + o, count);
+                if (gs) atomicAdd(reinterpret_cast<unsigned long long*>(a.gsum + o), (unsigned long long)gs);
+            } else {
+                a.cnt[o] = count;
+                a.gsum[o] = gs;
+            }
+        }
+        __syncthreads();
     }
 }
 
@@ -171,16 +211,23 @@ int launch_hist(const HistLaunch& h, cudaStream_t stream) {
     a.node_stride = h.node_stride;
     a.cnt = h.cnt;
     a.gsum = h.gsum;
+    a.count_bits = h.count_bits;
+    a.lo_bits = h.lo_bits;
 
-    if (h.max_era_rows <= kSingleTileRows) {
+    const int rpi = (h.code_bits == 4) ? 32 : 16;
+    a.tile_rows = kTileRowsMax;
+    if (h.max_era_rows <= kTileRowsMax) {
         a.tiles_per_era = 1;
-        a.tile_rows = kSingleTileRows;
         a.use_atomics = 0;
     } else {
-        a.tile_rows = kSplitTileRows;
-        a.tiles_per_era = (h.max_era_rows + kSplitTileRows - 1) / kSplitTileRows;
+        a.tiles_per_era = (h.max_era_rows + kTileRowsMax - 1) / kTileRowsMax;
         a.use_atomics = 1;
     }
+    const int max_tile = (h.max_era_rows < kTileRowsMax) ? h.max_era_rows : kTileRowsMax;
+    int threads = (max_tile + rpi - 1) / rpi + 1;  // +1: a tile may straddle one extra chunk
+    threads = (threads + 31) / 32 * 32;
+    const int thread_cap = (h.code_bits == 4) ? 256 : 512;
+    if (threads > thread_cap) return fail_arg("histogram tile of %d rows exceeds the thread block", max_tile);
 
     // shared-memory plan: cells per feature, node chunks, feature group, copies
     const int64_t per_feat_all = (int64_t)h.n_nodes * h.max_bins;
@@ -191,10 +238,10 @@ int launch_hist(const HistLaunch& h, cudaStream_t stream) {
     }
     const int chunks = (h.n_nodes + nodes_per_chunk - 1) / nodes_per_chunk;
     const int64_t per_feat = (int64_t)nodes_per_chunk * h.max_bins;
+    if (per_feat > 65534) return fail_arg("node chunk too large");
     int copies = 1;
     while (copies < 32 && per_feat * copies * 2 <= 256) copies *= 2;
-    // keep a CTA near 32 KB of cells so that several CTAs share an SM
-    int group = (int)(4096 / (per_feat * copies));
+    int group = (int)(2048 / (per_feat * copies));
     if (group < 1) group = 1;
     if (group > kMaxGroup) group = kMaxGroup;
     if (group > h.n_feat) group = h.n_feat;
@@ -202,23 +249,33 @@ int launch_hist(const HistLaunch& h, cudaStream_t stream) {
     a.group = group;
     a.copies = copies;
 
-    const size_t smem = (size_t)group * per_feat * copies * sizeof(unsigned long long);
+    // feature ranges: enough CTAs for several waves, each amortising its row-state load
+    const int n_tiles = h.n_eras * a.tiles_per_era;
+    const int n_groups = (h.n_feat + group - 1) / group;
+    int split = (2400 + n_tiles * chunks - 1) / (n_tiles * chunks);
+    if (split < 1) split = 1;
+    if (split > n_groups) split = n_groups;
+    int feats_per_cta = ((n_groups + split - 1) / split) * group;
+    if (feats_per_cta > 256) feats_per_cta = 256 / group * group;
+    a.feats_per_cta = feats_per_cta;
+
+    const size_t smem = (size_t)group * per_feat * copies * 2 * sizeof(uint32_t);
     const size_t out_cells = (size_t)h.n_feat * h.node_stride * h.n_eras * h.max_bins;
     if (a.use_atomics) {
         PB_CUDA_TRY(cudaMemsetAsync(h.cnt, 0, out_cells * sizeof(uint32_t), stream));
         PB_CUDA_TRY(cudaMemsetAsync(h.gsum, 0, out_cells * sizeof(int64_t), stream));
     }
-    dim3 grid((unsigned)(h.n_eras * a.tiles_per_era), (unsigned)((h.n_feat + group - 1) / group), (unsigned)chunks);
+    dim3 grid((unsigned)n_tiles, (unsigned)((h.n_feat + feats_per_cta - 1) / feats_per_cta), (unsigned)chunks);
     if (grid.y > 65535u || grid.z > 65535u) return fail_arg("histogram grid too large");
     prof_begin(kProfHist, stream);
     if (h.code_bits == 4) {
         if (smem > 48 * 1024)
-            PB_CUDA_TRY(cudaFuncSetAttribute(hist_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        hist_kernel<4><<<grid, kHistThreads, smem, stream>>>(a);
+            PB_CUDA_TRY(cudaFuncSetAttribute(hist_kernel<4, 256>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        hist_kernel<4, 256><<<grid, threads, smem, stream>>>(a);
     } else {
         if (smem > 48 * 1024)
-            PB_CUDA_TRY(cudaFuncSetAttribute(hist_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        hist_kernel<8><<<grid, kHistThreads, smem, stream>>>(a);
+            PB_CUDA_TRY(cudaFuncSetAttribute(hist_kernel<8, 512>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        hist_kernel<8, 512><<<grid, threads, smem, stream>>>(a);
     }
     prof_end(kProfHist, stream);
     count_launch(1);

@@ -97,7 +97,7 @@ class PackedMatrix:
 
 
 def pack_feature_major(
-    X: np.ndarray,
+    X: np.ndarray | torch.Tensor,
     edges: np.ndarray | None,
     max_bins: int,
     *,
@@ -123,9 +123,17 @@ def pack_feature_major(
     edges_t = torch.from_numpy(np.ascontiguousarray(edges, dtype=np.float32)).to(dev) if is_f32 else None
     stream = torch.cuda.current_stream().cuda_stream
     src_dtype = np.float32 if is_f32 else np.uint8
+    on_device = isinstance(X, torch.Tensor)
+    order_t = None
+    if on_device and row_order is not None:
+        order_t = torch.from_numpy(np.ascontiguousarray(row_order, dtype=np.int64)).to(X.device)
     for a, b in _row_chunks(n_rows, n_feat * (4 if is_f32 else 1)):
-        rows = X[a:b] if row_order is None else X[row_order[a:b]]
-        chunk = torch.from_numpy(np.ascontiguousarray(rows, dtype=src_dtype)).to(dev, non_blocking=False)
+        if on_device:
+            rows = X[a:b] if order_t is None else X.index_select(0, order_t[a:b])
+            chunk = rows.to(device=dev, dtype=torch.float32 if is_f32 else torch.uint8).contiguous()
+        else:
+            rows = X[a:b] if row_order is None else X[row_order[a:b]]
+            chunk = torch.from_numpy(np.ascontiguousarray(rows, dtype=src_dtype)).to(dev, non_blocking=False)
         if is_f32:
             B.check(lib.pb_bin_pack_f32(chunk.data_ptr(), b - a, n_feat, a, edges_t.data_ptr(), edges_t.shape[0],
                                         max_bins, B._ptr(fmap_t), pm.codes.data_ptr(), pm.pitch, bits, stream))

@@ -50,7 +50,6 @@ def _hist_case(n, f, e, nb, n_nodes, seed, big_era=False):
     pm = pack_feature_major(codes, None, nb)
     npad = pm.rows_padded
     gq = np.zeros(npad, np.int32)
-    gq[:n] = rng.integers(-(1 << 30), 1 << 30, size=n)
     slot = np.full(npad, 0xFFFF, np.uint16)
     slot[:n] = rng.integers(0, n_nodes + 1, size=n)
     slot[:n][slot[:n] == n_nodes] = 0xFFFF      # some rows sit in finished leaves
@@ -71,6 +70,9 @@ def _hist_case(n, f, e, nb, n_nodes, seed, big_era=False):
     ws = torch.zeros(int(B.lib().pb_workspace_min_bytes(C.byref(st))) + 1024, dtype=torch.uint8, device=dev)
     st.ctl, st.workspace, st.workspace_bytes = ctl.data_ptr(), ws.data_ptr(), ws.numel()
     B.check(B.lib().pb_train_prepare(C.byref(st), era_off.ctypes.data))
+    lim = 1 << int(st.gq_bits)
+    gq[:n] = rng.integers(-lim, lim + 1, size=n)     # the full range the quantiser may produce
+    t["gq"].copy_(torch.from_numpy(gq))
     feat = rng.permutation(f)[: max(1, f // 2)].astype(np.int32)
     feat_t = torch.from_numpy(feat).to(dev)
     cnt = torch.full((feat.shape[0], n_nodes, e, nb), -1, dtype=torch.int32, device=dev)
@@ -97,7 +99,7 @@ def _hist_case(n, f, e, nb, n_nodes, seed, big_era=False):
 
 @pytest.mark.parametrize("n,f,e,nb,nodes", [
     (5000, 12, 7, 5, 1), (5000, 12, 7, 5, 32), (4097, 9, 3, 16, 4), (6000, 10, 5, 128, 8),
-    (3001, 6, 4, 200, 3), (20000, 5, 2, 64, 300), (1000, 3, 1, 2, 1),
+    (3001, 6, 4, 200, 3), (20000, 5, 2, 64, 300), (1000, 3, 1, 2, 1), (16000, 4, 2, 5, 2),
 ])
 def test_histogram_exact(n, f, e, nb, nodes):
     _hist_case(n, f, e, nb, nodes, seed=n + nb)
@@ -106,6 +108,7 @@ def test_histogram_exact(n, f, e, nb, nodes):
 def test_histogram_exact_when_an_era_spans_several_tiles():
     _hist_case(120_000, 6, 3, 5, 4, seed=5, big_era=True)
     _hist_case(90_000, 4, 1, 32, 2, seed=6)
+    _hist_case(30_000, 3, 2, 128, 40, seed=7)
 
 
 def test_legacy_predictors_match_oracle_router():
