@@ -1,0 +1,134 @@
+"""Host-side logic that needs no GPU: log replay, threshold lists, feature sharding (gloo)."""
+
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from oracle import packboost_oracle as po
+from packboost_b200 import sharding
+from packboost_b200.booster import _HEADER_DT, _WINNER_DT, _tree_from_log, even_cut_ids
+
+
+def test_log_dtypes_match_the_c_structs():
+    assert _WINNER_DT.itemsize == 80 and _HEADER_DT.itemsize == 88
+
+
+def test_even_cuts_match_oracle():
+    for nb in (4, 5, 16, 63, 128):
+        for k in (1, 2, 3, 7, 15, 200):
+            np.testing.assert_array_equal(even_cut_ids(nb, k), po.even_cuts(nb, k).numpy())
+
+
+def _log(rows, n_ctx, root=0.5, n_nodes=None, depth=3):
+    head = np.zeros(1, dtype=_HEADER_DT)[0]
+    head["root_value"] = root
+    for d, c in enumerate(n_ctx):
+        head["n_ctx"][d] = c
+    win = np.zeros((1 << depth) - 1, dtype=_WINNER_DT)
+    for (d, i), r in rows.items():
+        w = win[(1 << d) - 1 + i]
+        for k, v in r.items():
+            w[k] = v
+    head["n_tree_nodes"] = n_nodes
+    return head, win
+
+
+def test_tree_replay_numbers_children_like_the_reference():
+    # depth 0 splits the root; depth 1: first child splits, second has no usable candidate
+    rows = {
+        (0, 0): dict(feature=3, threshold=1, tree_node=0, left_id=1, right_id=2, left_value=-0.1, right_value=0.2),
+        (1, 0): dict(feature=5, threshold=0, tree_node=1, left_id=3, right_id=4, left_value=-0.3, right_value=0.4),
+        (1, 1): dict(feature=-1, threshold=-1, tree_node=2, left_id=-1, right_id=-1, left_value=0.25, right_value=0.25),
+    }
+    head, win = _log(rows, [1, 2, 0], n_nodes=5)
+    tree, n_ctx = _tree_from_log(head, win, 3)
+    assert n_ctx[:3] == [1, 2, 0]
+    sig = [(n.feature, n.threshold, n.left, n.right, n.is_leaf) for n in tree.nodes]
+    assert sig == [(3, 1, 1, 2, False), (5, 0, 3, 4, False), (-1, 0, -1, -1, True), (-1, 0, -1, -1, True),
+                   (-1, 0, -1, -1, True)]
+    assert [n.value for n in tree.nodes][2:] == [0.25, -0.3, 0.4]
+
+
+def test_tree_replay_detects_numbering_mismatch():
+    rows = {(0, 0): dict(feature=3, threshold=1, tree_node=0, left_id=2, right_id=3, left_value=0.0, right_value=0.0)}
+    head, win = _log(rows, [1, 0, 0], n_nodes=3)
+    with pytest.raises(RuntimeError):
+        _tree_from_log(head, win, 3)
+
+
+def test_root_only_tree():
+    head, win = _log({}, [0, 0, 0], root=-1.5, n_nodes=1)
+    tree, n_ctx = _tree_from_log(head, win, 3)
+    assert len(tree.nodes) == 1 and tree.nodes[0].is_leaf and tree.nodes[0].value == -1.5
+
+
+def test_feature_map_and_local_part_partition_the_features():
+    F, world = 37, 4
+    seen = np.zeros(F, dtype=int)
+    for r in range(world):
+        m = sharding.feature_map(F, r, world)
+        own = np.nonzero(m >= 0)[0]
+        assert np.array_equal(m[own], own // world)
+        seen[own] += 1
+    assert np.all(seen == 1)
+    subset = np.random.default_rng(0).permutation(F)[:11].astype(np.int32)
+    pos_all = []
+    for r in range(world):
+        rows, pos = sharding.local_part(subset, r, world)
+        assert np.array_equal(rows, subset[pos] // world) and np.all(subset[pos] % world == r)
+        pos_all.append(pos)
+    assert np.array_equal(np.sort(np.concatenate(pos_all)), np.arange(11))
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _worker(rank, world, port, out):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    rng = np.random.default_rng(5)                       # same seed on every rank
+    F, nodes, n_rows = 23, 4, 1000
+    subset = rng.permutation(F)[:9].astype(np.int32)
+    full = rng.integers(1, 1 << 30, size=(subset.shape[0], nodes, 6)).astype(np.int32)   # 24-byte records
+    # each rank fills the records of the features it holds; the others stay zero
+    table = np.zeros_like(full)
+    _, pos = sharding.local_part(subset, rank, world)
+    table[pos] = full[pos]
+    t = torch.from_numpy(table)
+    dist.all_reduce(t, op=dist.ReduceOp.SUM)
+    ok1 = np.array_equal(t.numpy(), full)
+    # go-left bits: the owner of each node's winning feature sets the bits of that node's rows
+    node_of = rng.integers(0, nodes, size=n_rows)
+    win_feat = subset[rng.integers(0, subset.shape[0], size=nodes)]
+    go_left = rng.integers(0, 2, size=n_rows).astype(bool)
+    mine = (win_feat[node_of] % world == rank) & go_left
+    bits = np.packbits(mine, bitorder="little")
+    bits = np.pad(bits, (0, (-len(bits)) % 4)).view(np.int32).copy()
+    tb = torch.from_numpy(bits)
+    dist.all_reduce(tb, op=dist.ReduceOp.SUM)
+    want = np.packbits(go_left, bitorder="little")
+    want = np.pad(want, (0, (-len(want)) % 4)).view(np.int32)
+    ok2 = np.array_equal(tb.numpy(), want)
+    out[rank] = int(ok1 and ok2)
+    dist.destroy_process_group()
+
+
+def test_two_rank_exchange_merges_disjoint_tables_and_bitmasks():
+    """The per-depth exchange of the feature-sharded path on CPU ranks (gloo, world size 2):
+    a SUM all-reduce over int32 words merges disjoint candidate records exactly, and a SUM of
+    disjoint go-left bit words equals their OR."""
+    world = 2
+    out = mp.Manager().dict()
+    mp.spawn(_worker, args=(world, _free_port(), out), nprocs=world, join=True)
+    assert [out[r] for r in range(world)] == [1, 1]
