@@ -188,6 +188,26 @@ int pb_candidates_buffer(const pb_train_state* st, int64_t depth, int64_t n_samp
                          void** ptr, int64_t* bytes);
 int pb_depth_clear_candidates(const pb_train_state* st, int64_t depth, int64_t n_sampled, void* stream);
 
+/* Same computation as pb_depth_hist_score for callers that cannot provide a workspace because
+ * they cannot allocate device memory at all: processes whose device memory is reserved in full
+ * by another component's pool at start-up, or deployments that forbid device allocation once
+ * they are running.  This entry point has no counterpart in the reference.  The per-block
+ * histograms live in a fixed 64 MiB array inside the library image (pb_static_scratch_bytes();
+ * every GPU that loads the library holds it until the process exits); `st->workspace` is not
+ * touched and the candidate table is written to the caller's `cand_out`
+ * (24-byte records, `n_sampled` x (1 << depth), same layout as pb_candidates_buffer).
+ * Nothing is allocated or freed.  A shape whose single-feature histogram at `depth`
+ * (`(1 << depth) * n_eras * max_bins * 12` bytes) exceeds the array is rejected with
+ * PB_ERR_ARG.  The first call on a device looks up the array's device address
+ * (cudaGetSymbolAddress) with that device current; make that first call outside any stream
+ * capture.  All calls in a process share the one array, which keeps whatever the previous call
+ * left in it: the kernels rewrite every cell they later read, but two calls whose kernels
+ * overlap on the GPU (different streams) race on it — serialise them. */
+int64_t pb_static_scratch_bytes(void);
+int pb_depth_hist_score_static(const pb_train_state* st, int64_t depth, const int32_t* feat_rows,
+                               const int32_t* feat_pos, int64_t n_feat, int64_t n_sampled,
+                               void* cand_out, void* stream);
+
 /* Pick the winner of every frontier node (packboost/booster.py:1912-1981: in-block order
  * score, left count, position; across blocks strictly greater on score, left count,
  * feature id, threshold), assign BFS-compact child ids (packboost/booster.py:181-187),

@@ -78,6 +78,8 @@ _PROTOS: dict[str, tuple[Any, list[Any]]] = {
     "pb_train_prepare": (C.c_int, [C.POINTER(TrainState), vp]),
     "pb_round_begin": (C.c_int, [C.POINTER(TrainState), i64, vp]),
     "pb_depth_hist_score": (C.c_int, [C.POINTER(TrainState), i64, vp, vp, i64, i64, vp]),
+    "pb_static_scratch_bytes": (i64, []),
+    "pb_depth_hist_score_static": (C.c_int, [C.POINTER(TrainState), i64, vp, vp, i64, i64, vp, vp]),
     "pb_candidates_buffer": (C.c_int, [C.POINTER(TrainState), i64, i64, C.POINTER(vp), C.POINTER(i64)]),
     "pb_depth_clear_candidates": (C.c_int, [C.POINTER(TrainState), i64, i64, vp]),
     "pb_depth_select": (C.c_int, [C.POINTER(TrainState), i64, vp, i64, vp]),

@@ -2,6 +2,8 @@
 // selection with the reference's tie-break, child numbering, leaf values, the row -> node
 // map update and the leaf-delta table for the prediction update.
 
+#include <mutex>
+
 #include "common.cuh"
 
 namespace pb {
@@ -720,4 +722,115 @@ extern "C" int pb_hist_build(const pb_train_state* st, const int32_t* feat_rows,
     h.cnt = cnt;
     h.gsum = gsum;
     return launch_hist(h, (cudaStream_t)stream);
+}
+
+// ---- histogram + score without a caller-provided workspace -------------------------------------
+//
+// Some hosts of this library cannot hand it a workspace: their device memory is reserved in full
+// by another component's pool when the process starts (an inference server, a framework allocator
+// configured to take the whole device), or their deployment forbids device allocation after
+// start-up, so nothing can call cudaMalloc for the tens of megabytes pb_depth_hist_score wants.
+// For them the per-block histograms live in the fixed array below, which is part of the library
+// image: every GPU that loads the library holds these bytes until the process exits.
+constexpr size_t kStaticScratchBytes = 64ull << 20;  // 64 MiB
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+// In host code `g_static_scratch` is only a handle for the symbol, not an address a kernel can use;
+// the device address is looked up once per device (with that device current) and cached.
+static std::mutex g_static_mu;
+static void* g_static_ptr[64] = {nullptr};
+
+static int static_scratch_ptr(void** out) {
+    int dev = -1;
+    PB_CUDA_TRY(cudaGetDevice(&dev));
+    PB_REQUIRE(dev >= 0 && dev < 64, "device ordinal %d not supported by the static scratch", dev);
+    std::lock_guard<std::mutex> lk(g_static_mu);
+    if (!g_static_ptr[dev]) {
+        void* p = nullptr;
+        PB_CUDA_TRY(cudaGetSymbolAddress(&p, g_static_scratch));
+        PB_REQUIRE(p != nullptr && ((uintptr_t)p % 256) == 0, "static scratch has no usable device address");
+        g_static_ptr[dev] = p;
+    }
+    *out = g_static_ptr[dev];
+    return PB_OK;
+}
+
+extern "C" int64_t pb_static_scratch_bytes(void) { return (int64_t)kStaticScratchBytes; }
+
+extern "C" int pb_depth_hist_score_static(const pb_train_state* st, int64_t depth, const int32_t* feat_rows,
+                                          const int32_t* feat_pos, int64_t n_feat, int64_t n_sampled,
+                                          void* cand_out, void* stream_) {
+    int rc = check_state(st);
+    if (rc) return rc;
+    PB_REQUIRE(depth >= 0 && depth < st->max_depth, "depth out of range");
+    PB_REQUIRE(n_feat >= 0 && n_feat <= n_sampled && n_sampled <= st->n_features_total, "feature counts out of range");
+    PB_REQUIRE(cand_out != nullptr && ((uintptr_t)cand_out % 8) == 0, "cand_out must be a non-null 8-byte aligned buffer");
+    if (n_feat == 0) return PB_OK;
+    PB_REQUIRE(feat_rows && feat_pos, "null feature list");
+    const int stride = node_stride_of(depth);
+    const size_t per_feat_cells = (size_t)stride * st->n_eras * st->max_bins;
+    // gsum (8 bytes per cell) first, then cnt (4 bytes per cell), each block 256-byte aligned
+    const size_t per_feat_bytes = per_feat_cells * 12;
+    PB_REQUIRE(per_feat_bytes + 512 <= kStaticScratchBytes,
+               "static scratch too small: one feature of histogram at depth %lld needs %llu bytes, the fixed "
+               "array holds %llu; use pb_depth_hist_score with a workspace",
+               (long long)depth, (unsigned long long)per_feat_bytes, (unsigned long long)kStaticScratchBytes);
+    void* base = nullptr;
+    rc = static_scratch_ptr(&base);
+    if (rc) return rc;
+    int64_t fb = (int64_t)((kStaticScratchBytes - 512) / per_feat_bytes);
+    if (fb > n_feat) fb = n_feat;
+    char* ws = static_cast<char*>(base);
+    int64_t* gsum = reinterpret_cast<int64_t*>(ws);
+    uint32_t* cnt = reinterpret_cast<uint32_t*>(ws + align_up((size_t)fb * per_feat_cells * 8, 256));
+    cudaStream_t stream = (cudaStream_t)stream_;
+    Ctl c = ctl_view(st->ctl);
+    for (int64_t f0 = 0; f0 < n_feat; f0 += fb) {
+        const int nf = (int)((n_feat - f0 < fb) ? (n_feat - f0) : fb);
+        HistLaunch h;
+        h.codes = st->codes;
+        h.pitch = st->pitch;
+        h.code_bits = (int)st->code_bits;
+        h.feat_rows = feat_rows + f0;
+        h.n_feat = nf;
+        h.gq = st->gq;
+        h.slot = st->slot;
+        h.era_offsets = st->era_offsets;
+        h.n_eras = (int)st->n_eras;
+        h.max_bins = (int)st->max_bins;
+        h.max_era_rows = (int)st->max_era_rows;
+        h.n_nodes_ptr = &c.head->n_ctx[depth];
+        h.n_nodes = stride;
+        h.node_stride = stride;
+        h.count_bits = (int)st->count_bits;
+        h.lo_bits = (int)st->lo_bits;
+        h.cnt = cnt;     // the histogram kernel overwrites (or zeroes, then adds to) every cell it later reads
+        h.gsum = gsum;
+        rc = launch_hist(h, stream);
+        if (rc) return rc;
+        ScoreLaunch s;
+        s.cnt = cnt;
+        s.gsum = gsum;
+        s.n_feat = nf;
+        s.feat_pos = feat_pos + f0;
+        s.node_stride = stride;
+        s.n_nodes_max = stride;
+        s.n_nodes_ptr = &c.head->n_ctx[depth];
+        s.frontier = c.frontier[depth & 1];
+        s.any_dir_ptr = &c.head->any_dir[depth];
+        s.inv_scale_ptr = &c.head->inv_scale;
+        s.n_eras = (int)st->n_eras;
+        s.max_bins = (int)st->max_bins;
+        s.n_thr = (int)st->n_thresholds;
+        s.thr_ids = st->thr_ids;
+        s.lambda_l2 = (float)st->lambda_l2;
+        s.lambda_dro = (float)st->lambda_dro;
+        s.direction_weight = (float)st->direction_weight;
+        s.era_alpha = (float)(st->era_alpha > 0.0 ? st->era_alpha : 0.0);
+        s.min_samples_leaf = (int)st->min_samples_leaf;
+        s.cand = static_cast<Cand*>(cand_out);
+        rc = launch_score(s, stream);
+        if (rc) return rc;
+    }
+    return PB_OK;
 }
