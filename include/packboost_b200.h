@@ -28,7 +28,7 @@
  *              active nodes) or 0xFFFF when the row sits in a finished leaf.
  *  leaf        uint16 id of the tree node the row currently sits in (BFS-compact ids: a
  *              split appends `left = n_nodes, right = n_nodes + 1`).
- *  histograms  `cnt` uint32 and `gsum` int64, both `[feature][node][era][bin]`.
+ *  histograms  `cnt` uint32 and `gsum` int64, both `[feature][era][node][bin]`.
  */
 #ifndef PACKBOOST_B200_H
 #define PACKBOOST_B200_H
@@ -271,7 +271,7 @@ typedef struct pb_round_log_header {
 
 /* Histogram pass alone (packboost/booster.py:933-977, counts and gradient sums; the
  * hessian of the squared loss is 1, so its histogram is the count).  Output layout
- * `[n_feat][node_stride][n_eras][max_bins]`. `n_nodes` frontier slots are accumulated. */
+ * `[n_feat][n_eras][node_stride][max_bins]`. `n_nodes` frontier slots are accumulated. */
 int pb_hist_build(const pb_train_state* st, const int32_t* feat_rows, int64_t n_feat,
                   int64_t n_nodes, int64_t node_stride, uint32_t* cnt, int64_t* gsum, void* stream);
 

@@ -564,6 +564,7 @@ extern "C" int pb_depth_hist_score(const pb_train_state* st, int64_t depth, cons
         h.node_stride = stride;
         h.count_bits = (int)st->count_bits;
         h.lo_bits = (int)st->lo_bits;
+        h.max_arity = hist_max_arity();
         h.cnt = cnt;
         h.gsum = gsum;
         rc = launch_hist(h, stream);
@@ -719,6 +720,7 @@ extern "C" int pb_hist_build(const pb_train_state* st, const int32_t* feat_rows,
     h.node_stride = (int)node_stride;
     h.count_bits = (int)st->count_bits;
     h.lo_bits = (int)st->lo_bits;
+    h.max_arity = hist_max_arity();
     h.cnt = cnt;
     h.gsum = gsum;
     return launch_hist(h, (cudaStream_t)stream);
@@ -804,6 +806,7 @@ extern "C" int pb_depth_hist_score_static(const pb_train_state* st, int64_t dept
         h.node_stride = stride;
         h.count_bits = (int)st->count_bits;
         h.lo_bits = (int)st->lo_bits;
+        h.max_arity = hist_max_arity();
         h.cnt = cnt;     // the histogram kernel overwrites (or zeroes, then adds to) every cell it later reads
         h.gsum = gsum;
         rc = launch_hist(h, stream);

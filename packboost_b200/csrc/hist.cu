@@ -16,8 +16,21 @@
 //   B = sum of hi                        hi = gq >> LB (arithmetic)
 // With fewer than 2^CB rows per tile, LB = 32 - 2*CB and |gq| <= 2^(63 - 3*CB) (capped at
 // 2^30) neither word can overflow; pb_train_prepare derives CB/LB and the gradient scale from
-// the largest tile.  When a feature has few cells they are replicated ("copies") so that the
-// lanes of a warp rarely hit the same address.
+// the largest tile.
+//
+// Two kernels share that cell format:
+//  * hist_lane_kernel (few cells per feature: nodes * bins^A <= kLaneCellsMax): a lane owns a
+//    tuple of A features and a private column of cells (bank == lane, so the shared atomics of a
+//    warp never conflict); all lanes of a warp walk the same rows, whose state (cell base, word A,
+//    word B) is staged per warp and read with one broadcast load.  With A > 1 the cell index is
+//    the joint code of the tuple, one pair of atomics serves A features, and the per-feature
+//    histograms are the marginals of the joint table, taken when the tile is flushed.
+//  * hist_kernel (everything else): lanes own 16-byte chunks of rows of one feature; cells of a
+//    feature are shared by the CTA and, when few, replicated ("copies") to thin out conflicts.
+//
+// Output layout: [feature][era][node_stride][bin] for both arrays.
+
+#include <stdlib.h>
 
 #include "common.cuh"
 
@@ -57,7 +70,7 @@ struct HistKernelArgs {
 template <int BITS, int THREADS>
 __global__ void __launch_bounds__(THREADS) hist_kernel(HistKernelArgs a) {
     constexpr int RPI = (BITS == 4) ? 32 : 16;  // rows per thread (16 bytes of codes)
-    extern __shared__ uint32_t cells[];         // [group][cells_per_feat][copies][2]
+    extern __shared__ uint32_t cells[];         // word A plane [group][cells_per_feat][copies], then word B plane
     __shared__ int s_frow[256];
 
     const int n_nodes = a.n_nodes_ptr ? min(*a.n_nodes_ptr, a.n_nodes) : a.n_nodes;
@@ -130,8 +143,12 @@ __global__ void __launch_bounds__(THREADS) hist_kernel(HistKernelArgs a) {
 
     for (int g0 = fa; g0 < fb; g0 += a.group) {
         const int nf = min(a.group, fb - g0);
-        const int total_words = nf * cells_per_feat * copies * 2;
-        for (int i = threadIdx.x; i < total_words; i += blockDim.x) cells[i] = 0u;
+        const int plane = a.group * cells_per_feat * copies;  // words per plane
+        const int total_words = nf * cells_per_feat * copies;
+        for (int i = threadIdx.x; i < total_words; i += blockDim.x) {
+            cells[i] = 0u;
+            cells[plane + i] = 0u;
+        }
         __syncthreads();
 
         for (int fi = 0; fi < nf; ++fi) {
@@ -141,7 +158,7 @@ __global__ void __launch_bounds__(THREADS) hist_kernel(HistKernelArgs a) {
                 nxt = __ldg(reinterpret_cast<const uint4*>(a.codes + (int64_t)s_frow[fnext - fa] * a.pitch) + c);
             if (has) {
                 const uint32_t w[4] = {cur.x, cur.y, cur.z, cur.w};
-                uint32_t* fc = cells + ((size_t)fi * cells_per_feat * copies + lane_copy) * 2;
+                uint32_t* fc = cells + (size_t)fi * cells_per_feat * copies + lane_copy;
 #pragma unroll
                 for (int j = 0; j < RPI; ++j) {
                     int code;
@@ -152,9 +169,9 @@ __global__ void __launch_bounds__(THREADS) hist_kernel(HistKernelArgs a) {
                     }
                     const uint32_t base = (cb2[j >> 1] >> ((j & 1) * 16)) & 0xFFFFu;
                     if (base != 0xFFFFu) {
-                        uint32_t* cell = fc + (size_t)(base + code) * copies * 2;
+                        uint32_t* cell = fc + (size_t)(base + code) * copies;
                         atomicAdd(cell, (((uint32_t)g[j] & lo_mask) << CB) + 1u);
-                        atomicAdd(reinterpret_cast<int*>(cell) + 1, g[j] >> LB);
+                        atomicAdd(reinterpret_cast<int*>(cell + plane), g[j] >> LB);
                     }
                 }
             }
@@ -162,24 +179,24 @@ __global__ void __launch_bounds__(THREADS) hist_kernel(HistKernelArgs a) {
         }
         __syncthreads();
 
-        // flush: fold the copies, rebuild count and gradient sum, write [feature][node][era][bin]
+        // flush: fold the copies, rebuild count and gradient sum, write [feature][era][node][bin]
         const int out_cells = nf * cells_per_feat;
         for (int i = threadIdx.x; i < out_cells; i += blockDim.x) {
             const int fi = i / cells_per_feat;
             const int rem = i - fi * cells_per_feat;
             const int node = node_lo + rem / nb;
             const int bin = rem - (rem / nb) * nb;
-            const uint32_t* src = cells + (size_t)i * copies * 2;
+            const uint32_t* src = cells + (size_t)i * copies;
             uint32_t count = 0;
             long long lo_sum = 0, hi_sum = 0;
             for (int k = 0; k < copies; ++k) {
-                const uint32_t A = src[2 * k];
+                const uint32_t A = src[k];
                 count += A & ((1u << CB) - 1u);
                 lo_sum += (long long)(A >> CB);
-                hi_sum += (long long)(int32_t)src[2 * k + 1];
+                hi_sum += (long long)(int32_t)src[plane + k];
             }
             const long long gs = hi_sum * (1ll << LB) + lo_sum;
-            const size_t o = (((size_t)(g0 + fi) * a.node_stride + node) * a.n_eras + era) * nb + bin;
+            const size_t o = (((size_t)(g0 + fi) * a.n_eras + era) * a.node_stride + node) * nb + bin;
             if (a.use_atomics) {
                 if (count) atomicAdd(a.cnt + o, count);
                 if (gs) atomicAdd(reinterpret_cast<unsigned long long*>(a.gsum + o), (unsigned long long)gs);
@@ -192,7 +209,188 @@ __global__ void __launch_bounds__(THREADS) hist_kernel(HistKernelArgs a) {
     }
 }
 
+
+// ---- lane-private kernel for small cell counts ------------------------------------------------
+
+constexpr int kLaneCellBytes = 256;        // word A of lane l at l*4, word B at 128 + l*4: bank == lane
+constexpr int kLaneSmemMax = 64 * 1024;    // cells of one CTA
+constexpr int kLaneWarps = 8;
+constexpr int kLaneRows = 64;              // rows per warp step: 32 bytes of 4-bit codes per feature
+
+// All lanes of a warp walk the same rows, so the row state is warp-uniform.  It is staged per
+// warp, two rows per 16-byte record {cell base of both rows (16 bits each, 0xFFFF: skip), gq of
+// row 0, gq of row 1, unused}: one broadcast shared load serves two row steps.  The codes and
+// the raw row state of the warp's next chunk are loaded while the current chunk is accumulated.
+template <int A>
+__global__ void __launch_bounds__(kLaneWarps * 32, 3) hist_lane_kernel(HistKernelArgs a) {
+    extern __shared__ __align__(16) unsigned char smb[];  // cells | staging [warps][32] uint4
+    const int n_nodes = a.n_nodes_ptr ? min(*a.n_nodes_ptr, a.n_nodes) : a.n_nodes;
+    if (n_nodes <= 0) return;
+    const int era = blockIdx.x / a.tiles_per_era;
+    const int tile = blockIdx.x - era * a.tiles_per_era;
+    const int era_begin = a.era_offsets[era];
+    const int era_end = a.era_offsets[era + 1];
+    const int r0 = era_begin + tile * a.tile_rows;
+    const int r1 = min(era_end, r0 + a.tile_rows);
+    if (r0 >= r1 && a.use_atomics) return;
+
+    const int nb = a.max_bins;
+    int cpn = nb;  // cells per node = bins^A
+#pragma unroll
+    for (int i = 1; i < A; ++i) cpn *= nb;
+    const int n_cells = a.n_nodes * cpn;  // sized for the upper bound of nodes
+    uint32_t* cells = reinterpret_cast<uint32_t*>(smb);
+    uint4* staging = reinterpret_cast<uint4*>(smb + (size_t)n_cells * kLaneCellBytes);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int CB = a.count_bits, LB = a.lo_bits;
+    const uint32_t lo_mask = (1u << LB) - 1u;
+
+    for (int i = threadIdx.x; i < n_cells * 64; i += blockDim.x) cells[i] = 0u;
+
+    // features of this lane's tuple
+    const int tuple = blockIdx.y * 32 + lane;
+    int n_mine = a.n_feat - tuple * A;
+    n_mine = max(0, min(A, n_mine));
+    const uint8_t* frow[A];
+#pragma unroll
+    for (int i = 0; i < A; ++i)
+        frow[i] = a.codes + (int64_t)__ldg(a.feat_rows + min(tuple * A + i, a.n_feat - 1)) * a.pitch;
+    __syncthreads();
+
+    unsigned char* lane_base = smb + lane * 4;
+    uint4* st = staging + warp * (kLaneRows / 2);
+    const int c0 = r0 / kLaneRows, c1 = (r1 + kLaneRows - 1) / kLaneRows;
+
+    uint32_t w[A][8];
+    int raw_s[2], raw_g[2];
+    auto load_chunk = [&](int c, uint32_t (&ww)[A][8], int (&rs)[2], int (&rg)[2]) {
+        // lane l takes rows 2l and 2l+1 of the chunk: they share one staged record
+        const int r = c * kLaneRows + 2 * lane;
+        const uint32_t sv = *reinterpret_cast<const uint32_t*>(a.slot + r);
+        const int2 gv = *reinterpret_cast<const int2*>(a.gq + r);
+        rs[0] = sv & 0xFFFF;
+        rs[1] = sv >> 16;
+        rg[0] = gv.x;
+        rg[1] = gv.y;
+#pragma unroll
+        for (int i = 0; i < A; ++i) {
+            const uint4* p = reinterpret_cast<const uint4*>(frow[i] + (int64_t)c * (kLaneRows / 2));
+            const uint4 v0 = __ldg(p), v1 = __ldg(p + 1);
+            ww[i][0] = v0.x; ww[i][1] = v0.y; ww[i][2] = v0.z; ww[i][3] = v0.w;
+            ww[i][4] = v1.x; ww[i][5] = v1.y; ww[i][6] = v1.z; ww[i][7] = v1.w;
+        }
+    };
+    int c = c0 + warp;
+    if (c < c1) load_chunk(c, w, raw_s, raw_g);
+    for (; c < c1; c += kLaneWarps) {
+        {
+            uint4 rec;
+            uint32_t cb[2];
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const int r = c * kLaneRows + 2 * lane + h;
+                const bool ok = (r >= r0) & (r < r1) & (raw_s[h] < n_nodes);
+                cb[h] = ok ? (uint32_t)(raw_s[h] * cpn) : 0xFFFFu;
+            }
+            rec.x = cb[0] | (cb[1] << 16);
+            rec.y = (uint32_t)raw_g[0];
+            rec.z = (uint32_t)raw_g[1];
+            rec.w = 0u;
+            st[lane] = rec;
+        }
+        __syncwarp();
+        uint32_t wn[A][8];
+        int nraw_s[2], nraw_g[2];
+        const int cn = c + kLaneWarps;
+        if (cn < c1) load_chunk(cn, wn, nraw_s, nraw_g);
+        if (n_mine > 0) {
+#pragma unroll
+            for (int jb = 0; jb < kLaneRows; jb += 4) {
+                uint4 rec[2];
+                rec[0] = st[jb >> 1];  // every lane reads the same record: a broadcast load
+                rec[1] = st[(jb >> 1) + 1];
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const int j = jb + q;
+                    const uint32_t cbase = (rec[q >> 1].x >> ((q & 1) * 16)) & 0xFFFFu;
+                    if (cbase != 0xFFFFu) {
+                        const int g = (int)((q & 1) ? rec[q >> 1].z : rec[q >> 1].y);
+                        // joint code of the tuple
+                        const int bit = (j & 7) * 4;
+                        uint32_t idx = (w[0][j >> 3] >> bit) & 0xFu;
+                        int mul = nb;
+#pragma unroll
+                        for (int i = 1; i < A; ++i) {
+                            idx += (uint32_t)mul * ((w[i][j >> 3] >> bit) & 0xFu);
+                            mul *= nb;
+                        }
+                        unsigned char* cell = lane_base + (cbase + idx) * kLaneCellBytes;
+                        atomicAdd(reinterpret_cast<uint32_t*>(cell), (((uint32_t)g & lo_mask) << CB) + 1u);
+                        atomicAdd(reinterpret_cast<int*>(cell + 128), g >> LB);
+                    }
+                }
+            }
+        }
+        __syncwarp();
+        if (cn < c1) {
+#pragma unroll
+            for (int i = 0; i < A; ++i)
+#pragma unroll
+                for (int q = 0; q < 8; ++q) w[i][q] = wn[i][q];
+            raw_s[0] = nraw_s[0]; raw_s[1] = nraw_s[1];
+            raw_g[0] = nraw_g[0]; raw_g[1] = nraw_g[1];
+        }
+    }
+    __syncthreads();
+
+    // flush: marginals of this lane's joint table -> [feature][era][node][bin]
+    const uint32_t cmask = (1u << CB) - 1u;
+    for (int item = warp; item < n_nodes * A; item += kLaneWarps) {
+        const int n = item / A, fi = item - n * A;
+        if (fi >= n_mine) continue;
+        int below = 1;  // bins^fi
+        for (int i = 0; i < fi; ++i) below *= nb;
+        const int above = cpn / (below * nb);
+        for (int b = 0; b < nb; ++b) {
+            uint32_t count = 0;
+            long long lo_sum = 0, hi_sum = 0;
+            for (int hi = 0; hi < above; ++hi)
+                for (int lo = 0; lo < below; ++lo) {
+                    const uint32_t cell = (uint32_t)(n * cpn + (hi * nb + b) * below + lo) * 64u + lane;
+                    const uint32_t Aw = cells[cell];
+                    count += Aw & cmask;
+                    lo_sum += (long long)(Aw >> CB);
+                    hi_sum += (long long)(int32_t)cells[cell + 32];
+                }
+            const long long gs = hi_sum * (1ll << LB) + lo_sum;
+            const size_t o = (((size_t)(tuple * A + fi) * a.n_eras + era) * a.node_stride + n) * nb + b;
+            if (a.use_atomics) {
+                if (count) atomicAdd(a.cnt + o, count);
+                if (gs) atomicAdd(reinterpret_cast<unsigned long long*>(a.gsum + o), (unsigned long long)gs);
+            } else {
+                a.cnt[o] = count;
+                a.gsum[o] = gs;
+            }
+        }
+    }
+}
+
+template <int A>
+int launch_lane(const HistKernelArgs& a, int n_tuples, size_t smem, cudaStream_t stream) {
+    if (smem > 48 * 1024)
+        PB_CUDA_TRY(cudaFuncSetAttribute(hist_lane_kernel<A>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    dim3 grid((unsigned)(a.n_eras * a.tiles_per_era), (unsigned)((n_tuples + 31) / 32), 1);
+    hist_lane_kernel<A><<<grid, kLaneWarps * 32, smem, stream>>>(a);
+    return PB_OK;
+}
+
 }  // namespace
+
+int hist_max_arity() {
+    const char* e = getenv("PACKBOOST_HIST_MAX_ARITY");
+    if (e && e[0] >= '1' && e[0] <= '3' && e[1] == 0) return e[0] - '0';
+    return 2;
+}
 
 int launch_hist(const HistLaunch& h, cudaStream_t stream) {
     if (h.n_feat <= 0 || h.n_nodes <= 0) return PB_OK;
@@ -229,6 +427,40 @@ int launch_hist(const HistLaunch& h, cudaStream_t stream) {
     const int thread_cap = (h.code_bits == 4) ? 256 : 512;
     if (threads > thread_cap) return fail_arg("histogram tile of %d rows exceeds the thread block", max_tile);
 
+    const size_t out_cells = (size_t)h.n_feat * h.node_stride * h.n_eras * h.max_bins;
+    if (a.use_atomics) {
+        PB_CUDA_TRY(cudaMemsetAsync(h.cnt, 0, out_cells * sizeof(uint32_t), stream));
+        PB_CUDA_TRY(cudaMemsetAsync(h.gsum, 0, out_cells * sizeof(int64_t), stream));
+    }
+
+    // lane-private kernel when a lane's cells are few: the largest tuple size (joint code of up
+    // to `max_arity` features) whose cells fit one CTA
+    if (h.code_bits == 4 && (int64_t)h.n_nodes * h.max_bins * kLaneCellBytes <= kLaneSmemMax &&
+        (int64_t)h.n_nodes * h.max_bins <= 0xFFFE) {
+        int arity = 1;
+        int64_t cpn = h.max_bins;
+        while (arity < h.max_arity && (int64_t)h.n_nodes * cpn * h.max_bins * kLaneCellBytes <= kLaneSmemMax &&
+               (int64_t)h.n_nodes * cpn * h.max_bins <= 0xFFFE) {
+            cpn *= h.max_bins;
+            ++arity;
+        }
+        a.nodes_per_chunk = h.n_nodes;
+        a.feats_per_cta = 32 * arity;
+        a.group = arity;
+        a.copies = 1;
+        const int n_tuples = (h.n_feat + arity - 1) / arity;
+        const size_t smem = (size_t)h.n_nodes * cpn * kLaneCellBytes + (size_t)kLaneWarps * (kLaneRows / 2) * sizeof(uint4);
+        prof_begin(kProfHist, stream);
+        const int rc = (arity == 3) ? launch_lane<3>(a, n_tuples, smem, stream)
+                       : (arity == 2) ? launch_lane<2>(a, n_tuples, smem, stream)
+                                      : launch_lane<1>(a, n_tuples, smem, stream);
+        prof_end(kProfHist, stream);
+        if (rc) return rc;
+        count_launch(1);
+        PB_LAUNCH_CHECK("hist_lane_kernel");
+        return PB_OK;
+    }
+
     // shared-memory plan: cells per feature, node chunks, feature group, copies
     const int64_t per_feat_all = (int64_t)h.n_nodes * h.max_bins;
     int nodes_per_chunk = h.n_nodes;
@@ -240,7 +472,7 @@ int launch_hist(const HistLaunch& h, cudaStream_t stream) {
     const int64_t per_feat = (int64_t)nodes_per_chunk * h.max_bins;
     if (per_feat > 65534) return fail_arg("node chunk too large");
     int copies = 1;
-    while (copies < 32 && per_feat * copies * 2 <= 256) copies *= 2;
+    while (copies < 32 && per_feat * copies * 2 <= 512) copies *= 2;
     int group = (int)(2048 / (per_feat * copies));
     if (group < 1) group = 1;
     if (group > kMaxGroup) group = kMaxGroup;
@@ -260,11 +492,6 @@ int launch_hist(const HistLaunch& h, cudaStream_t stream) {
     a.feats_per_cta = feats_per_cta;
 
     const size_t smem = (size_t)group * per_feat * copies * 2 * sizeof(uint32_t);
-    const size_t out_cells = (size_t)h.n_feat * h.node_stride * h.n_eras * h.max_bins;
-    if (a.use_atomics) {
-        PB_CUDA_TRY(cudaMemsetAsync(h.cnt, 0, out_cells * sizeof(uint32_t), stream));
-        PB_CUDA_TRY(cudaMemsetAsync(h.gsum, 0, out_cells * sizeof(int64_t), stream));
-    }
     dim3 grid((unsigned)n_tiles, (unsigned)((h.n_feat + feats_per_cta - 1) / feats_per_cta), (unsigned)chunks);
     if (grid.y > 65535u || grid.z > 65535u) return fail_arg("histogram grid too large");
     prof_begin(kProfHist, stream);

@@ -75,8 +75,8 @@ def _hist_case(n, f, e, nb, n_nodes, seed, big_era=False):
     t["gq"].copy_(torch.from_numpy(gq))
     feat = rng.permutation(f)[: max(1, f // 2)].astype(np.int32)
     feat_t = torch.from_numpy(feat).to(dev)
-    cnt = torch.full((feat.shape[0], n_nodes, e, nb), -1, dtype=torch.int32, device=dev)
-    gs = torch.full((feat.shape[0], n_nodes, e, nb), -1, dtype=torch.int64, device=dev)
+    cnt = torch.full((feat.shape[0], e, n_nodes, nb), -1, dtype=torch.int32, device=dev)
+    gs = torch.full((feat.shape[0], e, n_nodes, nb), -1, dtype=torch.int64, device=dev)
     B.check(B.lib().pb_hist_build(C.byref(st), feat_t.data_ptr(), feat.shape[0], n_nodes, n_nodes, cnt.data_ptr(),
                                   gs.data_ptr(), torch.cuda.current_stream().cuda_stream))
     torch.cuda.synchronize()
@@ -93,13 +93,16 @@ def _hist_case(n, f, e, nb, n_nodes, seed, big_era=False):
         acc = np.zeros(n_nodes * e * nb, np.int64)
         np.add.at(acc, key, gq[:n][live].astype(np.int64))
         want_g[i] = acc.reshape(n_nodes, e, nb)
-    np.testing.assert_array_equal(cnt.cpu().numpy().astype(np.int64), want_c)
-    np.testing.assert_array_equal(gs.cpu().numpy(), want_g)
+    # device layout is [feature][era][node][bin]
+    np.testing.assert_array_equal(cnt.cpu().numpy().astype(np.int64).transpose(0, 2, 1, 3), want_c)
+    np.testing.assert_array_equal(gs.cpu().numpy().transpose(0, 2, 1, 3), want_g)
 
 
 @pytest.mark.parametrize("n,f,e,nb,nodes", [
     (5000, 12, 7, 5, 1), (5000, 12, 7, 5, 32), (4097, 9, 3, 16, 4), (6000, 10, 5, 128, 8),
     (3001, 6, 4, 200, 3), (20000, 5, 2, 64, 300), (1000, 3, 1, 2, 1), (16000, 4, 2, 5, 2),
+    (7000, 70, 3, 5, 2), (7000, 41, 3, 5, 8), (7000, 33, 2, 5, 50), (5000, 9, 2, 16, 1), (5000, 9, 2, 3, 9),
+    (5000, 20, 2, 16, 17),
 ])
 def test_histogram_exact(n, f, e, nb, nodes):
     _hist_case(n, f, e, nb, nodes, seed=n + nb)
