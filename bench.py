@@ -261,11 +261,10 @@ def main():
         X_host.copy_(X)
         del X
         torch.cuda.empty_cache()
-        Xh = X_host.numpy()
         barrier()
         t0 = time.perf_counter()
         b2 = PackBoost(PackBoostConfig(device="cuda", **CFG))
-        b2.fit(Xh, y_host, era_host, num_rounds=args.steps)
+        b2.fit(X_host, y_host, era_host, num_rounds=args.steps)   # pinned host tensor
         p = b2.train_predictions()          # device -> host read of the result
         barrier()
         wall = time.perf_counter() - t0

@@ -196,9 +196,9 @@ int pb_depth_clear_candidates(const pb_train_state* st, int64_t depth, int64_t n
  * every GPU that loads the library holds it until the process exits); `st->workspace` is not
  * touched and the candidate table is written to the caller's `cand_out`
  * (24-byte records, `n_sampled` x (1 << depth), same layout as pb_candidates_buffer).
- * Nothing is allocated or freed.  A shape whose single-feature histogram at `depth`
- * (`(1 << depth) * n_eras * max_bins * 12` bytes) exceeds the array is rejected with
- * PB_ERR_ARG.  The first call on a device looks up the array's device address
+ * Nothing is allocated or freed.  A shape whose single-feature scratch at `depth`
+ * (`(1 << depth) * n_eras * (max_bins * 12 + n_thresholds * 8)` bytes of histogram and scorer
+ * tables) exceeds the array is rejected with PB_ERR_ARG.  The first call on a device looks up the array's device address
  * (cudaGetSymbolAddress) with that device current; make that first call outside any stream
  * capture.  All calls in a process share the one array, which keeps whatever the previous call
  * left in it: the kernels rewrite every cell they later read, but two calls whose kernels

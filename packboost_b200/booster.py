@@ -239,7 +239,7 @@ class _DeviceTrainer:
         # workspace: candidate table + as many features of histogram as fit the budget
         k_sampled = self.n_sampled()
         stride = 1 << (int(cfg.max_depth) - 1)
-        per_feat = stride * self.E * nb * 12
+        per_feat = stride * self.E * (nb * 12 + int(thr.shape[0]) * 8) + stride * int(thr.shape[0]) * 12
         local_sampled = (k_sampled + world - 1) // world + 1
         want = 24 * self.F * stride + per_feat * min(local_sampled, max(matrix.n_features_local, 1)) + (1 << 20)
         min_bytes = int(self.lib.pb_workspace_min_bytes(C.byref(st)))
@@ -395,11 +395,14 @@ class PackBoost:
         self._fit_ctx: dict | None = None
         self._eval_states: list = []
         self._last_n_ctx: list[int] = []
+        self._pending_log = None
+        self._predrawn = None
 
     # Public -------------------------------------------------------------
 
     @property
     def trees(self) -> Sequence[Tree]:
+        self._flush_pending_tree()
         return self._trees
 
     @property
@@ -430,8 +433,9 @@ class PackBoost:
     def _start(self, X, y, era, *, feature_names=None, eval_sets=None) -> None:
         """Validate, bin, pack and upload the data; allocate the device state."""
         cfg = self.config
-        on_device = isinstance(X, torch.Tensor) and X.is_cuda
-        X_np = X if on_device else (X.detach().cpu().numpy() if isinstance(X, torch.Tensor) else np.asarray(X))
+        # torch tensors (device-resident, or pinned host memory) are consumed without conversion
+        on_device = isinstance(X, torch.Tensor)
+        X_np = X.detach() if on_device else np.asarray(X)
         y_np = np.asarray(y.detach().cpu().numpy() if isinstance(y, torch.Tensor) else y, dtype=np.float32)
         if y_np.ndim != 1:
             raise ValueError("y must be 1-D")
@@ -467,8 +471,13 @@ class PackBoost:
         era_offsets = np.concatenate([[0], np.cumsum(counts)]).astype(np.int32)
 
         # binning (packboost/data.py:61-93)
-        if on_device:
-            is_binned = X_np.dtype in (torch.uint8, torch.int8) and int(X_np.max()) < cfg.max_bins
+        small_int = X_np.dtype in (torch.uint8, torch.int8, np.dtype(np.uint8), np.dtype(np.int8))
+        validate_on_device = bool(cfg.prebinned) and small_int
+        if validate_on_device:
+            is_binned = True   # declared by the caller; the range is checked on the device while packing
+        elif on_device:
+            host_view = X_np.cpu().numpy() if X_np.is_cuda else X_np.numpy()
+            is_binned = detect_prebinned(host_view, cfg.max_bins)
         else:
             is_binned = detect_prebinned(X_np, cfg.max_bins)
         if bool(cfg.prebinned) and not is_binned:
@@ -477,7 +486,7 @@ class PackBoost:
             edges = None
             self._binner = BinningResult(bins=None, bin_edges=None, prebinned=True)
             if on_device:
-                X_src = X_np.view(torch.uint8)
+                X_src = X_np.view(torch.uint8) if X_np.dtype == torch.int8 else X_np.to(torch.uint8)
             else:
                 X_src = X_np if X_np.dtype in (np.uint8, np.int8) else X_np.astype(np.uint8)
                 X_src = X_src.view(np.uint8)
@@ -496,7 +505,8 @@ class PackBoost:
         feat_local = feature_map(F, rank, world)
         n_local = int((feat_local >= 0).sum())
         matrix = pack_feature_major(X_src, edges, cfg.max_bins, row_order=order,
-                                    feature_map=feat_local if world > 1 else None, n_features_local=n_local)
+                                    feature_map=feat_local if world > 1 else None, n_features_local=n_local,
+                                    validate_codes=validate_on_device)
         y_sorted = y_np if order is None else y_np[order]
         self._trainer = _DeviceTrainer(cfg, matrix, y_sorted, era_offsets, F, feat_local, rank, world)
         self._row_order = order
@@ -510,32 +520,46 @@ class PackBoost:
         self._tree_weight = float(cfg.learning_rate)
         self._trained_pack_size = int(cfg.pack_size)
         self._eval_states = self._prepare_eval_sets(eval_sets)
+        self._pending_log = None
+        self._predrawn = None
 
     def _boost_one_round(self, round_idx: int, num_rounds: int, want_callback: bool = False) -> dict[str, float]:
         """One boosting round (``packboost/booster.py:494-655``)."""
         cfg, trainer, ctx = self.config, self._trainer, self._fit_ctx
         F, D, k = ctx["F"], int(cfg.max_depth), trainer.n_sampled()
         t0 = perf_counter()
-        # one draw per depth, speculating that every depth has active nodes; the generator is
-        # rewound below when the device reports an empty frontier (packboost/booster.py:516-519)
-        states, subsets = [], []
-        for _ in range(D):
-            states.append(self._rng.get_state())
-            subsets.append(torch.randperm(F, generator=self._rng)[:k].numpy().astype(np.int32))
-        trainer.run_round(subsets)
-        head, winners = trainer.read_log()
-        tree, n_ctx = _tree_from_log(head, winners, D)
-        self._last_n_ctx = n_ctx
-        for d in range(D):
-            if n_ctx[d] == 0:
-                self._rng.set_state(states[d])
-                break
-            self._depth_logs.append(self._depth_log(d, n_ctx[d], k))
-        self._distinct.append((tree, int(cfg.pack_size)))
-        self._trees.extend([tree] * int(cfg.pack_size))
+        # One draw per depth, speculating that every depth has active nodes; when the device
+        # reports an empty frontier at depth d the reference would not have drawn for d or any
+        # later depth of this round (packboost/booster.py:516-519), so the generator is rewound to
+        # the round's start and the first d draws are replayed.
+        def draw():
+            st0 = self._rng.get_state()
+            return st0, [torch.randperm(F, generator=self._rng)[:k].numpy().astype(np.int32) for _ in range(D)]
 
+        state0, subsets = self._predrawn if self._predrawn is not None else draw()
+        self._predrawn = None
+        trainer.run_round(subsets)
+        # while the device works on this round: finish the host bookkeeping of the previous round
+        # and draw the next round's subsets (discarded below if this round rewinds the generator)
+        self._flush_pending_tree()
+        if round_idx + 1 < num_rounds:
+            self._predrawn = draw()
+        head, winners = trainer.read_log()
+        n_ctx = [int(v) for v in head["n_ctx"][: D + 1]]
+        self._last_n_ctx = n_ctx
+        used = next((d for d in range(D) if n_ctx[d] == 0), D)
+        if used < D:
+            self._rng.set_state(state0)
+            for _ in range(used):
+                torch.randperm(F, generator=self._rng)
+            self._predrawn = None
+        for d in range(used):
+            self._depth_logs.append(self._depth_log(d, n_ctx[d], k))
+        self._pending_log = (head.copy(), winners[: (1 << D) - 1].copy())
         eval_states = self._eval_states
         want_metrics = want_callback or bool(eval_states) or os.getenv("PACKBOOST_TRAIN_METRICS") == "1"
+        if want_metrics:
+            self._flush_pending_tree()  # callbacks and evaluation sets see this round's trees
         metrics: dict[str, float] = {"round": round_idx + 1}
         if want_metrics:
             trainer.flush_predictions()
@@ -556,7 +580,18 @@ class PackBoost:
         self._round_metrics.append(metrics)
         return metrics
 
+    def _flush_pending_tree(self) -> None:
+        """Replay the stored decision log of the last finished round into ``Tree`` objects."""
+        if self._pending_log is None:
+            return
+        head, winners = self._pending_log
+        self._pending_log = None
+        tree, _ = _tree_from_log(head, winners, int(self.config.max_depth))
+        self._distinct.append((tree, int(self.config.pack_size)))
+        self._trees.extend([tree] * int(self.config.pack_size))
+
     def _finish(self) -> None:
+        self._flush_pending_tree()
         self._trainer.flush_predictions()
         torch.cuda.current_stream().synchronize()
 
@@ -656,6 +691,7 @@ class PackBoost:
         (``packboost/booster.py:658-712``)."""
         if self._binner is None:
             raise RuntimeError("Model must be fitted before predict()")
+        self._flush_pending_tree()
         rows = self._pack_rows(X)
         if not self._trees:
             return np.zeros(rows.n_rows, dtype=np.float32)

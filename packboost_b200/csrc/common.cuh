@@ -171,7 +171,12 @@ struct ScoreLaunch {
     float lambda_l2, lambda_dro, direction_weight, era_alpha;
     int min_samples_leaf;
     Cand* cand;                  // [n_sampled][node_stride]
+    // scratch of the two-kernel scorer, for the n_feat features of this block
+    float2* gw;                  // [n_feat][n_eras][node_stride][n_thr] (gain, validity weight)
+    uint32_t* lc_tot;            // [n_feat][node_stride][n_thr] left counts summed over eras
+    int64_t* lg_tot;             // [n_feat][node_stride][n_thr] left gradient sums summed over eras
 };
 int launch_score(const ScoreLaunch& s, cudaStream_t stream);
+size_t score_scratch_bytes_per_feature(int node_stride, int n_eras, int n_thr);
 
 }  // namespace pb

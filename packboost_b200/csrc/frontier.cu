@@ -445,6 +445,96 @@ static int check_state(const pb_train_state* st) {
     return PB_OK;
 }
 
+
+// Carving of the scratch that one block of features needs between the histogram pass and the
+// scorer: gsum | cnt | gain-weight table | era-summed gradient sums | era-summed counts.
+struct BlockPlan {
+    int64_t fb;  // features per block
+    size_t off_gsum, off_cnt, off_gw, off_lg, off_lc;
+};
+
+static bool plan_block(size_t avail, int stride, int64_t n_eras, int64_t max_bins, int64_t n_thr, int64_t n_feat,
+                       BlockPlan* p) {
+    const size_t cells = (size_t)stride * n_eras * max_bins;
+    const size_t per_feat = cells * 12 + score_scratch_bytes_per_feature(stride, (int)n_eras, (int)n_thr);
+    if (avail < per_feat + 5 * 256) return false;
+    int64_t fb = (int64_t)((avail - 5 * 256) / per_feat);
+    if (fb > n_feat) fb = n_feat;
+    if (fb < 1) return false;
+    p->fb = fb;
+    size_t o = 0;
+    p->off_gsum = o;
+    o += align_up((size_t)fb * cells * 8, 256);
+    p->off_cnt = o;
+    o += align_up((size_t)fb * cells * 4, 256);
+    p->off_gw = o;
+    o += align_up((size_t)fb * stride * n_eras * n_thr * 8, 256);
+    p->off_lg = o;
+    o += align_up((size_t)fb * stride * n_thr * 8, 256);
+    p->off_lc = o;
+    return true;
+}
+
+static int hist_score_blocks(const pb_train_state* st, int64_t depth, const int32_t* feat_rows, const int32_t* feat_pos,
+                             int64_t n_feat, char* scratch, const BlockPlan& plan, Cand* cand, cudaStream_t stream) {
+    Ctl c = ctl_view(st->ctl);
+    const int stride = node_stride_of(depth);
+    int64_t* gsum = reinterpret_cast<int64_t*>(scratch + plan.off_gsum);
+    uint32_t* cnt = reinterpret_cast<uint32_t*>(scratch + plan.off_cnt);
+    for (int64_t f0 = 0; f0 < n_feat; f0 += plan.fb) {
+        const int nf = (int)((n_feat - f0 < plan.fb) ? (n_feat - f0) : plan.fb);
+        HistLaunch h;
+        h.codes = st->codes;
+        h.pitch = st->pitch;
+        h.code_bits = (int)st->code_bits;
+        h.feat_rows = feat_rows + f0;
+        h.n_feat = nf;
+        h.gq = st->gq;
+        h.slot = st->slot;
+        h.era_offsets = st->era_offsets;
+        h.n_eras = (int)st->n_eras;
+        h.max_bins = (int)st->max_bins;
+        h.max_era_rows = (int)st->max_era_rows;
+        h.n_nodes_ptr = &c.head->n_ctx[depth];
+        h.n_nodes = stride;
+        h.node_stride = stride;
+        h.count_bits = (int)st->count_bits;
+        h.lo_bits = (int)st->lo_bits;
+        h.max_arity = hist_max_arity();
+        h.cnt = cnt;   // the histogram kernel overwrites (or zeroes, then adds to) every cell that is read later
+        h.gsum = gsum;
+        int rc = launch_hist(h, stream);
+        if (rc) return rc;
+        ScoreLaunch s;
+        s.cnt = cnt;
+        s.gsum = gsum;
+        s.n_feat = nf;
+        s.feat_pos = feat_pos + f0;
+        s.node_stride = stride;
+        s.n_nodes_max = stride;
+        s.n_nodes_ptr = &c.head->n_ctx[depth];
+        s.frontier = c.frontier[depth & 1];
+        s.any_dir_ptr = &c.head->any_dir[depth];
+        s.inv_scale_ptr = &c.head->inv_scale;
+        s.n_eras = (int)st->n_eras;
+        s.max_bins = (int)st->max_bins;
+        s.n_thr = (int)st->n_thresholds;
+        s.thr_ids = st->thr_ids;
+        s.lambda_l2 = (float)st->lambda_l2;
+        s.lambda_dro = (float)st->lambda_dro;
+        s.direction_weight = (float)st->direction_weight;
+        s.era_alpha = (float)(st->era_alpha > 0.0 ? st->era_alpha : 0.0);
+        s.min_samples_leaf = (int)st->min_samples_leaf;
+        s.cand = cand;
+        s.gw = reinterpret_cast<float2*>(scratch + plan.off_gw);
+        s.lg_tot = reinterpret_cast<int64_t*>(scratch + plan.off_lg);
+        s.lc_tot = reinterpret_cast<uint32_t*>(scratch + plan.off_lc);
+        rc = launch_score(s, stream);
+        if (rc) return rc;
+    }
+    return PB_OK;
+}
+
 extern "C" int64_t pb_ctl_bytes(void) { return (int64_t)kCtlBytes; }
 
 extern "C" int64_t pb_workspace_min_bytes(const pb_train_state* st) {
@@ -452,8 +542,9 @@ extern "C" int64_t pb_workspace_min_bytes(const pb_train_state* st) {
     // candidate table at the deepest level for every feature + one feature of histogram
     const int64_t stride = 1ll << (st->max_depth - 1);
     const int64_t cand = (int64_t)sizeof(Cand) * st->n_features_total * stride;
-    const int64_t hist_one = stride * st->n_eras * st->max_bins * 12;
-    return align_up((size_t)cand, 256) + hist_one + 4096;
+    const int64_t hist_one = stride * st->n_eras * st->max_bins * 12 +
+                             (int64_t)score_scratch_bytes_per_feature((int)stride, (int)st->n_eras, (int)st->n_thresholds);
+    return align_up((size_t)cand, 256) + hist_one + 8192;
 }
 
 extern "C" int pb_train_prepare(pb_train_state* st, const int32_t* era_offsets_host) {
@@ -527,73 +618,16 @@ extern "C" int pb_depth_hist_score(const pb_train_state* st, int64_t depth, cons
     PB_REQUIRE(n_feat >= 0 && n_feat <= n_sampled && n_sampled <= st->n_features_total, "feature counts out of range");
     if (n_feat == 0) return PB_OK;
     PB_REQUIRE(feat_rows && feat_pos, "null feature list");
-    cudaStream_t stream = (cudaStream_t)stream_;
-    Ctl c = ctl_view(st->ctl);
     const int stride = node_stride_of(depth);
     const size_t cand_bytes = align_up(sizeof(Cand) * (size_t)n_sampled * stride, 256);
     PB_REQUIRE((int64_t)cand_bytes < st->workspace_bytes, "workspace too small for the candidate table");
     char* ws = static_cast<char*>(st->workspace);
-    Cand* cand = reinterpret_cast<Cand*>(ws);
-    const size_t per_feat_cells = (size_t)stride * st->n_eras * st->max_bins;
-    const size_t per_feat_bytes = per_feat_cells * 12;
-    int64_t fb = (int64_t)((st->workspace_bytes - cand_bytes - 256) / per_feat_bytes);
-    PB_REQUIRE(fb >= 1, "workspace too small for one feature of histogram at depth %lld", (long long)depth);
-    if (fb > n_feat) fb = n_feat;
-    // gsum (int64) first, then cnt: both 8-byte aligned
-    int64_t* gsum = reinterpret_cast<int64_t*>(ws + cand_bytes);
-    uint32_t* cnt = reinterpret_cast<uint32_t*>(ws + cand_bytes + align_up((size_t)fb * per_feat_cells * 8, 256));
-    if ((char*)cnt + (size_t)fb * per_feat_cells * 4 > ws + st->workspace_bytes) fb -= 1;
-    PB_REQUIRE(fb >= 1, "workspace too small for one feature of histogram at depth %lld", (long long)depth);
-
-    for (int64_t f0 = 0; f0 < n_feat; f0 += fb) {
-        const int nf = (int)((n_feat - f0 < fb) ? (n_feat - f0) : fb);
-        HistLaunch h;
-        h.codes = st->codes;
-        h.pitch = st->pitch;
-        h.code_bits = (int)st->code_bits;
-        h.feat_rows = feat_rows + f0;
-        h.n_feat = nf;
-        h.gq = st->gq;
-        h.slot = st->slot;
-        h.era_offsets = st->era_offsets;
-        h.n_eras = (int)st->n_eras;
-        h.max_bins = (int)st->max_bins;
-        h.max_era_rows = (int)st->max_era_rows;
-        h.n_nodes_ptr = &c.head->n_ctx[depth];
-        h.n_nodes = stride;
-        h.node_stride = stride;
-        h.count_bits = (int)st->count_bits;
-        h.lo_bits = (int)st->lo_bits;
-        h.max_arity = hist_max_arity();
-        h.cnt = cnt;
-        h.gsum = gsum;
-        rc = launch_hist(h, stream);
-        if (rc) return rc;
-        ScoreLaunch s;
-        s.cnt = cnt;
-        s.gsum = gsum;
-        s.n_feat = nf;
-        s.feat_pos = feat_pos + f0;
-        s.node_stride = stride;
-        s.n_nodes_max = stride;
-        s.n_nodes_ptr = &c.head->n_ctx[depth];
-        s.frontier = c.frontier[depth & 1];
-        s.any_dir_ptr = &c.head->any_dir[depth];
-        s.inv_scale_ptr = &c.head->inv_scale;
-        s.n_eras = (int)st->n_eras;
-        s.max_bins = (int)st->max_bins;
-        s.n_thr = (int)st->n_thresholds;
-        s.thr_ids = st->thr_ids;
-        s.lambda_l2 = (float)st->lambda_l2;
-        s.lambda_dro = (float)st->lambda_dro;
-        s.direction_weight = (float)st->direction_weight;
-        s.era_alpha = (float)(st->era_alpha > 0.0 ? st->era_alpha : 0.0);
-        s.min_samples_leaf = (int)st->min_samples_leaf;
-        s.cand = cand;
-        rc = launch_score(s, stream);
-        if (rc) return rc;
-    }
-    return PB_OK;
+    BlockPlan plan;
+    PB_REQUIRE(plan_block((size_t)st->workspace_bytes - cand_bytes, stride, st->n_eras, st->max_bins, st->n_thresholds,
+                          n_feat, &plan),
+               "workspace too small for one feature of histogram at depth %lld", (long long)depth);
+    return hist_score_blocks(st, depth, feat_rows, feat_pos, n_feat, ws + cand_bytes, plan, reinterpret_cast<Cand*>(ws),
+                             (cudaStream_t)stream_);
 }
 
 extern "C" int pb_depth_select(const pb_train_state* st, int64_t depth, const int32_t* sampled_features,
@@ -770,70 +804,17 @@ extern "C" int pb_depth_hist_score_static(const pb_train_state* st, int64_t dept
     if (n_feat == 0) return PB_OK;
     PB_REQUIRE(feat_rows && feat_pos, "null feature list");
     const int stride = node_stride_of(depth);
-    const size_t per_feat_cells = (size_t)stride * st->n_eras * st->max_bins;
-    // gsum (8 bytes per cell) first, then cnt (4 bytes per cell), each block 256-byte aligned
-    const size_t per_feat_bytes = per_feat_cells * 12;
-    PB_REQUIRE(per_feat_bytes + 512 <= kStaticScratchBytes,
-               "static scratch too small: one feature of histogram at depth %lld needs %llu bytes, the fixed "
-               "array holds %llu; use pb_depth_hist_score with a workspace",
-               (long long)depth, (unsigned long long)per_feat_bytes, (unsigned long long)kStaticScratchBytes);
+    BlockPlan plan;
+    PB_REQUIRE(plan_block(kStaticScratchBytes, stride, st->n_eras, st->max_bins, st->n_thresholds, n_feat, &plan),
+               "static scratch too small: one feature of histogram and scorer tables at depth %lld needs %llu bytes, "
+               "the fixed array holds %llu; use pb_depth_hist_score with a workspace",
+               (long long)depth,
+               (unsigned long long)((size_t)stride * st->n_eras * st->max_bins * 12 +
+                                    score_scratch_bytes_per_feature(stride, (int)st->n_eras, (int)st->n_thresholds)),
+               (unsigned long long)kStaticScratchBytes);
     void* base = nullptr;
     rc = static_scratch_ptr(&base);
     if (rc) return rc;
-    int64_t fb = (int64_t)((kStaticScratchBytes - 512) / per_feat_bytes);
-    if (fb > n_feat) fb = n_feat;
-    char* ws = static_cast<char*>(base);
-    int64_t* gsum = reinterpret_cast<int64_t*>(ws);
-    uint32_t* cnt = reinterpret_cast<uint32_t*>(ws + align_up((size_t)fb * per_feat_cells * 8, 256));
-    cudaStream_t stream = (cudaStream_t)stream_;
-    Ctl c = ctl_view(st->ctl);
-    for (int64_t f0 = 0; f0 < n_feat; f0 += fb) {
-        const int nf = (int)((n_feat - f0 < fb) ? (n_feat - f0) : fb);
-        HistLaunch h;
-        h.codes = st->codes;
-        h.pitch = st->pitch;
-        h.code_bits = (int)st->code_bits;
-        h.feat_rows = feat_rows + f0;
-        h.n_feat = nf;
-        h.gq = st->gq;
-        h.slot = st->slot;
-        h.era_offsets = st->era_offsets;
-        h.n_eras = (int)st->n_eras;
-        h.max_bins = (int)st->max_bins;
-        h.max_era_rows = (int)st->max_era_rows;
-        h.n_nodes_ptr = &c.head->n_ctx[depth];
-        h.n_nodes = stride;
-        h.node_stride = stride;
-        h.count_bits = (int)st->count_bits;
-        h.lo_bits = (int)st->lo_bits;
-        h.max_arity = hist_max_arity();
-        h.cnt = cnt;     // the histogram kernel overwrites (or zeroes, then adds to) every cell it later reads
-        h.gsum = gsum;
-        rc = launch_hist(h, stream);
-        if (rc) return rc;
-        ScoreLaunch s;
-        s.cnt = cnt;
-        s.gsum = gsum;
-        s.n_feat = nf;
-        s.feat_pos = feat_pos + f0;
-        s.node_stride = stride;
-        s.n_nodes_max = stride;
-        s.n_nodes_ptr = &c.head->n_ctx[depth];
-        s.frontier = c.frontier[depth & 1];
-        s.any_dir_ptr = &c.head->any_dir[depth];
-        s.inv_scale_ptr = &c.head->inv_scale;
-        s.n_eras = (int)st->n_eras;
-        s.max_bins = (int)st->max_bins;
-        s.n_thr = (int)st->n_thresholds;
-        s.thr_ids = st->thr_ids;
-        s.lambda_l2 = (float)st->lambda_l2;
-        s.lambda_dro = (float)st->lambda_dro;
-        s.direction_weight = (float)st->direction_weight;
-        s.era_alpha = (float)(st->era_alpha > 0.0 ? st->era_alpha : 0.0);
-        s.min_samples_leaf = (int)st->min_samples_leaf;
-        s.cand = static_cast<Cand*>(cand_out);
-        rc = launch_score(s, stream);
-        if (rc) return rc;
-    }
-    return PB_OK;
+    return hist_score_blocks(st, depth, feat_rows, feat_pos, n_feat, static_cast<char*>(base), plan,
+                             static_cast<Cand*>(cand_out), (cudaStream_t)stream_);
 }

@@ -104,11 +104,14 @@ def pack_feature_major(
     row_order: np.ndarray | None = None,
     feature_map: np.ndarray | None = None,
     n_features_local: int | None = None,
+    validate_codes: bool = False,
 ) -> PackedMatrix:
     """Bin (when ``edges`` is given) and pack host data into a device ``PackedMatrix``.
 
     ``row_order`` lists source rows in destination order (era-sorted rows);
     ``feature_map[j]`` is the destination feature row of column ``j`` or -1.
+    ``validate_codes`` checks on the device that pre-binned input stays below ``max_bins``
+    (negative int8 values show up as codes >= 128) and raises ``ValueError`` otherwise.
     """
     dev = _device()
     lib = B.lib()
@@ -123,24 +126,35 @@ def pack_feature_major(
     edges_t = torch.from_numpy(np.ascontiguousarray(edges, dtype=np.float32)).to(dev) if is_f32 else None
     stream = torch.cuda.current_stream().cuda_stream
     src_dtype = np.float32 if is_f32 else np.uint8
-    on_device = isinstance(X, torch.Tensor)
+    is_tensor = isinstance(X, torch.Tensor)
     order_t = None
-    if on_device and row_order is not None:
+    if is_tensor and row_order is not None:
         order_t = torch.from_numpy(np.ascontiguousarray(row_order, dtype=np.int64)).to(X.device)
+    want = torch.float32 if is_f32 else torch.uint8
+    top = torch.zeros((), dtype=torch.uint8, device=dev)
     for a, b in _row_chunks(n_rows, n_feat * (4 if is_f32 else 1)):
-        if on_device:
+        if is_tensor:
+            # device tensors are sliced in place; pinned host tensors are copied asynchronously
             rows = X[a:b] if order_t is None else X.index_select(0, order_t[a:b])
-            chunk = rows.to(device=dev, dtype=torch.float32 if is_f32 else torch.uint8).contiguous()
+            if rows.dtype == torch.int8 and not is_f32:
+                rows = rows.view(torch.uint8)
+            chunk = rows.to(device=dev, dtype=want, non_blocking=True).contiguous()
         else:
             rows = X[a:b] if row_order is None else X[row_order[a:b]]
             chunk = torch.from_numpy(np.ascontiguousarray(rows, dtype=src_dtype)).to(dev, non_blocking=False)
+        if validate_codes and not is_f32:
+            top = torch.maximum(top, chunk.max())
         if is_f32:
             B.check(lib.pb_bin_pack_f32(chunk.data_ptr(), b - a, n_feat, a, edges_t.data_ptr(), edges_t.shape[0],
                                         max_bins, B._ptr(fmap_t), pm.codes.data_ptr(), pm.pitch, bits, stream))
         else:
             B.check(lib.pb_pack_codes_u8(chunk.data_ptr(), b - a, n_feat, a, B._ptr(fmap_t), pm.codes.data_ptr(),
                                          pm.pitch, bits, stream))
-        torch.cuda.current_stream().synchronize()
+        # no synchronisation per chunk: the copy, the pack kernel and the release of `chunk` are
+        # ordered on the current stream
+    torch.cuda.current_stream().synchronize()
+    if validate_codes and int(top.item()) >= min(max_bins, 128):
+        raise ValueError("prebinned=True requires X to contain integer bins within [0, max_bins).")
     return pm
 
 

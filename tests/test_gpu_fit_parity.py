@@ -128,3 +128,21 @@ def test_errors_are_loud():
         b.fit(np.zeros((10, 2), np.float32), np.zeros(10, np.float32), None, num_rounds=1)
     with pytest.raises(RuntimeError):
         PackBoost(PackBoostConfig(device="cuda")).predict(np.zeros((4, 2), np.float32))
+
+
+def test_wrapper_and_predictor_roundtrip(tmp_path):
+    """README-style usage: regressor with an eval set, then a saved / reloaded predictor."""
+    from packboost_b200 import PackBoostPredictor, PackBoostRegressor
+    X, y, era, cfg, rounds, Xh = cases.CASES["interleaved"]()
+    seen = []
+    m = PackBoostRegressor(num_rounds=rounds, **cfg)
+    m.fit(X, y, era=era, eval_set=(X[:100], y[:100], era[:100]), round_callback=lambda r, met: seen.append(met))
+    assert len(seen) == rounds and "valid_corr" in seen[-1] and np.isfinite(seen[-1]["train_corr"])
+    gold = np.load(os.path.join(GOLD, "interleaved.npz"))
+    scale = np.abs(gold["pred_holdout"]).max()
+    np.testing.assert_allclose(m.predict(Xh), gold["pred_holdout"], rtol=1e-5, atol=1e-5 * scale)
+    path = str(tmp_path / "m.npz")
+    m.to_predictor().save(path)
+    p = PackBoostPredictor.load(path)
+    np.testing.assert_array_equal(p.predict(Xh).view(np.int32), m.predict(Xh).view(np.int32))
+    assert m.score(X, y) > 0.3
