@@ -213,17 +213,20 @@ __global__ void __launch_bounds__(THREADS) hist_kernel(HistKernelArgs a) {
 // ---- lane-private kernel for small cell counts ------------------------------------------------
 
 constexpr int kLaneCellBytes = 256;        // word A of lane l at l*4, word B at 128 + l*4: bank == lane
-constexpr int kLaneSmemMax = 64 * 1024;    // cells of one CTA
+constexpr int kLaneSmemMax = 104 * 1024;   // cells of one CTA (two CTAs per SM)
 constexpr int kLaneWarps = 8;
 constexpr int kLaneRows = 64;              // rows per warp step: 32 bytes of 4-bit codes per feature
 
 // All lanes of a warp walk the same rows, so the row state is warp-uniform.  It is staged per
-// warp, two rows per 16-byte record {cell base of both rows (16 bits each, 0xFFFF: skip), gq of
-// row 0, gq of row 1, unused}: one broadcast shared load serves two row steps.  The codes and
-// the raw row state of the warp's next chunk are loaded while the current chunk is accumulated.
-template <int A>
-__global__ void __launch_bounds__(kLaneWarps * 32, 3) hist_lane_kernel(HistKernelArgs a) {
-    extern __shared__ __align__(16) unsigned char smb[];  // cells | staging [warps][32] uint4
+// warp as one 16-byte record per row {byte offset of the node's first cell (0xFFFFFFFF: skip),
+// word A addend, word B addend, unused}, computed once per row by one lane and read by all lanes
+// with a single broadcast load, so the per-lane work of a row step is just code extraction, one
+// three-input add and the two atomics of each tuple.  A lane owns T tuples of A features (T*A
+// consecutive sampled features), each tuple with its own set of cells.  The codes and the raw
+// row state of the warp's next chunk are loaded while the current chunk is accumulated.
+template <int A, int T>
+__global__ void __launch_bounds__(kLaneWarps * 32, 2) hist_lane_kernel(HistKernelArgs a) {
+    extern __shared__ __align__(16) unsigned char smb[];  // cells [T][n_cells] | staging [warps][64] uint4
     const int n_nodes = a.n_nodes_ptr ? min(*a.n_nodes_ptr, a.n_nodes) : a.n_nodes;
     if (n_nodes <= 0) return;
     const int era = blockIdx.x / a.tiles_per_era;
@@ -238,34 +241,35 @@ __global__ void __launch_bounds__(kLaneWarps * 32, 3) hist_lane_kernel(HistKerne
     int cpn = nb;  // cells per node = bins^A
 #pragma unroll
     for (int i = 1; i < A; ++i) cpn *= nb;
-    const int n_cells = a.n_nodes * cpn;  // sized for the upper bound of nodes
+    const int n_cells = a.n_nodes * cpn;  // per tuple, sized for the upper bound of nodes
+    const uint32_t slot_bytes = (uint32_t)n_cells * kLaneCellBytes;
     uint32_t* cells = reinterpret_cast<uint32_t*>(smb);
-    uint4* staging = reinterpret_cast<uint4*>(smb + (size_t)n_cells * kLaneCellBytes);
+    uint4* staging = reinterpret_cast<uint4*>(smb + (size_t)T * slot_bytes);
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int CB = a.count_bits, LB = a.lo_bits;
     const uint32_t lo_mask = (1u << LB) - 1u;
 
-    for (int i = threadIdx.x; i < n_cells * 64; i += blockDim.x) cells[i] = 0u;
+    for (int i = threadIdx.x; i < T * n_cells * 64; i += blockDim.x) cells[i] = 0u;
 
-    // features of this lane's tuple
-    const int tuple = blockIdx.y * 32 + lane;
-    int n_mine = a.n_feat - tuple * A;
-    n_mine = max(0, min(A, n_mine));
-    const uint8_t* frow[A];
+    // features of this lane: T tuples of A consecutive sampled features
+    constexpr int FPL = A * T;
+    const int feat0 = (blockIdx.y * 32 + lane) * FPL;
+    const int n_mine = max(0, min(FPL, a.n_feat - feat0));
+    const uint8_t* frow[FPL];
 #pragma unroll
-    for (int i = 0; i < A; ++i)
-        frow[i] = a.codes + (int64_t)__ldg(a.feat_rows + min(tuple * A + i, a.n_feat - 1)) * a.pitch;
+    for (int i = 0; i < FPL; ++i)
+        frow[i] = a.codes + (int64_t)__ldg(a.feat_rows + min(feat0 + i, a.n_feat - 1)) * a.pitch;
     __syncthreads();
 
     unsigned char* lane_base = smb + lane * 4;
-    uint4* st = staging + warp * (kLaneRows / 2);
+    uint4* st = staging + warp * kLaneRows;
     const int c0 = r0 / kLaneRows, c1 = (r1 + kLaneRows - 1) / kLaneRows;
+    const uint32_t nb_scaled = (uint32_t)nb * kLaneCellBytes;
 
-    uint32_t w[A][8];
+    uint32_t w[FPL][8];
     int raw_s[2], raw_g[2];
-    auto load_chunk = [&](int c, uint32_t (&ww)[A][8], int (&rs)[2], int (&rg)[2]) {
-        // lane l takes rows 2l and 2l+1 of the chunk: they share one staged record
-        const int r = c * kLaneRows + 2 * lane;
+    auto load_chunk = [&](int c, uint32_t (&ww)[FPL][8], int (&rs)[2], int (&rg)[2]) {
+        const int r = c * kLaneRows + 2 * lane;  // lane l stages rows 2l and 2l+1 of the chunk
         const uint32_t sv = *reinterpret_cast<const uint32_t*>(a.slot + r);
         const int2 gv = *reinterpret_cast<const int2*>(a.gq + r);
         rs[0] = sv & 0xFFFF;
@@ -273,7 +277,7 @@ __global__ void __launch_bounds__(kLaneWarps * 32, 3) hist_lane_kernel(HistKerne
         rg[0] = gv.x;
         rg[1] = gv.y;
 #pragma unroll
-        for (int i = 0; i < A; ++i) {
+        for (int i = 0; i < FPL; ++i) {
             const uint4* p = reinterpret_cast<const uint4*>(frow[i] + (int64_t)c * (kLaneRows / 2));
             const uint4 v0 = __ldg(p), v1 = __ldg(p + 1);
             ww[i][0] = v0.x; ww[i][1] = v0.y; ww[i][2] = v0.z; ww[i][3] = v0.w;
@@ -283,50 +287,48 @@ __global__ void __launch_bounds__(kLaneWarps * 32, 3) hist_lane_kernel(HistKerne
     int c = c0 + warp;
     if (c < c1) load_chunk(c, w, raw_s, raw_g);
     for (; c < c1; c += kLaneWarps) {
-        {
-            uint4 rec;
-            uint32_t cb[2];
 #pragma unroll
-            for (int h = 0; h < 2; ++h) {
-                const int r = c * kLaneRows + 2 * lane + h;
-                const bool ok = (r >= r0) & (r < r1) & (raw_s[h] < n_nodes);
-                cb[h] = ok ? (uint32_t)(raw_s[h] * cpn) : 0xFFFFu;
-            }
-            rec.x = cb[0] | (cb[1] << 16);
-            rec.y = (uint32_t)raw_g[0];
-            rec.z = (uint32_t)raw_g[1];
+        for (int h = 0; h < 2; ++h) {
+            const int r = c * kLaneRows + 2 * lane + h;
+            const bool ok = (r >= r0) & (r < r1) & (raw_s[h] < n_nodes);
+            uint4 rec;
+            rec.x = ok ? (uint32_t)(raw_s[h] * cpn) * kLaneCellBytes : 0xFFFFFFFFu;
+            rec.y = (((uint32_t)raw_g[h] & lo_mask) << CB) + 1u;
+            rec.z = (uint32_t)(raw_g[h] >> LB);
             rec.w = 0u;
-            st[lane] = rec;
+            st[2 * lane + h] = rec;
         }
         __syncwarp();
-        uint32_t wn[A][8];
+        uint32_t wn[FPL][8];
         int nraw_s[2], nraw_g[2];
         const int cn = c + kLaneWarps;
         if (cn < c1) load_chunk(cn, wn, nraw_s, nraw_g);
         if (n_mine > 0) {
 #pragma unroll
             for (int jb = 0; jb < kLaneRows; jb += 4) {
-                uint4 rec[2];
-                rec[0] = st[jb >> 1];  // every lane reads the same record: a broadcast load
-                rec[1] = st[(jb >> 1) + 1];
+                uint4 rec[4];
+#pragma unroll
+                for (int q = 0; q < 4; ++q) rec[q] = st[jb + q];  // broadcast loads, issued together
 #pragma unroll
                 for (int q = 0; q < 4; ++q) {
                     const int j = jb + q;
-                    const uint32_t cbase = (rec[q >> 1].x >> ((q & 1) * 16)) & 0xFFFFu;
-                    if (cbase != 0xFFFFu) {
-                        const int g = (int)((q & 1) ? rec[q >> 1].z : rec[q >> 1].y);
-                        // joint code of the tuple
+                    if (rec[q].x != 0xFFFFFFFFu) {
                         const int bit = (j & 7) * 4;
-                        uint32_t idx = (w[0][j >> 3] >> bit) & 0xFu;
-                        int mul = nb;
 #pragma unroll
-                        for (int i = 1; i < A; ++i) {
-                            idx += (uint32_t)mul * ((w[i][j >> 3] >> bit) & 0xFu);
-                            mul *= nb;
+                        for (int t = 0; t < T; ++t) {
+                            // joint code of the tuple, pre-scaled by the cell pitch (256 bytes)
+                            const uint32_t w0 = w[t * A][j >> 3];
+                            uint32_t off = (bit >= 8) ? ((w0 >> (bit - 8)) & 0xF00u) : ((w0 << (8 - bit)) & 0xF00u);
+                            uint32_t mul = nb_scaled;
+#pragma unroll
+                            for (int i = 1; i < A; ++i) {
+                                off += mul * ((w[t * A + i][j >> 3] >> bit) & 0xFu);
+                                mul *= (uint32_t)nb;
+                            }
+                            unsigned char* cell = lane_base + (rec[q].x + off + (uint32_t)t * slot_bytes);
+                            atomicAdd(reinterpret_cast<uint32_t*>(cell), rec[q].y);
+                            atomicAdd(reinterpret_cast<int*>(cell + 128), (int)rec[q].z);
                         }
-                        unsigned char* cell = lane_base + (cbase + idx) * kLaneCellBytes;
-                        atomicAdd(reinterpret_cast<uint32_t*>(cell), (((uint32_t)g & lo_mask) << CB) + 1u);
-                        atomicAdd(reinterpret_cast<int*>(cell + 128), g >> LB);
                     }
                 }
             }
@@ -334,7 +336,7 @@ __global__ void __launch_bounds__(kLaneWarps * 32, 3) hist_lane_kernel(HistKerne
         __syncwarp();
         if (cn < c1) {
 #pragma unroll
-            for (int i = 0; i < A; ++i)
+            for (int i = 0; i < FPL; ++i)
 #pragma unroll
                 for (int q = 0; q < 8; ++q) w[i][q] = wn[i][q];
             raw_s[0] = nraw_s[0]; raw_s[1] = nraw_s[1];
@@ -343,27 +345,29 @@ __global__ void __launch_bounds__(kLaneWarps * 32, 3) hist_lane_kernel(HistKerne
     }
     __syncthreads();
 
-    // flush: marginals of this lane's joint table -> [feature][era][node][bin]
+    // flush: marginals of this lane's joint tables -> [feature][era][node][bin]
     const uint32_t cmask = (1u << CB) - 1u;
-    for (int item = warp; item < n_nodes * A; item += kLaneWarps) {
-        const int n = item / A, fi = item - n * A;
-        if (fi >= n_mine) continue;
+    for (int item = warp; item < n_nodes * FPL; item += kLaneWarps) {
+        const int n = item / FPL, fl = item - n * FPL;  // node, feature of the lane
+        if (fl >= n_mine) continue;
+        const int t = fl / A, fi = fl - t * A;
         int below = 1;  // bins^fi
         for (int i = 0; i < fi; ++i) below *= nb;
         const int above = cpn / (below * nb);
+        const uint32_t* tcells = cells + (size_t)t * n_cells * 64;
         for (int b = 0; b < nb; ++b) {
             uint32_t count = 0;
             long long lo_sum = 0, hi_sum = 0;
             for (int hi = 0; hi < above; ++hi)
                 for (int lo = 0; lo < below; ++lo) {
                     const uint32_t cell = (uint32_t)(n * cpn + (hi * nb + b) * below + lo) * 64u + lane;
-                    const uint32_t Aw = cells[cell];
+                    const uint32_t Aw = tcells[cell];
                     count += Aw & cmask;
                     lo_sum += (long long)(Aw >> CB);
-                    hi_sum += (long long)(int32_t)cells[cell + 32];
+                    hi_sum += (long long)(int32_t)tcells[cell + 32];
                 }
             const long long gs = hi_sum * (1ll << LB) + lo_sum;
-            const size_t o = (((size_t)(tuple * A + fi) * a.n_eras + era) * a.node_stride + n) * nb + b;
+            const size_t o = (((size_t)(feat0 + fl) * a.n_eras + era) * a.node_stride + n) * nb + b;
             if (a.use_atomics) {
                 if (count) atomicAdd(a.cnt + o, count);
                 if (gs) atomicAdd(reinterpret_cast<unsigned long long*>(a.gsum + o), (unsigned long long)gs);
@@ -375,12 +379,13 @@ __global__ void __launch_bounds__(kLaneWarps * 32, 3) hist_lane_kernel(HistKerne
     }
 }
 
-template <int A>
-int launch_lane(const HistKernelArgs& a, int n_tuples, size_t smem, cudaStream_t stream) {
+template <int A, int T>
+int launch_lane(const HistKernelArgs& a, size_t smem, cudaStream_t stream) {
     if (smem > 48 * 1024)
-        PB_CUDA_TRY(cudaFuncSetAttribute(hist_lane_kernel<A>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    dim3 grid((unsigned)(a.n_eras * a.tiles_per_era), (unsigned)((n_tuples + 31) / 32), 1);
-    hist_lane_kernel<A><<<grid, kLaneWarps * 32, smem, stream>>>(a);
+        PB_CUDA_TRY(cudaFuncSetAttribute(hist_lane_kernel<A, T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    const int per_cta = 32 * A * T;
+    dim3 grid((unsigned)(a.n_eras * a.tiles_per_era), (unsigned)((a.n_feat + per_cta - 1) / per_cta), 1);
+    hist_lane_kernel<A, T><<<grid, kLaneWarps * 32, smem, stream>>>(a);
     return PB_OK;
 }
 
@@ -433,27 +438,30 @@ int launch_hist(const HistLaunch& h, cudaStream_t stream) {
         PB_CUDA_TRY(cudaMemsetAsync(h.gsum, 0, out_cells * sizeof(int64_t), stream));
     }
 
-    // lane-private kernel when a lane's cells are few: the largest tuple size (joint code of up
-    // to `max_arity` features) whose cells fit one CTA
-    if (h.code_bits == 4 && (int64_t)h.n_nodes * h.max_bins * kLaneCellBytes <= kLaneSmemMax &&
-        (int64_t)h.n_nodes * h.max_bins <= 0xFFFE) {
+    // lane-private kernel when a lane's cells are few: tuples of A features (joint code) as wide as
+    // the cells allow, then T tuples per lane while shared memory lasts (A * T <= 4)
+    if (h.code_bits == 4 && (int64_t)h.n_nodes * h.max_bins * kLaneCellBytes <= kLaneSmemMax) {
         int arity = 1;
         int64_t cpn = h.max_bins;
-        while (arity < h.max_arity && (int64_t)h.n_nodes * cpn * h.max_bins * kLaneCellBytes <= kLaneSmemMax &&
-               (int64_t)h.n_nodes * cpn * h.max_bins <= 0xFFFE) {
+        const int cap = h.max_arity < 3 ? h.max_arity : 3;
+        while (arity < cap && (int64_t)h.n_nodes * cpn * h.max_bins * kLaneCellBytes <= kLaneSmemMax) {
             cpn *= h.max_bins;
             ++arity;
         }
+        const size_t slot = (size_t)h.n_nodes * cpn * kLaneCellBytes;
+        int tuples = (arity == 3) ? 1 : 4 / arity;
+        while (tuples > 1 && (slot * tuples > (size_t)kLaneSmemMax || 32 * arity * tuples > 2 * h.n_feat)) tuples /= 2;
         a.nodes_per_chunk = h.n_nodes;
-        a.feats_per_cta = 32 * arity;
+        a.feats_per_cta = 32 * arity * tuples;
         a.group = arity;
         a.copies = 1;
-        const int n_tuples = (h.n_feat + arity - 1) / arity;
-        const size_t smem = (size_t)h.n_nodes * cpn * kLaneCellBytes + (size_t)kLaneWarps * (kLaneRows / 2) * sizeof(uint4);
+        const size_t smem = slot * tuples + (size_t)kLaneWarps * kLaneRows * sizeof(uint4);
         prof_begin(kProfHist, stream);
-        const int rc = (arity == 3) ? launch_lane<3>(a, n_tuples, smem, stream)
-                       : (arity == 2) ? launch_lane<2>(a, n_tuples, smem, stream)
-                                      : launch_lane<1>(a, n_tuples, smem, stream);
+        int rc;
+        if (arity == 3) rc = launch_lane<3, 1>(a, smem, stream);
+        else if (arity == 2) rc = (tuples == 2) ? launch_lane<2, 2>(a, smem, stream) : launch_lane<2, 1>(a, smem, stream);
+        else rc = (tuples == 4) ? launch_lane<1, 4>(a, smem, stream)
+                  : (tuples == 2) ? launch_lane<1, 2>(a, smem, stream) : launch_lane<1, 1>(a, smem, stream);
         prof_end(kProfHist, stream);
         if (rc) return rc;
         count_launch(1);
