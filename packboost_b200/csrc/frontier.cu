@@ -357,32 +357,53 @@ __global__ void __launch_bounds__(kRowThreads) partition_kernel(PartArgs a) {
     if (n_ctx <= 0) return;
     for (int i = threadIdx.x; i < n_ctx; i += blockDim.x) tab[i] = a.c.part[i];
     __syncthreads();
+    // each thread takes kPer rows spaced one grid apart, so that its dependent loads
+    // (slot -> table entry -> code) of different rows overlap
+    constexpr int kPer = 4;
     const int64_t n_round = (a.n + 31) / 32 * 32;
-    for (int64_t r = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; r < n_round; r += (int64_t)gridDim.x * blockDim.x) {
-        const int s = (r < a.n) ? a.slot[r] : kSlotNone;
-        bool left = false;
-        PartEntry pe;
-        pe.feature = -1;
-        if (s != kSlotNone && s < n_ctx) {
-            pe = tab[s];
-            if (pe.feature >= 0) {
-                if (MODE == 2) {
-                    left = (a.bits_in[r >> 5] >> (r & 31)) & 1u;
-                } else {
-                    const int frow = a.feat_local[pe.feature];
-                    if (frow >= 0) left = load_code<BITS>(a.codes, a.pitch, frow, r) <= pe.threshold;
-                }
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t r0 = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; r0 < n_round; r0 += stride * kPer) {
+        int s[kPer];
+        PartEntry pe[kPer];
+        int frow[kPer];
+        bool left[kPer];
+#pragma unroll
+        for (int u = 0; u < kPer; ++u) {
+            const int64_t r = r0 + u * stride;
+            s[u] = (r < a.n) ? a.slot[r] : kSlotNone;
+        }
+#pragma unroll
+        for (int u = 0; u < kPer; ++u) {
+            pe[u].feature = -1;
+            frow[u] = -1;
+            if (s[u] != kSlotNone && s[u] < n_ctx) {
+                pe[u] = tab[s[u]];
+                if (pe[u].feature >= 0 && MODE != 2) frow[u] = a.feat_local[pe[u].feature];
             }
         }
-        if (MODE == 1) {
-            const unsigned m = __ballot_sync(0xFFFFFFFFu, left);
-            if ((threadIdx.x & 31) == 0) a.bits[r >> 5] = m;
-        } else if (s != kSlotNone) {
-            if (s < n_ctx && pe.feature >= 0) {
-                a.slot[r] = left ? pe.slot_left : pe.slot_right;
-                a.leaf[r] = left ? pe.leaf_left : pe.leaf_right;
-            } else {
-                a.slot[r] = kSlotNone;
+#pragma unroll
+        for (int u = 0; u < kPer; ++u) {
+            const int64_t r = r0 + u * stride;
+            left[u] = false;
+            if (r < n_round && pe[u].feature >= 0) {
+                if (MODE == 2) left[u] = (a.bits_in[r >> 5] >> (r & 31)) & 1u;
+                else if (frow[u] >= 0) left[u] = load_code<BITS>(a.codes, a.pitch, frow[u], r) <= pe[u].threshold;
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < kPer; ++u) {
+            const int64_t r = r0 + u * stride;
+            if (r >= n_round) continue;  // uniform per warp: n_round and the strides are multiples of 32
+            if (MODE == 1) {
+                const unsigned m = __ballot_sync(0xFFFFFFFFu, left[u]);
+                if ((threadIdx.x & 31) == 0) a.bits[r >> 5] = m;
+            } else if (s[u] != kSlotNone) {
+                if (s[u] < n_ctx && pe[u].feature >= 0) {
+                    a.slot[r] = left[u] ? pe[u].slot_left : pe[u].slot_right;
+                    a.leaf[r] = left[u] ? pe[u].leaf_left : pe[u].leaf_right;
+                } else {
+                    a.slot[r] = kSlotNone;
+                }
             }
         }
     }

@@ -258,7 +258,10 @@ __global__ void __launch_bounds__(kGainThreads) gain_kernel_wide(GainArgs a) {
 struct ChainArgs {
     ScoreLaunch s;
     int nodes_per_cta;
+    int unit_weights;  // 1: era weights are 0/1 and n_eras fits the reciprocal table
 };
+
+constexpr int kInvTable = 4096;
 
 __device__ __forceinline__ void welford_step(float gn, float w, float& wsum, float& mean, float& m2) {
     const float wsum_new = f_add(wsum, w);
@@ -285,6 +288,11 @@ __global__ void __launch_bounds__(kChainThreads) chain_kernel(ChainArgs a) {
     long long* res_lg = reinterpret_cast<long long*>(smem_raw);
     float* res_score = reinterpret_cast<float*>(res_lg + (size_t)npc * K);
     uint32_t* res_cnt = reinterpret_cast<uint32_t*>(res_score + (size_t)npc * K);
+    float* s_inv = reinterpret_cast<float*>(res_cnt + (size_t)npc * K);  // s_inv[n] = 1/n, n <= n_eras
+    if (a.unit_weights) {
+        for (int n = threadIdx.x; n <= E; n += blockDim.x) s_inv[n] = (n > 0) ? f_div(1.f, (float)n) : 0.f;
+        __syncthreads();
+    }
 
     const int my_i = threadIdx.x / K;
     const int my_k = threadIdx.x - my_i * K;
@@ -294,7 +302,37 @@ __global__ void __launch_bounds__(kChainThreads) chain_kernel(ChainArgs a) {
         float wsum = 0.f, mean = 0.f, m2 = 0.f, a_num = 0.f, a_den = 0.f;
         const float2* gw = s.gw + ((size_t)f * E * s.node_stride + node) * K + my_k;
         const size_t e_stride = (size_t)s.node_stride * K;
-        if (!use_dir) {
+        if (!use_dir && a.unit_weights) {
+            // Every era weight is 0 or 1 (era_alpha == 0), so the running weight sum is a small
+            // integer n and the Welford factor w / n is either 0 or the correctly rounded 1 / n,
+            // which is read from a table built once per CTA: no division on the recursion.
+            constexpr int kChunk = 16;
+            float2 cur[kChunk], nxt[kChunk];
+#pragma unroll
+            for (int q = 0; q < kChunk; ++q)
+                cur[q] = (q < E) ? gw[(size_t)q * e_stride] : make_float2(0.f, 0.f);
+            int n_valid = 0;
+            for (int e = 0; e < E; e += kChunk) {
+#pragma unroll
+                for (int q = 0; q < kChunk; ++q) {
+                    const int en = e + kChunk + q;
+                    nxt[q] = (en < E) ? gw[(size_t)en * e_stride] : make_float2(0.f, 0.f);
+                }
+#pragma unroll
+                for (int q = 0; q < kChunk; ++q) {
+                    const float gn = cur[q].x, w = cur[q].y;
+                    const bool on = w > 0.f;
+                    n_valid += on ? 1 : 0;
+                    const float fac = on ? s_inv[n_valid] : 0.f;
+                    const float delta = f_sub(gn, mean);
+                    mean = f_add(mean, f_mul(fac, delta));
+                    m2 = f_add(m2, f_mul(f_mul(w, delta), f_sub(gn, mean)));
+                }
+#pragma unroll
+                for (int q = 0; q < kChunk; ++q) cur[q] = nxt[q];
+            }
+            wsum = (float)n_valid;
+        } else if (!use_dir) {
             // Chunks of kChunk eras: the running weight sums are a short dependent chain of adds,
             // the kChunk divisions w / wsum are independent of each other (the scheduler overlaps
             // them), and only the mean / M2 updates form the long dependent chain.  The next
@@ -467,7 +505,8 @@ int launch_score(const ScoreLaunch& s, cudaStream_t stream) {
     if (npc < 1) npc = 1;
     if (npc > s.n_nodes_max) npc = s.n_nodes_max;
     c.nodes_per_cta = npc;
-    const size_t smem = (size_t)npc * K * 16;
+    c.unit_weights = (s.era_alpha <= 0.f && s.n_eras < kInvTable) ? 1 : 0;
+    const size_t smem = (size_t)npc * K * 16 + (c.unit_weights ? (size_t)(s.n_eras + 1) * 4 : 0);
     dim3 grid((unsigned)s.n_feat, (unsigned)((s.n_nodes_max + npc - 1) / npc));
     if (grid.y > 65535u) return fail_arg("scorer grid too large");
     const int threads = ((npc * K + 31) / 32) * 32;
