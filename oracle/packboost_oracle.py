@@ -735,3 +735,35 @@ def fit(
     return OracleModel(params=p, trees=trees, bin_edges=edges, tree_weight=lr32,
                        train_preds=preds.numpy().copy(), depth_records=depth_records,
                        round_seconds=round_seconds, wide=wide)
+
+
+def near_tie_gaps(X, y, era, p: OracleParams, num_rounds: int) -> np.ndarray:
+    """Relative gap between the best and the second-best distinct score of every node split
+    during ``fit``.  The CUDA path sums gradients exactly while this oracle (like the
+    reference) sums them sequentially in float32, so two candidates whose scores differ by
+    less than that rounding noise (~1e-6 relative) may be ranked differently; parity tests on
+    split structure use inputs whose smallest gap is well above it and assert so."""
+    global find_splits
+    inner = find_splits
+    gaps: list[float] = []
+
+    def spy(node_rows, node_eras, grad, hess, codes, subset, n_eras, params, trace=None):
+        tr: dict = {}
+        out = inner(node_rows, node_eras, grad, hess, codes, subset, n_eras, params, trace=tr)
+        for ctx in range(len(tr.get("context_nodes", []))):
+            sc = torch.cat([b["score"][ctx].reshape(-1) for b in tr["blocks"]])
+            sc = sc[torch.isfinite(sc)]
+            if sc.numel() < 2:
+                continue
+            top = sc.max()
+            rest = sc[sc < top]
+            if rest.numel():
+                gaps.append(float((top - rest.max()) / max(abs(float(top)), 1e-30)))
+        return out
+
+    find_splits = spy
+    try:
+        fit(X, y, era, p, num_rounds)
+    finally:
+        find_splits = inner
+    return np.asarray(gaps, dtype=np.float64)

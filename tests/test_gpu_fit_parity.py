@@ -146,3 +146,78 @@ def test_wrapper_and_predictor_roundtrip(tmp_path):
     p = PackBoostPredictor.load(path)
     np.testing.assert_array_equal(p.predict(Xh).view(np.int32), m.predict(Xh).view(np.int32))
     assert m.score(X, y) > 0.3
+
+
+def _compare_with_oracle(X, y, era, cfg, rounds, env=None):
+    model = po.fit(X, y, era, po.OracleParams(**cfg, **(env or {})), rounds)
+    booster = _fit_gpu(X, y, era, cfg, rounds)
+    off_o, cols_o = flatten_oracle(model.trees)
+    off_g, cols_g = flatten_trees(booster.trees)
+    np.testing.assert_array_equal(off_g, off_o)
+    for k in ("feature", "threshold", "left", "right", "is_leaf"):
+        np.testing.assert_array_equal(cols_g[k], cols_o[k], err_msg=k)
+    codes_train, _ = po.preprocess(X, po.OracleParams(**cfg, **(env or {})))
+    populated = populated_leaves(off_o, cols_o, codes_train)
+    assert_values_close(cols_g["value"], cols_o["value"], cols_o["is_leaf"] & populated)
+    scale = np.abs(model.train_preds).max()
+    np.testing.assert_allclose(booster.train_predictions(), model.train_preds, rtol=1e-5, atol=1e-5 * scale)
+    return booster, model
+
+
+def test_deep_frontier_matches_oracle():
+    """Reduced stand-in for the deep-frontier configuration: depth 9 (up to 256 live nodes),
+    128 bins, all features per depth; exercises the shared-cell histogram kernel, node
+    chunking and the many-bin scorer path."""
+    from packboost_b200 import workloads
+    w = workloads.config4(seed=11, n_rows=40_000, n_features=24, n_eras=4, num_rounds=2, max_bins=128, tree_depth=6)
+    cfg = dict(w.config)
+    cfg.update(pack_size=2, max_depth=9, learning_rate=0.1, min_samples_leaf=30, lambda_l2=1.0)
+    # structure can only be compared where no two candidates are closer than the float32 summation
+    # noise of the CPU path (see oracle.near_tie_gaps); this input keeps a 10x margin
+    assert po.near_tie_gaps(w.X, w.y, w.era, po.OracleParams(**cfg), 2).min() > 1e-5
+    booster, _ = _compare_with_oracle(w.X, w.y, w.era, cfg, 2)
+    assert max(len(t.nodes) for t in booster.trees) > 400
+
+
+def test_mixed_columns_matches_oracle():
+    """Reduced stand-in for the mixed-column configuration (Gaussian / log-normal / integer-valued
+    columns, era-dependent sign flips), 128 bins, depth 6."""
+    from packboost_b200 import workloads
+    w = workloads.config2(seed=7, n_rows=30_000, n_features=40, n_eras=15, num_rounds=3)
+    cfg = dict(w.config)
+    cfg.update(pack_size=4, learning_rate=0.1)
+    _compare_with_oracle(w.X, w.y, w.era, cfg, 3)
+
+
+def test_small_workspace_forces_feature_blocks():
+    """With a workspace that holds only a few features of histogram the per-depth pass loops over
+    feature blocks; the trees must not change."""
+    X, y, era, cfg, rounds, Xh = cases.CASES["config1"]()
+    ref = _fit_gpu(X, y, era, cfg, 2)
+    os.environ["PACKBOOST_WORKSPACE_BYTES"] = str(24 << 20)
+    try:
+        small = _fit_gpu(X, y, era, cfg, 2)
+    finally:
+        del os.environ["PACKBOOST_WORKSPACE_BYTES"]
+    _, ca = flatten_trees(ref.trees)
+    _, cb = flatten_trees(small.trees)
+    for k in ca:
+        a, b = (ca[k].view(np.int64), cb[k].view(np.int64)) if k == "value" else (ca[k], cb[k])
+        np.testing.assert_array_equal(a, b)
+
+
+def test_wide_bins_match_widened_oracle():
+    """255 bins: the reference refuses more than 128 (int8 storage); with the guard lifted on both
+    sides (8-bit codes here, int16 codes in the oracle) the trees agree."""
+    rng = np.random.default_rng(12)
+    n = 6000
+    X = rng.normal(size=(n, 6)).astype(np.float32)
+    y = (np.sin(2 * X[:, 0]) + X[:, 1] * X[:, 2] + 0.1 * rng.standard_normal(n)).astype(np.float32)
+    era = (np.arange(n) // 1000).astype(np.int16)
+    cfg = dict(pack_size=2, max_depth=4, learning_rate=0.2, lambda_l2=1.0, lambda_dro=0.2, min_samples_leaf=10,
+               max_bins=255, random_state=3)
+    os.environ["PACKBOOST_ALLOW_WIDE_BINS"] = "1"
+    try:
+        _compare_with_oracle(X, y, era, cfg, 2, env=dict(allow_wide_bins=True))
+    finally:
+        del os.environ["PACKBOOST_ALLOW_WIDE_BINS"]
