@@ -141,7 +141,7 @@ def pick_sample_eras(steps, warmup, n_eras, budget_s=90.0, per_era_round_s=0.2):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="packboost_b200", choices=["packboost_b200", "reference"])
     ap.add_argument("--scale", type=float, default=1.0, help="row/era scale of the workload (profiling captures use < 1)")
@@ -247,6 +247,10 @@ def main():
         peak_src = "measured (MEASURED_PEAKS.json hbm_gbs)"
     else:
         peak, peak_src = 6650.0, "fallback"
+    # DRAM bytes per histogram launch from the ncu capture of the 1/10-scale case (33.85 MB read +
+    # written at 269 952 rows), scaled by rows: traffic is proportional to rows x sampled features
+    traffic = 33.85e6 * (n_rows / 269952.0) / world
+    traffic_src = "ncu dram__bytes_read+write of the 1/10-scale capture (profiles/hist_lane_kernel_config3_small.md) scaled by rows"
     phases = {"hist_ms_per_step": hist_ms / args.steps, "score_ms_per_step": float(ms5[1]) / args.steps,
               "select_ms_per_step": float(ms5[2]) / args.steps, "partition_ms_per_step": float(ms5[3]) / args.steps,
               "round_begin_ms_per_step": float(ms5[4]) / args.steps}
@@ -298,8 +302,9 @@ def main():
     line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "int64", "data": "synthetic", "config": config,
-            "roofline": {"bound": "hbm", "kernel": "hist_kernel<4>", "achieved": achieved, "peak": peak, "unit": "GB/s",
-                         "frac": achieved / peak, "traffic": None, "peak_source": peak_src,
+            "roofline": {"bound": "hbm", "kernel": "hist_lane_kernel", "achieved": achieved, "peak": peak, "unit": "GB/s",
+                         "frac": achieved / peak, "traffic": traffic, "traffic_source": traffic_src,
+                         "peak_source": peak_src,
                          "launches": hist_launches, "avg_launch_ms": hist_ms / max(hist_launches, 1),
                          "algorithmic_bytes_per_launch": hist_bytes / max(hist_launches, 1)},
             "cpu_baseline": cpu_baseline, "e2e": e2e, "gpu_launches": launches, "clocks": clocks, "phases": phases,

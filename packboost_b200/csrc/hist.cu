@@ -441,16 +441,26 @@ int launch_hist(const HistLaunch& h, cudaStream_t stream) {
     // lane-private kernel when a lane's cells are few: tuples of A features (joint code) as wide as
     // the cells allow, then T tuples per lane while shared memory lasts (A * T <= 4)
     if (h.code_bits == 4 && (int64_t)h.n_nodes * h.max_bins * kLaneCellBytes <= kLaneSmemMax) {
-        int arity = 1;
+        // Pick the tuple width A (joint code) and the tuples per lane T that minimise the
+        // shared-memory pipe time: a row step costs about one record load plus two atomics per
+        // tuple, and a launch walks the rows once per block of 32*A*T features.
+        const int cap = h.max_arity < 2 ? h.max_arity : 2;
+        int arity = 1, tuples = 1;
         int64_t cpn = h.max_bins;
-        const int cap = h.max_arity < 3 ? h.max_arity : 3;
-        while (arity < cap && (int64_t)h.n_nodes * cpn * h.max_bins * kLaneCellBytes <= kLaneSmemMax) {
-            cpn *= h.max_bins;
-            ++arity;
+        double best = 1e30;
+        {
+            int64_t c = h.max_bins;
+            for (int a_try = 1; a_try <= cap; ++a_try, c *= h.max_bins) {
+                for (int t_try = 1; t_try * a_try <= 4; t_try *= 2) {
+                    const size_t bytes = (size_t)h.n_nodes * c * kLaneCellBytes * t_try;
+                    if (bytes > (size_t)kLaneSmemMax) continue;
+                    const int blocks = (h.n_feat + 32 * a_try * t_try - 1) / (32 * a_try * t_try);
+                    const double cost = blocks * (2.2 + 5.6 * t_try);
+                    if (cost < best - 1e-9) { best = cost; arity = a_try; tuples = t_try; cpn = c; }
+                }
+            }
         }
         const size_t slot = (size_t)h.n_nodes * cpn * kLaneCellBytes;
-        int tuples = (arity == 3) ? 1 : 4 / arity;
-        while (tuples > 1 && (slot * tuples > (size_t)kLaneSmemMax || 32 * arity * tuples > 2 * h.n_feat)) tuples /= 2;
         a.nodes_per_chunk = h.n_nodes;
         a.feats_per_cta = 32 * arity * tuples;
         a.group = arity;
