@@ -292,6 +292,18 @@ int pb_predict_rows(const uint8_t* codes, int64_t n_rows, int64_t pitch_row, int
                     const int32_t* tree_offsets, const int32_t* repeat, int64_t n_trees,
                     float weight, float* out, const float* init, void* stream);
 
+/* Same ensemble sum with the trees in the packed form the training loop can produce directly:
+ * one 8-byte record per node, word 0 = feature (bits 0-15) | threshold (bits 16-23) | leaf flag
+ * (bit 31), word 1 = tree-relative index of the left child (the right child is the next node,
+ * as in the BFS-compact numbering of packboost/booster.py:181-187) or the float bits of a leaf
+ * value.  Requires feature ids < 65536 and thresholds < 256.  `max_tree_nodes` is the node count
+ * of the largest tree: trees of up to 512 nodes are streamed through shared memory in batches,
+ * larger ones are read from global memory. */
+int pb_predict_rows_packed(const uint8_t* codes, int64_t n_rows, int64_t pitch_row, int64_t code_bits,
+                           const void* nodes, const int32_t* tree_offsets, const int32_t* repeat,
+                           int64_t n_trees, int64_t max_tree_nodes, float weight, float* out,
+                           const float* init, void* stream);
+
 /* Single tree over feature-major uint8 codes `bins[F][N]`: the argument list of
  * predict_bins_cuda (packboost/backends/cuda/frontier_cuda.cu:853-861). */
 int pb_predict_bins_fm(const uint8_t* bins, int64_t n_features, int64_t n_rows,

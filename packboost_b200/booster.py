@@ -671,6 +671,18 @@ class PackBoost:
         out["offsets"] = torch.from_numpy(offs).to(self._device)
         out["repeat"] = torch.tensor([r for _, r in distinct], dtype=torch.int32, device=self._device)
         out["n_trees"] = len(arrs)
+        # packed 8-byte nodes when the trees allow it (right child == left child + 1, small ids)
+        internal = cat["is_leaf"] == 0
+        ok = (bool(np.all(cat["right"][internal] == cat["left"][internal] + 1))
+              and (cat["feature"][internal].max(initial=0) < 65536) and (cat["threshold"][internal].max(initial=0) < 256)
+              and (cat["threshold"][internal].min(initial=0) >= 0))
+        if ok:
+            w0 = np.where(internal, (cat["feature"].astype(np.int64) & 0xFFFF) | ((cat["threshold"].astype(np.int64) & 0xFF) << 16),
+                          1 << 31).astype(np.uint32)
+            w1 = np.where(internal, cat["left"].astype(np.int64) & 0xFFFFFFFF,
+                          cat["value"].astype(np.float32).view(np.uint32).astype(np.int64)).astype(np.uint32)
+            out["packed"] = torch.from_numpy(np.stack([w0, w1], axis=1).view(np.int32).copy()).to(self._device)
+            out["max_tree_nodes"] = int(np.diff(offs).max()) if len(arrs) else 1
         return out
 
     def _predict_packed(self, rows: PackedRows, forest: dict, init: torch.Tensor | None = None) -> torch.Tensor:
@@ -678,6 +690,13 @@ class PackBoost:
         if rows.n_rows == 0:
             return out
         f = forest
+        if "packed" in f:
+            B.check(B.lib().pb_predict_rows_packed(
+                rows.codes.data_ptr(), rows.n_rows, rows.pitch_row, rows.code_bits, f["packed"].data_ptr(),
+                f["offsets"].data_ptr(), f["repeat"].data_ptr(), f["n_trees"], f["max_tree_nodes"],
+                float(self._tree_weight),
+                out.data_ptr(), B._ptr(init) if init is not None else 0, torch.cuda.current_stream().cuda_stream))
+            return out
         B.check(B.lib().pb_predict_rows(
             rows.codes.data_ptr(), rows.n_rows, rows.pitch_row, rows.code_bits, f["feature"].data_ptr(),
             f["threshold"].data_ptr(), f["left"].data_ptr(), f["right"].data_ptr(), f["value"].data_ptr(),

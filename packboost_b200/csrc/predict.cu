@@ -67,6 +67,147 @@ __global__ void __launch_bounds__(128) predict_rows_kernel(PredictRowsArgs a) {
     }
 }
 
+// Packed ensemble: one 8-byte word pair per node,
+//   x = feature (bits 0-15) | threshold (bits 16-23) | leaf flag (bit 31)
+//   y = tree-relative index of the left child (the right child is the next node, which is how
+//       the trees are numbered when they are grown) or, for a leaf, the bits of its float value.
+// A thread owns one row and walks kWay trees at a time so that their dependent node loads
+// overlap; the leaf terms are still added in tree order.
+struct PredictPackedArgs {
+    const uint8_t* codes;
+    int64_t n_rows;
+    int64_t pitch_row;
+    const uint2* nodes;
+    const int32_t* tree_offsets;
+    const int32_t* repeat;
+    int n_trees;
+    float weight;
+    float* out;
+    const float* init;
+    int rows_per_cta;
+    int stage;
+    int trees_per_batch;
+};
+
+// kTpr threads share a row (they sit in the same warp): thread q walks trees t0+q, t0+kTpr+q, ...
+// of each group of kTpr*kWay consecutive trees, kWay at a time so that their dependent node
+// loads overlap, and the leaf terms are then added in tree order by passing them to the row's
+// first thread with shuffles — the float32 sum stays the sequential one.
+constexpr int kTpr = 4;
+constexpr int kWay = 2;
+
+constexpr int kStageNodes = 4096;  // nodes per staged batch of trees (32 KB), two buffers
+
+__device__ __forceinline__ void cp_async8(void* smem_dst, const void* gmem_src) {
+    const unsigned d = (unsigned)__cvta_generic_to_shared(smem_dst);
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 8;\n" ::"r"(d), "l"(gmem_src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory"); }
+
+// The CTA keeps its rows' codes in shared memory and streams the ensemble through two
+// shared-memory buffers in batches of `trees_per_batch` trees (asynchronous 8-byte copies, the
+// next batch in flight while the current one is walked), so a node visit is two shared-memory
+// loads instead of a cache-line lookup per lane.
+template <int BITS>
+__global__ void __launch_bounds__(512) predict_rows_packed_kernel(PredictPackedArgs a) {
+    extern __shared__ __align__(16) uint8_t s_rows[];
+    const int64_t row0 = (int64_t)blockIdx.x * a.rows_per_cta;
+    const int nr = (int)min((int64_t)a.rows_per_cta, a.n_rows - row0);
+    if (nr <= 0) return;
+    uint2* s_nodes = reinterpret_cast<uint2*>(s_rows + (size_t)a.rows_per_cta * a.pitch_row * (a.stage ? 1 : 0));
+    if (a.stage) {
+        const int64_t n16 = (int64_t)nr * a.pitch_row / 16;
+        const uint4* src = reinterpret_cast<const uint4*>(a.codes + row0 * a.pitch_row);
+        uint4* dst = reinterpret_cast<uint4*>(s_rows);
+        for (int64_t i = threadIdx.x; i < n16; i += blockDim.x) dst[i] = __ldg(src + i);
+    }
+    const int TB = a.trees_per_batch;  // 0: trees too large to stage, nodes are read from global memory
+    const int q = threadIdx.x % kTpr;
+    const int lane = threadIdx.x & 31;
+    const int quad_base = lane - q;  // lane of the row's first thread
+    const int rows_per_pass = blockDim.x / kTpr;
+    const int n_batches = TB ? (a.n_trees + TB - 1) / TB : 1;
+
+    auto prefetch = [&](int b) {
+        const int ta = b * TB, tb = min(a.n_trees, ta + TB);
+        const int o0 = __ldg(a.tree_offsets + ta), o1 = __ldg(a.tree_offsets + tb);
+        uint2* dst = s_nodes + (size_t)(b & 1) * kStageNodes;
+        for (int i = threadIdx.x; i < o1 - o0; i += blockDim.x) cp_async8(dst + i, a.nodes + o0 + i);
+        cp_async_commit();
+    };
+
+    // every warp runs the same number of passes, batches and tree groups, so the shuffles below
+    // always see all 32 lanes; threads whose row is past the end compute on row 0 and do not store
+    for (int lr0 = 0; lr0 < nr; lr0 += rows_per_pass) {
+        const int lr_raw = lr0 + threadIdx.x / kTpr;
+        const bool has_row = lr_raw < nr;
+        const int lr = has_row ? lr_raw : 0;
+        const uint8_t* row = a.stage ? (s_rows + (int64_t)lr * a.pitch_row) : (a.codes + (row0 + lr) * a.pitch_row);
+        float acc = a.init ? a.init[row0 + lr] : 0.f;
+        if (TB) prefetch(0);
+        for (int b = 0; b < n_batches; ++b) {
+            const int ta = TB ? b * TB : 0, tb = TB ? min(a.n_trees, ta + TB) : a.n_trees;
+            const uint2* node_base = a.nodes;
+            int off_shift = 0;
+            if (TB) {
+                if (b + 1 < n_batches) {
+                    prefetch(b + 1);
+                    cp_async_wait<1>();
+                } else {
+                    cp_async_wait<0>();
+                }
+                __syncthreads();  // batch b (and, on the first batch, the rows) are in shared memory
+                node_base = s_nodes + (size_t)(b & 1) * kStageNodes;
+                off_shift = __ldg(a.tree_offsets + ta);
+            } else {
+                __syncthreads();
+            }
+            for (int t0 = ta; t0 < tb; t0 += kTpr * kWay) {
+                const uint2* base[kWay];
+                uint2 nd[kWay];
+#pragma unroll
+                for (int u = 0; u < kWay; ++u) {
+                    const int t = min(t0 + u * kTpr + q, tb - 1);
+                    base[u] = node_base + (__ldg(a.tree_offsets + t) - off_shift);
+                    nd[u] = base[u][0];
+                }
+                bool any = true;
+                while (any) {
+                    any = false;
+#pragma unroll
+                    for (int u = 0; u < kWay; ++u) {
+                        if (!(nd[u].x >> 31)) {
+                            const int f = nd[u].x & 0xFFFF;
+                            const int thr = (nd[u].x >> 16) & 0xFF;
+                            const int child = (int)nd[u].y + ((code_at<BITS>(row, f) > thr) ? 1 : 0);
+                            nd[u] = base[u][child];
+                            any = true;
+                        }
+                    }
+                }
+                // ordered accumulation: tree t0 + u*kTpr + qq for u, then qq, ascending
+#pragma unroll
+                for (int u = 0; u < kWay; ++u) {
+                    const float mine = __fmul_rn(a.weight, __uint_as_float(nd[u].y));
+#pragma unroll
+                    for (int qq = 0; qq < kTpr; ++qq) {
+                        const float term = __shfl_sync(0xFFFFFFFFu, mine, quad_base + qq);
+                        const int t = t0 + u * kTpr + qq;
+                        if (t < tb) {
+                            const int rep = a.repeat ? __ldg(a.repeat + t) : 1;
+                            for (int k = 0; k < rep; ++k) acc = __fadd_rn(acc, term);
+                        }
+                    }
+                }
+            }
+            __syncthreads();  // the buffer of batch b may be overwritten by the prefetch of batch b + 2
+        }
+        if (has_row && q == 0) a.out[row0 + lr] = acc;
+    }
+}
+
 __global__ void __launch_bounds__(256) predict_bins_fm_kernel(
     const uint8_t* __restrict__ bins, int64_t n_rows, const int32_t* __restrict__ feature,
     const int32_t* __restrict__ threshold, const int32_t* __restrict__ left, const int32_t* __restrict__ right,
@@ -182,5 +323,57 @@ extern "C" int pb_predict_pack_fm(const uint8_t* bins, int64_t n_features, int64
         bins, n_rows, feature, threshold, left_abs, right_abs, value, is_leaf, offsets, (int)n_trees, tree_weight, out);
     count_launch(1);
     PB_LAUNCH_CHECK("predict_pack_fm_kernel");
+    return PB_OK;
+}
+
+extern "C" int pb_predict_rows_packed(const uint8_t* codes, int64_t n_rows, int64_t pitch_row, int64_t code_bits,
+                                      const void* nodes, const int32_t* tree_offsets, const int32_t* repeat,
+                                      int64_t n_trees, int64_t max_tree_nodes, float weight, float* out,
+                                      const float* init, void* stream_) {
+    PB_REQUIRE(codes && nodes && tree_offsets && out, "null buffer");
+    PB_REQUIRE(code_bits == 4 || code_bits == 8, "code_bits must be 4 or 8");
+    PB_REQUIRE(pitch_row >= 16 && pitch_row % 16 == 0, "pitch_row must be a positive multiple of 16");
+    PB_REQUIRE(((uintptr_t)codes % 16) == 0 && ((uintptr_t)nodes % 8) == 0, "codes / nodes are misaligned");
+    PB_REQUIRE(n_trees >= 0 && n_trees < (1ll << 31) && max_tree_nodes >= 1, "tree counts out of range");
+    if (n_rows <= 0 || n_trees == 0) {
+        if (n_rows > 0) {
+            if (init) PB_CUDA_TRY(cudaMemcpyAsync(out, init, (size_t)n_rows * 4, cudaMemcpyDeviceToDevice, (cudaStream_t)stream_));
+            else PB_CUDA_TRY(cudaMemsetAsync(out, 0, (size_t)n_rows * 4, (cudaStream_t)stream_));
+        }
+        return PB_OK;
+    }
+    cudaStream_t stream = (cudaStream_t)stream_;
+    PredictPackedArgs a{codes, n_rows, pitch_row, static_cast<const uint2*>(nodes), tree_offsets, repeat,
+                        (int)n_trees, weight, out, init, 128, 1, 0};
+    // trees per staged batch: a multiple of the group walked at once, as many as the buffer holds
+    const int group = kTpr * kWay;
+    int tb = (int)(kStageNodes / max_tree_nodes) / group * group;
+    a.trees_per_batch = tb;  // 0: no staging
+    const size_t stage_bytes = tb ? (size_t)2 * kStageNodes * sizeof(uint2) : 0;
+    const int64_t budget = 224 * 1024 - (int64_t)stage_bytes;
+    int rows = (int)(budget / pitch_row);
+    if (rows > 128) rows = 128;
+    rows = rows / 8 * 8;
+    size_t smem = stage_bytes;
+    if (rows < 8) {
+        a.stage = 0;
+        a.rows_per_cta = 128;
+    } else {
+        a.rows_per_cta = rows;
+        smem += (size_t)rows * pitch_row;
+    }
+    const unsigned grid = (unsigned)((n_rows + a.rows_per_cta - 1) / a.rows_per_cta);
+    const int threads = (a.rows_per_cta * kTpr + 31) / 32 * 32;
+    if (code_bits == 4) {
+        if (smem > 48 * 1024)
+            PB_CUDA_TRY(cudaFuncSetAttribute(predict_rows_packed_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        predict_rows_packed_kernel<4><<<grid, threads, smem, stream>>>(a);
+    } else {
+        if (smem > 48 * 1024)
+            PB_CUDA_TRY(cudaFuncSetAttribute(predict_rows_packed_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        predict_rows_packed_kernel<8><<<grid, threads, smem, stream>>>(a);
+    }
+    count_launch(1);
+    PB_LAUNCH_CHECK("predict_rows_packed_kernel");
     return PB_OK;
 }

@@ -221,3 +221,22 @@ def test_wide_bins_match_widened_oracle():
         _compare_with_oracle(X, y, era, cfg, 2, env=dict(allow_wide_bins=True))
     finally:
         del os.environ["PACKBOOST_ALLOW_WIDE_BINS"]
+
+
+def test_predict_generic_node_arrays_when_children_are_not_adjacent():
+    """Trees whose right child is not stored right after the left one cannot use the packed node
+    form; the array-based predictor must give the same answer as the CPU router."""
+    from packboost_b200 import PackBoost, PackBoostConfig
+    from packboost_b200.booster import Tree, TreeNode
+    rng = np.random.default_rng(8)
+    codes = rng.integers(0, 5, size=(500, 7), dtype=np.uint8)
+    nodes = [TreeNode(3, 1, 2, 1, 0.0, False), TreeNode(-1, 0, -1, -1, 0.7, True), TreeNode(5, 2, 4, 3, 0.0, False),
+             TreeNode(-1, 0, -1, -1, -0.2, True), TreeNode(-1, 0, -1, -1, 0.4, True)]
+    tree = Tree(nodes=nodes)
+    b = PackBoost(PackBoostConfig(device="cuda", pack_size=1, max_bins=5, prebinned=True))
+    b.set_forest([tree, tree], 0.3, repeats=[2, 1])
+    arr = {k: (v.astype(np.float64) if k == "value" else v) for k, v in tree.arrays().items()}
+    arr["is_leaf"] = arr["is_leaf"].astype(bool)
+    want = po.predict_codes([arr] * 3, codes.astype(np.int8), 0.3)
+    np.testing.assert_array_equal(b.predict(codes).view(np.int32), want.view(np.int32))
+    assert "packed" not in b._forest_cache
