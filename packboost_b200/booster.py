@@ -175,11 +175,12 @@ class _DeviceTrainer:
 
     def __init__(self, cfg: PackBoostConfig, matrix: PackedMatrix, y_sorted: np.ndarray, era_offsets: np.ndarray,
                  n_features_total: int, feat_local: np.ndarray, rank: int, world: int,
-                 workspace_bytes: int | None = None):
+                 workspace_bytes: int | None = None, replicated: bool = False):
         self.cfg = cfg
         self.lib = B.lib()
         self.dev = matrix.codes.device
         self.rank, self.world = rank, world
+        self.replicated = bool(replicated)  # every rank holds all feature rows (see PackBoost._start)
         self.matrix = matrix
         n = matrix.n_rows
         npad = matrix.rows_padded
@@ -203,7 +204,8 @@ class _DeviceTrainer:
         self.gq = torch.zeros(npad, dtype=torch.int32, device=self.dev)
         self.slot = torch.full((npad,), -1, dtype=torch.int16, device=self.dev)  # 0xFFFF: no slot
         self.leaf = torch.zeros(npad, dtype=torch.int16, device=self.dev)
-        self.bits = torch.zeros(npad // 32, dtype=torch.int32, device=self.dev) if world > 1 else None
+        self.bits = (torch.zeros(npad // 32, dtype=torch.int32, device=self.dev)
+                     if (world > 1 and not replicated) else None)
         self.ctl = torch.zeros(int(self.lib.pb_ctl_bytes()), dtype=torch.uint8, device=self.dev)
 
         st = B.TrainState()
@@ -285,6 +287,8 @@ class _DeviceTrainer:
             s = subsets[d]
             fh[d, 0, :k] = torch.from_numpy(s)
             rows, pos = local_part(s, self.rank, self.world)
+            if self.replicated and self.world > 1:
+                rows = s[pos].astype(np.int32)  # all feature rows are held locally: row == feature id
             n_local.append(int(pos.shape[0]))
             fh[d, 1, : pos.shape[0]] = torch.from_numpy(rows)
             fh[d, 2, : pos.shape[0]] = torch.from_numpy(pos)
@@ -300,7 +304,7 @@ class _DeviceTrainer:
             if self.world > 1:
                 self._allreduce_candidates(d, k)
             B.check(lib.pb_depth_select(st, d, sampled, k, stream))
-            if self.world > 1:
+            if self.world > 1 and not self.replicated:
                 B.check(lib.pb_depth_goleft_bits(st, d, self.bits.data_ptr(), stream))
                 torch.distributed.all_reduce(self.bits, op=torch.distributed.ReduceOp.SUM)
                 B.check(lib.pb_depth_apply_bits(st, d, self.bits.data_ptr(), stream))
@@ -502,13 +506,27 @@ class PackBoost:
         rank, world = 0, 1
         if torch.distributed.is_available() and torch.distributed.is_initialized():
             rank, world = torch.distributed.get_rank(), torch.distributed.get_world_size()
-        feat_local = feature_map(F, rank, world)
+        # With several GPUs every rank histograms and scores only the features it owns
+        # (feature % world == rank).  When the whole packed matrix fits comfortably in one GPU's
+        # memory it is kept on every rank anyway: each rank can then route rows itself and the
+        # per-depth go-left bitmask exchange disappears (one all-reduce per depth instead of two).
+        # PACKBOOST_SHARD_CODES=1 forces the memory-sharded layout.
+        replicate = False
+        if world > 1 and os.getenv("PACKBOOST_SHARD_CODES") != "1":
+            bits = code_bits_for(cfg.max_bins)
+            free, _tot = torch.cuda.mem_get_info(self._device)
+            replicate = (N * F * bits // 8) < 0.25 * free
+        if world > 1 and not replicate:
+            feat_local = feature_map(F, rank, world)
+        else:
+            feat_local = feature_map(F, 0, 1)
         n_local = int((feat_local >= 0).sum())
         matrix = pack_feature_major(X_src, edges, cfg.max_bins, row_order=order,
-                                    feature_map=feat_local if world > 1 else None, n_features_local=n_local,
-                                    validate_codes=validate_on_device)
+                                    feature_map=feat_local if (world > 1 and not replicate) else None,
+                                    n_features_local=n_local, validate_codes=validate_on_device)
         y_sorted = y_np if order is None else y_np[order]
-        self._trainer = _DeviceTrainer(cfg, matrix, y_sorted, era_offsets, F, feat_local, rank, world)
+        self._trainer = _DeviceTrainer(cfg, matrix, y_sorted, era_offsets, F, feat_local, rank, world,
+                                       replicated=replicate)
         self._row_order = order
         self._fit_ctx = {"era_sorted": era_sorted, "y_sorted": y_sorted, "F": F}
 

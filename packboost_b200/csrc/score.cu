@@ -68,6 +68,7 @@ __device__ __forceinline__ float2 gain_of(uint32_t lc, long long lgq, uint32_t t
 }
 
 // ---- few bins: a thread scans the bins of its (era, node) in registers ---------------------------
+template <int KT>  // compile-time bound of the threshold count
 __global__ void __launch_bounds__(kGainThreads) gain_kernel_small(GainArgs a) {
     const ScoreLaunch& s = a.s;
     __shared__ uint32_t s_lc[32 * kSmallBins];
@@ -93,13 +94,13 @@ __global__ void __launch_bounds__(kGainThreads) gain_kernel_small(GainArgs a) {
     const int e_per = (E + a.era_splits - 1) / a.era_splits;
     const int e_begin = blockIdx.z * e_per;
     const int e_end = min(E, e_begin + e_per);
-    int thr[kSmallBins];
+    int thr[KT];
 #pragma unroll
-    for (int k = 0; k < kSmallBins; ++k) thr[k] = (k < K) ? s.thr_ids[k] : 0;
-    uint32_t lc_sum[kSmallBins];
-    long long lg_sum[kSmallBins];
+    for (int k = 0; k < KT; ++k) thr[k] = (k < K) ? s.thr_ids[k] : 0;
+    uint32_t lc_sum[KT];
+    long long lg_sum[KT];
 #pragma unroll
-    for (int k = 0; k < kSmallBins; ++k) {
+    for (int k = 0; k < KT; ++k) {
         lc_sum[k] = 0u;
         lg_sum[k] = 0ll;
     }
@@ -107,8 +108,15 @@ __global__ void __launch_bounds__(kGainThreads) gain_kernel_small(GainArgs a) {
     if (node < n_nodes) {
         for (int e = e_begin + e_lane; e < e_end; e += e_step) {
             const size_t base = (((size_t)f * E + e) * s.node_stride + node) * NB;
-            uint32_t pc[kSmallBins];
-            long long pg[kSmallBins];
+            // running prefix over the bins; threshold k keeps the prefix at its bin (selects with
+            // static indices, so everything stays in registers)
+            uint32_t lcs[KT];
+            long long lgs[KT];
+#pragma unroll
+            for (int k = 0; k < KT; ++k) {
+                lcs[k] = 0u;
+                lgs[k] = 0ll;
+            }
             uint32_t c = 0;
             long long g = 0;
 #pragma unroll
@@ -116,9 +124,13 @@ __global__ void __launch_bounds__(kGainThreads) gain_kernel_small(GainArgs a) {
                 if (b < NB) {
                     c += s.cnt[base + b];
                     g += s.gsum[base + b];
+#pragma unroll
+                    for (int k = 0; k < KT; ++k) {
+                        const bool at = (k < K) && (thr[k] == b);
+                        lcs[k] = at ? c : lcs[k];
+                        lgs[k] = at ? g : lgs[k];
+                    }
                 }
-                pc[b] = c;
-                pg[b] = g;
             }
             const uint32_t tc = c;
             const float tg = f_mul(__ll2float_rn(g), inv_scale);
@@ -126,28 +138,43 @@ __global__ void __launch_bounds__(kGainThreads) gain_kernel_small(GainArgs a) {
             const float parent = f_div(f_mul(0.5f, f_mul(tg, tg)), f_add(th, lam));
             const float w_era = (tc == 0) ? 0.f : ((s.era_alpha > 0.f) ? f_add((float)tc, s.era_alpha) : 1.f);
             float2* out = s.gw + (((size_t)f * E + e) * s.node_stride + node) * K;
+            float2 gk[KT];
 #pragma unroll
-            for (int k = 0; k < kSmallBins; ++k) {
+            for (int k = 0; k < KT; ++k) {
                 if (k < K) {
-                    uint32_t lc = 0;
-                    long long lgq = 0;
-#pragma unroll
-                    for (int b = 0; b < kSmallBins; ++b)
-                        if (b == thr[k]) {
-                            lc = pc[b];
-                            lgq = pg[b];
-                        }
-                    out[k] = gain_of(lc, lgq, tc, tg, th, parent, inv_scale, lam, w_era);
+                    const uint32_t lc = lcs[k];
+                    const long long lgq = lgs[k];
+                    gk[k] = gain_of(lc, lgq, tc, tg, th, parent, inv_scale, lam, w_era);
                     lc_sum[k] += lc;
                     lg_sum[k] += lgq;
                 }
             }
-        }
+            if ((K & 1) == 0) {  // rows of an even K start on 16 bytes
 #pragma unroll
-        for (int k = 0; k < kSmallBins; ++k) {
-            if (k < K) {
-                if (lc_sum[k]) atomicAdd(&s_lc[nl * K + k], lc_sum[k]);
-                if (lg_sum[k]) atomicAdd(&s_lg[nl * K + k], (unsigned long long)lg_sum[k]);
+                for (int k = 0; k < KT; k += 2)
+                    if (k < K)
+                        reinterpret_cast<float4*>(out)[k >> 1] = make_float4(gk[k].x, gk[k].y, gk[k + 1].x, gk[k + 1].y);
+            } else {
+#pragma unroll
+                for (int k = 0; k < KT; ++k)
+                    if (k < K) out[k] = gk[k];
+            }
+        }
+    }
+    // threads of a warp that share a node (lanes a multiple of npc apart) are summed with shuffles
+    // first, so that only npc lanes per warp touch the shared accumulators
+#pragma unroll
+    for (int k = 0; k < KT; ++k) {
+        if (k < K) {
+            uint32_t c = lc_sum[k];
+            long long g = lg_sum[k];
+            for (int off = 16; off >= npc; off >>= 1) {
+                c += __shfl_xor_sync(0xFFFFFFFFu, c, off);
+                g += __shfl_xor_sync(0xFFFFFFFFu, g, off);
+            }
+            if ((threadIdx.x & 31) < npc) {
+                if (c) atomicAdd(&s_lc[nl * K + k], c);
+                if (g) atomicAdd(&s_lg[nl * K + k], (unsigned long long)g);
             }
         }
     }
@@ -259,6 +286,7 @@ struct ChainArgs {
     ScoreLaunch s;
     int nodes_per_cta;
     int unit_weights;  // 1: era weights are 0/1 and n_eras fits the reciprocal table
+    int era_chunk;     // eras per staged chunk of the (gain, weight) table
 };
 
 constexpr int kInvTable = 4096;
@@ -272,141 +300,23 @@ __device__ __forceinline__ void welford_step(float gn, float w, float& wsum, flo
     wsum = wsum_new;
 }
 
-__global__ void __launch_bounds__(kChainThreads) chain_kernel(ChainArgs a) {
-    const ScoreLaunch& s = a.s;
-    extern __shared__ unsigned char smem_raw[];
-    const int n_nodes = min(*s.n_nodes_ptr, s.n_nodes_max);
-    const int npc = a.nodes_per_cta;
-    const int node0 = blockIdx.y * npc;
-    if (node0 >= n_nodes) return;
-    const int nn = min(npc, n_nodes - node0);
-    const int f = blockIdx.x;
-    const int E = s.n_eras, K = s.n_thr;
-    const float lam = s.lambda_l2;
-    const bool use_dir = (s.direction_weight != 0.f) && (*s.any_dir_ptr != 0);
+__device__ __forceinline__ void cp_async8(void* smem_dst, const void* gmem_src) {
+    const unsigned d = (unsigned)__cvta_generic_to_shared(smem_dst);
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 8;\n" ::"r"(d), "l"(gmem_src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory"); }
 
-    long long* res_lg = reinterpret_cast<long long*>(smem_raw);
-    float* res_score = reinterpret_cast<float*>(res_lg + (size_t)npc * K);
-    uint32_t* res_cnt = reinterpret_cast<uint32_t*>(res_score + (size_t)npc * K);
-    float* s_inv = reinterpret_cast<float*>(res_cnt + (size_t)npc * K);  // s_inv[n] = 1/n, n <= n_eras
-    if (a.unit_weights) {
-        for (int n = threadIdx.x; n <= E; n += blockDim.x) s_inv[n] = (n > 0) ? f_div(1.f, (float)n) : 0.f;
-        __syncthreads();
-    }
-
-    const int my_i = threadIdx.x / K;
-    const int my_k = threadIdx.x - my_i * K;
-    const bool scorer = (threadIdx.x < nn * K);
+// Final score of every (node, threshold) slot of a CTA, the global min_samples_leaf mask and the
+// best threshold of each node (max score, then max left count, then max k).  Called by all
+// threads of the CTA; slot threads are the first nn * K.
+__device__ __forceinline__ void finish_pairs(const ScoreLaunch& s, int f, int node0, int nn, bool scorer, int my_i,
+                                             int my_k, float wsum, float mean, float m2, bool use_dir, float a_num,
+                                             float a_den, float* res_score, uint32_t* res_cnt, long long* res_lg) {
+    const int K = s.n_thr;
+    const int node = node0 + (scorer ? my_i : 0);
     if (scorer) {
-        const int node = node0 + my_i;
-        float wsum = 0.f, mean = 0.f, m2 = 0.f, a_num = 0.f, a_den = 0.f;
-        const float2* gw = s.gw + ((size_t)f * E * s.node_stride + node) * K + my_k;
-        const size_t e_stride = (size_t)s.node_stride * K;
-        if (!use_dir && a.unit_weights) {
-            // Every era weight is 0 or 1 (era_alpha == 0), so the running weight sum is a small
-            // integer n and the Welford factor w / n is either 0 or the correctly rounded 1 / n,
-            // which is read from a table built once per CTA: no division on the recursion.
-            constexpr int kChunk = 16;
-            float2 cur[kChunk], nxt[kChunk];
-#pragma unroll
-            for (int q = 0; q < kChunk; ++q)
-                cur[q] = (q < E) ? gw[(size_t)q * e_stride] : make_float2(0.f, 0.f);
-            int n_valid = 0;
-            for (int e = 0; e < E; e += kChunk) {
-#pragma unroll
-                for (int q = 0; q < kChunk; ++q) {
-                    const int en = e + kChunk + q;
-                    nxt[q] = (en < E) ? gw[(size_t)en * e_stride] : make_float2(0.f, 0.f);
-                }
-#pragma unroll
-                for (int q = 0; q < kChunk; ++q) {
-                    const float gn = cur[q].x, w = cur[q].y;
-                    const bool on = w > 0.f;
-                    n_valid += on ? 1 : 0;
-                    const float fac = on ? s_inv[n_valid] : 0.f;
-                    const float delta = f_sub(gn, mean);
-                    mean = f_add(mean, f_mul(fac, delta));
-                    m2 = f_add(m2, f_mul(f_mul(w, delta), f_sub(gn, mean)));
-                }
-#pragma unroll
-                for (int q = 0; q < kChunk; ++q) cur[q] = nxt[q];
-            }
-            wsum = (float)n_valid;
-        } else if (!use_dir) {
-            // Chunks of kChunk eras: the running weight sums are a short dependent chain of adds,
-            // the kChunk divisions w / wsum are independent of each other (the scheduler overlaps
-            // them), and only the mean / M2 updates form the long dependent chain.  The next
-            // chunk's table entries are loaded while the current one is processed.
-            constexpr int kChunk = 16;
-            float2 cur[kChunk], nxt[kChunk];
-#pragma unroll
-            for (int q = 0; q < kChunk; ++q)
-                cur[q] = (q < E) ? gw[(size_t)q * e_stride] : make_float2(0.f, 0.f);
-            for (int e = 0; e < E; e += kChunk) {
-#pragma unroll
-                for (int q = 0; q < kChunk; ++q) {
-                    const int en = e + kChunk + q;
-                    nxt[q] = (en < E) ? gw[(size_t)en * e_stride] : make_float2(0.f, 0.f);
-                }
-                float wsn[kChunk], fac[kChunk];
-                float ws = wsum;
-#pragma unroll
-                for (int q = 0; q < kChunk; ++q) {
-                    ws = f_add(ws, cur[q].y);
-                    wsn[q] = ws;
-                }
-                wsum = ws;
-#pragma unroll
-                for (int q = 0; q < kChunk; ++q) fac[q] = (wsn[q] > 0.f) ? f_div(cur[q].y, wsn[q]) : 0.f;
-#pragma unroll
-                for (int q = 0; q < kChunk; ++q) {
-                    // entries past the last era carry weight 0 and gain 0: they leave the state unchanged
-                    const float gn = cur[q].x, w = cur[q].y;
-                    const float delta = f_sub(gn, mean);
-                    mean = f_add(mean, f_mul(fac[q], delta));
-                    m2 = f_add(m2, f_mul(f_mul(w, delta), f_sub(gn, mean)));
-                }
-#pragma unroll
-                for (int q = 0; q < kChunk; ++q) cur[q] = nxt[q];
-            }
-        } else {
-            // directional agreement needs the per-era left / right leaf directions: recompute them
-            // from the histogram prefix of this threshold
-            const long long gpar = s.frontier[node].gq;
-            const float pa = (gpar > 0) ? -1.f : ((gpar < 0) ? 1.f : 0.f);  // sign(-G/(H+lambda)), H+lambda > 0
-            const float inv_scale = *s.inv_scale_ptr;
-            const int NB = s.max_bins;
-            const int t = s.thr_ids[my_k];
-            for (int e = 0; e < E; ++e) {
-                const float2 v = gw[(size_t)e * e_stride];
-                const float w = v.y;
-                welford_step(v.x, w, wsum, mean, m2);
-                const size_t base = (((size_t)f * E + e) * s.node_stride + node) * NB;
-                uint32_t lc = 0, tc = 0;
-                long long lgq = 0, tgq = 0;
-                for (int b = 0; b < NB; ++b) {
-                    const uint32_t cc = s.cnt[base + b];
-                    const long long gg = s.gsum[base + b];
-                    tc += cc;
-                    tgq += gg;
-                    if (b <= t) {
-                        lc += cc;
-                        lgq += gg;
-                    }
-                }
-                if (tc == 0) continue;
-                const float lg = f_mul(__ll2float_rn(lgq), inv_scale);
-                const float tg = f_mul(__ll2float_rn(tgq), inv_scale);
-                const float lh = (float)lc, th = (float)tc;
-                const float vl = f_div(-lg, f_add(lh, lam));
-                const float vr = f_div(-f_sub(tg, lg), f_add(f_sub(th, lh), lam));
-                const float agree =
-                    f_mul(0.5f, f_add((sign_of(vl) == pa) ? 1.f : 0.f, (sign_of(vr) == pa) ? 1.f : 0.f));
-                a_num = f_add(a_num, f_mul(w, agree));
-                a_den = f_add(a_den, w);
-            }
-        }
-        // final score, global min_samples_leaf mask
         const float ws = (wsum < 1e-12f) ? 1e-12f : wsum;
         float var = f_div(m2, ws);
         if (var < 0.f) var = 0.f;  // NaN stays NaN
@@ -454,6 +364,256 @@ __global__ void __launch_bounds__(kChainThreads) chain_kernel(ChainArgs a) {
     }
 }
 
+__global__ void __launch_bounds__(kChainThreads) chain_kernel(ChainArgs a) {
+    const ScoreLaunch& s = a.s;
+    extern __shared__ unsigned char smem_raw[];
+    const int n_nodes = min(*s.n_nodes_ptr, s.n_nodes_max);
+    const int npc = a.nodes_per_cta;
+    const int node0 = blockIdx.y * npc;
+    if (node0 >= n_nodes) return;
+    const int nn = min(npc, n_nodes - node0);
+    const int f = blockIdx.x;
+    const int E = s.n_eras, K = s.n_thr;
+    const float lam = s.lambda_l2;
+    const bool use_dir = (s.direction_weight != 0.f) && (*s.any_dir_ptr != 0);
+
+    // shared layout: res_lg int64 [npc*K] | staged table float2 [2][EC][npc*K] | res_score, res_cnt
+    const int npck = npc * K;
+    const int EC = a.era_chunk;
+    long long* res_lg = reinterpret_cast<long long*>(smem_raw);
+    float2* s_gw = reinterpret_cast<float2*>(res_lg + npck);
+    float* res_score = reinterpret_cast<float*>(s_gw + (size_t)2 * EC * npck);
+    uint32_t* res_cnt = reinterpret_cast<uint32_t*>(res_score + npck);
+
+    const int my_i = threadIdx.x / K;
+    const int my_k = threadIdx.x - my_i * K;
+    const int slots = nn * K;
+    const bool scorer = (threadIdx.x < slots);
+    const int node = node0 + (scorer ? my_i : 0);
+    float wsum = 0.f, mean = 0.f, m2 = 0.f, a_num = 0.f, a_den = 0.f;
+    const float2* gw_cta = s.gw + ((size_t)f * E * s.node_stride + node0) * K;  // + e * e_stride + slot
+    const size_t e_stride = (size_t)s.node_stride * K;
+
+    if (!use_dir) {
+        // The (gain, weight) table of this CTA is streamed through shared memory in chunks of EC
+        // eras with asynchronous copies, the next chunk in flight while the current one is walked;
+        // only the mean / M2 updates form the long dependent chain.
+        auto prefetch = [&](int c) {
+            const int e0 = c * EC, ec = min(EC, E - e0);
+            float2* dst = s_gw + (size_t)(c & 1) * EC * npck;
+            for (int i = threadIdx.x; i < ec * slots; i += blockDim.x) {
+                const int e = i / slots, j = i - e * slots;
+                cp_async8(dst + (size_t)e * npck + j, gw_cta + (size_t)(e0 + e) * e_stride + j);
+            }
+            cp_async_commit();
+        };
+        const int n_chunks = (E + EC - 1) / EC;
+        prefetch(0);
+        for (int c = 0; c < n_chunks; ++c) {
+            if (c + 1 < n_chunks) {
+                prefetch(c + 1);
+                cp_async_wait<1>();
+            } else {
+                cp_async_wait<0>();
+            }
+            __syncthreads();
+            if (scorer) {
+                const int ec = min(EC, E - c * EC);
+                const float2* src = s_gw + (size_t)(c & 1) * EC * npck + threadIdx.x;
+                {
+                    constexpr int kSub = 8;  // the kSub divisions of a sub-chunk are independent
+                    for (int e0 = 0; e0 < ec; e0 += kSub) {
+                        float2 v[kSub];
+                        float fac[kSub];
+                        float ws = wsum;
+#pragma unroll
+                        for (int q = 0; q < kSub; ++q) {
+                            v[q] = (e0 + q < ec) ? src[(size_t)(e0 + q) * npck] : make_float2(0.f, 0.f);
+                            ws = f_add(ws, v[q].y);
+                            fac[q] = ws;
+                        }
+                        wsum = ws;
+#pragma unroll
+                        for (int q = 0; q < kSub; ++q) fac[q] = (fac[q] > 0.f) ? f_div(v[q].y, fac[q]) : 0.f;
+#pragma unroll
+                        for (int q = 0; q < kSub; ++q) {
+                            // padding entries carry weight 0 and gain 0: they leave the state unchanged
+                            const float delta = f_sub(v[q].x, mean);
+                            mean = f_add(mean, f_mul(fac[q], delta));
+                            m2 = f_add(m2, f_mul(f_mul(v[q].y, delta), f_sub(v[q].x, mean)));
+                        }
+                    }
+                }
+            }
+            __syncthreads();
+        }
+    } else {
+        __syncthreads();
+        if (scorer) {
+            // directional agreement needs the per-era left / right leaf directions: recompute them
+            // from the histogram prefix of this threshold
+            const float2* gw = gw_cta + threadIdx.x;
+            const long long gpar = s.frontier[node].gq;
+            const float pa = (gpar > 0) ? -1.f : ((gpar < 0) ? 1.f : 0.f);  // sign(-G/(H+lambda)), H+lambda > 0
+            const float inv_scale = *s.inv_scale_ptr;
+            const int NB = s.max_bins;
+            const int t = s.thr_ids[my_k];
+            for (int e = 0; e < E; ++e) {
+                const float2 v = gw[(size_t)e * e_stride];
+                const float w = v.y;
+                welford_step(v.x, w, wsum, mean, m2);
+                const size_t base = (((size_t)f * E + e) * s.node_stride + node) * NB;
+                uint32_t lc = 0, tc = 0;
+                long long lgq = 0, tgq = 0;
+                for (int b = 0; b < NB; ++b) {
+                    const uint32_t cc = s.cnt[base + b];
+                    const long long gg = s.gsum[base + b];
+                    tc += cc;
+                    tgq += gg;
+                    if (b <= t) {
+                        lc += cc;
+                        lgq += gg;
+                    }
+                }
+                if (tc == 0) continue;
+                const float lg = f_mul(__ll2float_rn(lgq), inv_scale);
+                const float tg = f_mul(__ll2float_rn(tgq), inv_scale);
+                const float lh = (float)lc, th = (float)tc;
+                const float vl = f_div(-lg, f_add(lh, lam));
+                const float vr = f_div(-f_sub(tg, lg), f_add(f_sub(th, lh), lam));
+                const float agree =
+                    f_mul(0.5f, f_add((sign_of(vl) == pa) ? 1.f : 0.f, (sign_of(vr) == pa) ? 1.f : 0.f));
+                a_num = f_add(a_num, f_mul(w, agree));
+                a_den = f_add(a_den, w);
+            }
+        }
+    }
+
+    finish_pairs(s, f, node0, nn, scorer, my_i, my_k, wsum, mean, m2, use_dir, a_num, a_den, res_score, res_cnt, res_lg);
+}
+
+// The era recursion when every era weight is 0 or 1 (era_alpha == 0, no directional term): the
+// running weight sum is then a small integer n and the Welford factor is 0 or the correctly
+// rounded 1 / n, read from a table.  The CTA is split into two halves of equal size:
+//   consumers (first half)  one thread per (node, threshold) slot; per era only a shared load and
+//                           the mean / M2 updates, so the dependent float chain sets the pace;
+//   producers (second half) stream the (gain, weight) table of the CTA into a ring of three
+//                           chunks with asynchronous copies (chunk c + 2), and rewrite chunk
+//                           c + 1 in place to (gain, factor), one thread per slot counting the
+//                           valid eras seen so far, while the consumers walk chunk c.
+// One block-wide barrier per chunk hands the buffers on.
+constexpr int kUnitSlotsMax = 128;  // consumer threads per CTA
+
+__global__ void __launch_bounds__(2 * kUnitSlotsMax) chain_unit_kernel(ChainArgs a) {
+    const ScoreLaunch& s = a.s;
+    extern __shared__ unsigned char smem_raw[];
+    const int n_nodes = min(*s.n_nodes_ptr, s.n_nodes_max);
+    const int npc = a.nodes_per_cta;
+    const int node0 = blockIdx.y * npc;
+    if (node0 >= n_nodes) return;
+    const int nn = min(npc, n_nodes - node0);
+    const int f = blockIdx.x;
+    const int E = s.n_eras, K = s.n_thr;
+
+    // shared layout: res_lg int64 [npck] | ring float2 [3][EC][npck] | res_score, res_cnt, s_nv [npck] | s_inv [E+1]
+    const int npck = npc * K;
+    const int EC = a.era_chunk;
+    long long* res_lg = reinterpret_cast<long long*>(smem_raw);
+    float2* ring = reinterpret_cast<float2*>(res_lg + npck);
+    float* res_score = reinterpret_cast<float*>(ring + (size_t)3 * EC * npck);
+    uint32_t* res_cnt = reinterpret_cast<uint32_t*>(res_score + npck);
+    int* s_nv = reinterpret_cast<int*>(res_cnt + npck);
+    float* s_inv = reinterpret_cast<float*>(s_nv + npck);  // s_inv[n] = 1/n, n <= n_eras
+    for (int n = threadIdx.x; n <= E; n += blockDim.x) s_inv[n] = (n > 0) ? f_div(1.f, (float)n) : 0.f;
+
+    const int half = blockDim.x >> 1;
+    const bool producer = (threadIdx.x >= half);
+    const int t = producer ? threadIdx.x - half : threadIdx.x;  // slot of this thread in its half
+    const int slots = nn * K;
+    const bool active = (t < slots);
+    const int my_i = t / K;
+    const int my_k = t - my_i * K;
+    const float2* gw_cta = s.gw + ((size_t)f * E * s.node_stride + node0) * K;  // + e * e_stride + slot
+    const size_t e_stride = (size_t)s.node_stride * K;
+    const int n_chunks = (E + EC - 1) / EC;
+
+    // producers only
+    auto load_chunk = [&](int c) {  // always commits a group, possibly an empty one
+        if (c < n_chunks) {
+            const int e0 = c * EC, ec = min(EC, E - e0);
+            float2* dst = ring + (size_t)(c % 3) * EC * npck;
+            if (active)  // a producer copies and rewrites its own slot column only
+                for (int e = 0; e < ec; ++e)
+                    cp_async8(dst + (size_t)e * npck + t, gw_cta + (size_t)(e0 + e) * e_stride + t);
+        }
+        cp_async_commit();
+    };
+    int n_valid = 0;
+    auto rewrite_chunk = [&](int c) {
+        if (!active || c >= n_chunks) return;
+        const int ec = min(EC, E - c * EC);
+        float2* buf = ring + (size_t)(c % 3) * EC * npck + t;
+        constexpr int kSub = 8;
+        for (int e0 = 0; e0 < ec; e0 += kSub) {
+            float2 v[kSub];
+#pragma unroll
+            for (int q = 0; q < kSub; ++q)
+                v[q] = (e0 + q < ec) ? buf[(size_t)(e0 + q) * npck] : make_float2(0.f, 0.f);
+#pragma unroll
+            for (int q = 0; q < kSub; ++q) {
+                const bool on = v[q].y > 0.f;
+                n_valid += on ? 1 : 0;
+                v[q].y = on ? s_inv[n_valid] : 0.f;
+            }
+#pragma unroll
+            for (int q = 0; q < kSub; ++q)
+                if (e0 + q < ec) buf[(size_t)(e0 + q) * npck] = v[q];
+        }
+    };
+
+    if (producer) {
+        load_chunk(0);
+        load_chunk(1);
+        cp_async_wait<1>();  // chunk 0 of this thread has landed
+    }
+    __syncthreads();  // the reciprocal table is visible
+    if (producer) rewrite_chunk(0);
+    __syncthreads();
+
+    float mean = 0.f, m2 = 0.f;
+    for (int c = 0; c < n_chunks; ++c) {
+        if (producer) {
+            load_chunk(c + 2);  // its buffer held chunk c - 1, released by the last barrier
+            cp_async_wait<1>();  // chunk c + 1 (this thread's column) has landed
+            rewrite_chunk(c + 1);
+        } else if (active) {
+            const int ec = min(EC, E - c * EC);
+            const float2* src = ring + (size_t)(c % 3) * EC * npck + t;
+            constexpr int kSub = 8;
+            for (int e0 = 0; e0 < ec; e0 += kSub) {
+                float2 v[kSub];
+#pragma unroll
+                for (int q = 0; q < kSub; ++q)
+                    v[q] = (e0 + q < ec) ? src[(size_t)(e0 + q) * npck] : make_float2(0.f, 0.f);
+#pragma unroll
+                for (int q = 0; q < kSub; ++q) {
+                    // padding and invalid eras carry factor 0 and weight 0: the state is unchanged
+                    const float w = (v[q].y > 0.f) ? 1.f : 0.f;
+                    const float delta = f_sub(v[q].x, mean);
+                    mean = f_add(mean, f_mul(v[q].y, delta));
+                    m2 = f_add(m2, f_mul(f_mul(w, delta), f_sub(v[q].x, mean)));
+                }
+            }
+        }
+        __syncthreads();
+    }
+    if (producer && active) s_nv[t] = n_valid;
+    __syncthreads();
+    const bool scorer = !producer && active;
+    const float wsum = scorer ? (float)s_nv[t] : 0.f;
+    finish_pairs(s, f, node0, nn, scorer, my_i, my_k, wsum, mean, m2, false, 0.f, 0.f, res_score, res_cnt, res_lg);
+}
+
 }  // namespace
 
 size_t score_scratch_bytes_per_feature(int node_stride, int n_eras, int n_thr) {
@@ -484,7 +644,8 @@ int launch_score(const ScoreLaunch& s, cudaStream_t stream) {
         g.era_splits = splits;
         dim3 grid((unsigned)s.n_feat, (unsigned)groups, (unsigned)splits);
         if (grid.y > 65535u) return fail_arg("scorer grid too large");
-        gain_kernel_small<<<grid, kGainThreads, 0, stream>>>(g);
+        if (K <= 4) gain_kernel_small<4><<<grid, kGainThreads, 0, stream>>>(g);
+        else gain_kernel_small<kSmallBins><<<grid, kGainThreads, 0, stream>>>(g);
     } else {
         const int warps = kGainThreads / 32;
         const int groups = (s.n_nodes_max + warps - 1) / warps;
@@ -501,16 +662,42 @@ int launch_score(const ScoreLaunch& s, cudaStream_t stream) {
 
     ChainArgs c;
     c.s = s;
-    int npc = kChainThreads / K;
-    if (npc < 1) npc = 1;
-    if (npc > s.n_nodes_max) npc = s.n_nodes_max;
-    c.nodes_per_cta = npc;
-    c.unit_weights = (s.era_alpha <= 0.f && s.n_eras < kInvTable) ? 1 : 0;
-    const size_t smem = (size_t)npc * K * 16 + (c.unit_weights ? (size_t)(s.n_eras + 1) * 4 : 0);
-    dim3 grid((unsigned)s.n_feat, (unsigned)((s.n_nodes_max + npc - 1) / npc));
-    if (grid.y > 65535u) return fail_arg("scorer grid too large");
-    const int threads = ((npc * K + 31) / 32) * 32;
-    chain_kernel<<<grid, threads, smem, stream>>>(c);
+    const bool unit = (s.era_alpha <= 0.f && s.direction_weight == 0.f && s.n_eras < kInvTable && K <= kUnitSlotsMax);
+    c.unit_weights = unit ? 1 : 0;
+    if (unit) {
+        int npc = kUnitSlotsMax / K;
+        if (npc > s.n_nodes_max) npc = s.n_nodes_max;
+        c.nodes_per_cta = npc;
+        int ec = (int)((16 * 1024) / ((size_t)npc * K * sizeof(float2)));
+        if (ec < 8) ec = 8;
+        if (ec > 64) ec = 64;
+        if (ec > s.n_eras) ec = s.n_eras;
+        c.era_chunk = ec;
+        const size_t smem = (size_t)npc * K * 20 + (size_t)3 * ec * npc * K * sizeof(float2) + (size_t)(s.n_eras + 1) * 4;
+        if (smem > 48 * 1024)
+            PB_CUDA_TRY(cudaFuncSetAttribute(chain_unit_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        dim3 grid((unsigned)s.n_feat, (unsigned)((s.n_nodes_max + npc - 1) / npc));
+        if (grid.y > 65535u) return fail_arg("scorer grid too large");
+        const int half = ((npc * K + 31) / 32) * 32;
+        chain_unit_kernel<<<grid, 2 * half, smem, stream>>>(c);
+    } else {
+        int npc = kChainThreads / K;
+        if (npc < 1) npc = 1;
+        if (npc > s.n_nodes_max) npc = s.n_nodes_max;
+        c.nodes_per_cta = npc;
+        int ec = (int)((24 * 1024) / ((size_t)npc * K * sizeof(float2)));
+        if (ec < 8) ec = 8;
+        if (ec > 64) ec = 64;
+        if (ec > s.n_eras) ec = s.n_eras;
+        c.era_chunk = ec;
+        const size_t smem = (size_t)npc * K * 16 + (size_t)2 * ec * npc * K * sizeof(float2);
+        if (smem > 48 * 1024)
+            PB_CUDA_TRY(cudaFuncSetAttribute(chain_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        dim3 grid((unsigned)s.n_feat, (unsigned)((s.n_nodes_max + npc - 1) / npc));
+        if (grid.y > 65535u) return fail_arg("scorer grid too large");
+        const int threads = ((npc * K + 31) / 32) * 32;
+        chain_kernel<<<grid, threads, smem, stream>>>(c);
+    }
     prof_end(kProfScore, stream);
     count_launch(2);
     PB_LAUNCH_CHECK("chain_kernel");
