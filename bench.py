@@ -202,6 +202,7 @@ def main():
     total = args.warmup + args.steps
     for r in range(args.warmup):
         booster._boost_one_round(r, total)
+    booster._drain()
     barrier()
     launches0 = int(lib.pb_launch_count())
     lib.pb_profile_enable(1)
@@ -217,19 +218,18 @@ def main():
     F_s = trainer.n_sampled()
     barrier()
     ev0.record()
+    logs0 = len(booster._depth_logs)
     for r in range(args.warmup, total):
-        booster._boost_one_round(r, total)
-        n_ctx = booster._last_n_ctx
-        # algorithmic bytes of this round's histogram launches (this rank's features only)
-        f_loc = F_s / world
-        for d in range(CFG["max_depth"]):
-            if n_ctx[d] == 0:
-                break
-            hist_bytes += (n_rows * f_loc * code_bytes + n_rows * (4 + 2) + (n_eras + 1) * 4
-                           + n_ctx[d] * f_loc * n_eras * CFG["max_bins"] * 12)
+        booster._boost_one_round(r, total)   # enqueues round r, takes in the log of round r - 1
+    booster._drain()                         # waits for the last round and its log
     ev1.record()
     barrier()
     ms = ev0.elapsed_time(ev1)
+    # algorithmic bytes of the timed rounds' histogram launches (this rank's features only)
+    f_loc = F_s / world
+    for entry in booster._depth_logs[logs0:]:
+        hist_bytes += (n_rows * f_loc * code_bytes + n_rows * (4 + 2) + (n_eras + 1) * 4
+                       + int(entry["nodes_processed"]) * f_loc * n_eras * CFG["max_bins"] * 12)
     clocks = sampler.stop() if rank == 0 else None
     lib.pb_profile_enable(0)
     B.check(lib.pb_profile_collect(ms5, n5))

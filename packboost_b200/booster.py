@@ -170,6 +170,9 @@ def _era_correlation_np(era_ids: np.ndarray, target: np.ndarray, preds: np.ndarr
 # ------------------------------ device training state ------------------------------
 
 
+_RING = 4  # staging slots: at most three rounds are in flight (previous, a discarded one, its redo)
+
+
 class _DeviceTrainer:
     """Owns the device buffers of one fit and launches the round phases."""
 
@@ -263,9 +266,13 @@ class _DeviceTrainer:
         self.log_bytes = int(nbytes.value)
         off = ptr.value - self.ctl.data_ptr()
         self.log_dev = self.ctl[off: off + self.log_bytes]
-        self.log_host = torch.empty(self.log_bytes, dtype=torch.uint8).pin_memory()
-        self.feat_host = torch.empty((D, 3, max(k_sampled, 1)), dtype=torch.int32).pin_memory()
+        # Rounds are enqueued ahead of the host's bookkeeping, so the pinned staging buffers form a
+        # ring: a slot is reused only after the round that used it has delivered its log.
+        self.log_host = [torch.empty(self.log_bytes, dtype=torch.uint8).pin_memory() for _ in range(_RING)]
+        self.feat_host = [torch.empty((D, 3, max(k_sampled, 1)), dtype=torch.int32).pin_memory() for _ in range(_RING)]
+        self.log_event = [torch.cuda.Event() for _ in range(_RING)]
         self.feat_dev = torch.empty((D, 3, max(k_sampled, 1)), dtype=torch.int32, device=self.dev)
+        self.enqueued = 0
         self.rounds_done = 0
         self.pending_delta = False
 
@@ -275,13 +282,20 @@ class _DeviceTrainer:
         return min(k, self.F)
 
     # -- one round ---------------------------------------------------------
-    def run_round(self, subsets: list[np.ndarray]) -> None:
-        """Enqueue every phase of one round; ``subsets[d]`` is the sampled feature list of depth d."""
+    def run_round(self, subsets: list[np.ndarray], redo: bool = False) -> int:
+        """Enqueue every phase of one round; ``subsets[d]`` is the sampled feature list of depth d.
+
+        Returns the ticket to pass to :meth:`read_log`.  ``redo=True`` replaces the round enqueued
+        last (its leaf deltas are dropped, the predictions it started from are kept)."""
         lib, st = self.lib, C.byref(self.st)
         stream = torch.cuda.current_stream().cuda_stream
         D = self.D
         k = subsets[0].shape[0]
-        fh = self.feat_host
+        ticket = self.enqueued
+        slot = ticket % _RING
+        if ticket >= _RING:
+            self.log_event[slot].synchronize()  # the slot's previous round has long finished
+        fh = self.feat_host[slot]
         n_local = []
         for d in range(D):
             s = subsets[d]
@@ -293,7 +307,7 @@ class _DeviceTrainer:
             fh[d, 1, : pos.shape[0]] = torch.from_numpy(rows)
             fh[d, 2, : pos.shape[0]] = torch.from_numpy(pos)
         self.feat_dev.copy_(fh, non_blocking=True)
-        B.check(lib.pb_round_begin(st, 1 if self.pending_delta else 0, stream))
+        B.check(lib.pb_round_begin(st, 1 if (self.pending_delta and not redo) else 0, stream))
         for d in range(D):
             sampled = self.feat_dev[d, 0].data_ptr()
             rows = self.feat_dev[d, 1].data_ptr()
@@ -312,8 +326,12 @@ class _DeviceTrainer:
                 B.check(lib.pb_depth_partition(st, d, stream))
         B.check(lib.pb_round_end(st, stream))
         self.pending_delta = True
-        self.log_host.copy_(self.log_dev, non_blocking=True)
-        self.rounds_done += 1
+        self.log_host[slot].copy_(self.log_dev, non_blocking=True)
+        self.log_event[slot].record()
+        self.enqueued += 1
+        if not redo:
+            self.rounds_done += 1
+        return ticket
 
     def _allreduce_candidates(self, depth: int, k: int) -> None:
         ptr, nbytes = C.c_void_p(), C.c_int64()
@@ -328,9 +346,13 @@ class _DeviceTrainer:
             B.check(self.lib.pb_apply_leaf_delta(C.byref(self.st), torch.cuda.current_stream().cuda_stream))
             self.pending_delta = False
 
-    def read_log(self) -> tuple[np.ndarray, np.ndarray]:
-        torch.cuda.current_stream().synchronize()
-        raw = self.log_host.numpy()
+    def read_log(self, ticket: int) -> tuple[np.ndarray, np.ndarray]:
+        """Wait for the round behind ``ticket`` and return its decision log (views of pinned memory)."""
+        if not 0 <= self.enqueued - 1 - ticket < _RING:
+            raise RuntimeError("round log is no longer held")
+        slot = ticket % _RING
+        self.log_event[slot].synchronize()
+        raw = self.log_host[slot].numpy()
         head = raw[:88].view(_HEADER_DT)[0]
         winners = raw[88:].view(_WINNER_DT)
         return head, winners
@@ -401,11 +423,13 @@ class PackBoost:
         self._last_n_ctx: list[int] = []
         self._pending_log = None
         self._predrawn = None
+        self._inflight = None  # (log ticket, generator state at the round's start) of the enqueued round
 
     # Public -------------------------------------------------------------
 
     @property
     def trees(self) -> Sequence[Tree]:
+        self._drain()
         self._flush_pending_tree()
         return self._trees
 
@@ -540,6 +564,7 @@ class PackBoost:
         self._eval_states = self._prepare_eval_sets(eval_sets)
         self._pending_log = None
         self._predrawn = None
+        self._inflight = None
 
     def _boost_one_round(self, round_idx: int, num_rounds: int, want_callback: bool = False) -> dict[str, float]:
         """One boosting round (``packboost/booster.py:494-655``)."""
@@ -554,28 +579,29 @@ class PackBoost:
             st0 = self._rng.get_state()
             return st0, [torch.randperm(F, generator=self._rng)[:k].numpy().astype(np.int32) for _ in range(D)]
 
-        state0, subsets = self._predrawn if self._predrawn is not None else draw()
-        self._predrawn = None
-        trainer.run_round(subsets)
-        # while the device works on this round: finish the host bookkeeping of the previous round
-        # and draw the next round's subsets (discarded below if this round rewinds the generator)
-        self._flush_pending_tree()
-        if round_idx + 1 < num_rounds:
-            self._predrawn = draw()
-        head, winners = trainer.read_log()
-        n_ctx = [int(v) for v in head["n_ctx"][: D + 1]]
-        self._last_n_ctx = n_ctx
-        used = next((d for d in range(D) if n_ctx[d] == 0), D)
-        if used < D:
-            self._rng.set_state(state0)
-            for _ in range(used):
-                torch.randperm(F, generator=self._rng)
-            self._predrawn = None
-        for d in range(used):
-            self._depth_logs.append(self._depth_log(d, n_ctx[d], k))
-        self._pending_log = (head.copy(), winners[: (1 << D) - 1].copy())
         eval_states = self._eval_states
         want_metrics = want_callback or bool(eval_states) or os.getenv("PACKBOOST_TRAIN_METRICS") == "1"
+        # Without per-round consumers the host runs one round ahead of the device: round r is
+        # enqueued before the log of round r - 1 is read, so the device never waits for the host.
+        run_ahead = not want_metrics and os.getenv("PACKBOOST_RUN_AHEAD") != "0"
+
+        state0, subsets = self._predrawn if self._predrawn is not None else draw()
+        self._predrawn = None
+        ticket = trainer.run_round(subsets)
+        previous, self._inflight = self._inflight, (ticket, state0)
+        # while the device works on this round: finish the host bookkeeping of earlier rounds and
+        # draw the next round's subsets (discarded if a round turns out to rewind the generator)
+        self._flush_pending_tree()
+        if previous is not None and not self._retire(previous):
+            # round r - 1 ended early and the generator was rewound, so this round's subsets came
+            # from the wrong state.  Enqueue it again with the right ones; the first attempt is dropped.
+            state0, subsets = draw()
+            ticket = trainer.run_round(subsets, redo=True)
+            self._inflight = (ticket, state0)
+        if round_idx + 1 < num_rounds:
+            self._predrawn = draw()
+        if not run_ahead:
+            self._drain()
         if want_metrics:
             self._flush_pending_tree()  # callbacks and evaluation sets see this round's trees
         metrics: dict[str, float] = {"round": round_idx + 1}
@@ -608,7 +634,37 @@ class PackBoost:
         self._distinct.append((tree, int(self.config.pack_size)))
         self._trees.extend([tree] * int(self.config.pack_size))
 
+    def _retire(self, inflight) -> bool:
+        """Take in the decision log of an enqueued round.  Returns False when the round ended before
+        ``max_depth``: the reference would not have drawn feature subsets for the unused depths
+        (``packboost/booster.py:516-519``), so the generator is rewound to the round's start, the
+        used draws are replayed and every later draw is invalid."""
+        ticket, state0 = inflight
+        D = int(self.config.max_depth)
+        head, winners = self._trainer.read_log(ticket)
+        n_ctx = [int(v) for v in head["n_ctx"][: D + 1]]
+        self._last_n_ctx = n_ctx
+        used = next((d for d in range(D) if n_ctx[d] == 0), D)
+        if used < D:
+            self._rng.set_state(state0)
+            for _ in range(used):
+                torch.randperm(self._fit_ctx["F"], generator=self._rng)
+            self._predrawn = None
+        k = self._trainer.n_sampled()
+        for d in range(used):
+            self._depth_logs.append(self._depth_log(d, n_ctx[d], k))
+        self._flush_pending_tree()
+        self._pending_log = (head.copy(), winners[: (1 << D) - 1].copy())
+        return used == D
+
+    def _drain(self) -> None:
+        """Wait for the round in flight, if any, and take in its log."""
+        if self._inflight is not None:
+            inflight, self._inflight = self._inflight, None
+            self._retire(inflight)
+
     def _finish(self) -> None:
+        self._drain()
         self._flush_pending_tree()
         self._trainer.flush_predictions()
         torch.cuda.current_stream().synchronize()
@@ -728,6 +784,7 @@ class PackBoost:
         (``packboost/booster.py:658-712``)."""
         if self._binner is None:
             raise RuntimeError("Model must be fitted before predict()")
+        self._drain()
         self._flush_pending_tree()
         rows = self._pack_rows(X)
         if not self._trees:

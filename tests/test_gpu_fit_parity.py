@@ -74,6 +74,37 @@ def test_fit_matches_oracle_fresh_seeds(seed):
     np.testing.assert_allclose(booster.train_predictions(), model.train_preds, rtol=1e-5, atol=1e-5 * scale)
 
 
+@pytest.mark.parametrize("run_ahead", ["1", "0"])
+def test_rounds_that_end_early_rewind_the_generator(run_ahead, monkeypatch):
+    """min_samples_leaf stops every tree after two or three levels of max_depth 6, so each round
+    draws fewer feature subsets than speculated: the generator is rewound and, when the host runs
+    a round ahead of the device, the round already enqueued is replaced."""
+    monkeypatch.setenv("PACKBOOST_RUN_AHEAD", run_ahead)
+    rng = np.random.default_rng(11)
+    n, f, e = 2400, 16, 6
+    X = rng.normal(size=(n, f)).astype(np.float32)
+    y = (X[:, 0] - 0.5 * X[:, 4] + 0.2 * rng.standard_normal(n)).astype(np.float32)
+    era = rng.integers(0, e, size=n).astype(np.int16)
+    cfg = dict(pack_size=2, max_depth=6, learning_rate=0.1, lambda_l2=1.0, lambda_dro=0.25, min_samples_leaf=500,
+               max_bins=32, layer_feature_fraction=0.5, random_state=3)
+    rounds = 6
+    model = po.fit(X, y, era, po.OracleParams(**cfg), rounds)
+    def height(t, nid=0):
+        return 0 if t["is_leaf"][nid] else 1 + max(height(t, t["left"][nid]), height(t, t["right"][nid]))
+
+    heights = [height(t) for t in model.trees[:: cfg["pack_size"]]]
+    assert 0 < max(heights) < cfg["max_depth"], "the case must split and still end rounds early"
+    booster = _fit_gpu(X, y, era, cfg, rounds)
+    off_o, cols_o = flatten_oracle(model.trees)
+    off_g, cols_g = flatten_trees(booster.trees)
+    np.testing.assert_array_equal(off_g, off_o)
+    for k in ("feature", "threshold", "left", "right", "is_leaf"):
+        np.testing.assert_array_equal(cols_g[k], cols_o[k], err_msg=k)
+    assert_values_close(cols_g["value"], cols_o["value"], cols_o["is_leaf"])
+    scale = np.abs(model.train_preds).max()
+    np.testing.assert_allclose(booster.train_predictions(), model.train_preds, rtol=1e-5, atol=1e-5 * scale)
+
+
 def test_fit_is_bitwise_deterministic():
     X, y, era, cfg, rounds, Xh = cases.CASES["prebinned5"]()
     a = _fit_gpu(X, y, era, cfg, rounds)
