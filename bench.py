@@ -199,41 +199,54 @@ def main():
     booster = PackBoost(PackBoostConfig(device="cuda", **CFG))
     booster._start(X, y_host, era_host)
     trainer = booster._trainer
-    total = args.warmup + args.steps
+    total = args.warmup + 2 * args.steps
     for r in range(args.warmup):
         booster._boost_one_round(r, total)
     booster._drain()
     barrier()
-    launches0 = int(lib.pb_launch_count())
-    lib.pb_profile_enable(1)
-    ms5 = (C.c_double * 5)()
-    n5 = (C.c_int64 * 5)()
+    total = args.warmup + 2 * args.steps
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    k_local_sum = 0
-    hist_bytes = 0.0
-    code_bytes = 0.5
     F_s = trainer.n_sampled()
+    launches0 = int(lib.pb_launch_count())
+    replays0 = trainer.graph_replays
     barrier()
     ev0.record()
-    logs0 = len(booster._depth_logs)
-    for r in range(args.warmup, total):
+    for r in range(args.warmup, args.warmup + args.steps):
         booster._boost_one_round(r, total)   # enqueues round r, takes in the log of round r - 1
     booster._drain()                         # waits for the last round and its log
     ev1.record()
     barrier()
     ms = ev0.elapsed_time(ev1)
-    # algorithmic bytes of the timed rounds' histogram launches (this rank's features only)
+    clocks = sampler.stop() if rank == 0 else None
+    # kernels of the timed region: eager launches are counted by the library as they are issued,
+    # a replayed round graph holds the number counted while it was captured
+    launches = (int(lib.pb_launch_count()) - launches0
+                + (trainer.graph_replays - replays0) * trainer.graph_launches)
+
+    # Second pass of the same length for the per-kernel figures: the round graph is switched off
+    # and every launch of a kernel family is bracketed by CUDA events on the launching stream.
+    trainer.use_graph = False
+    lib.pb_profile_enable(1)
+    ms5 = (C.c_double * 5)()
+    n5 = (C.c_int64 * 5)()
+    hist_bytes = 0.0
+    code_bytes = 0.5
+    logs0 = len(booster._depth_logs)
+    barrier()
+    for r in range(args.warmup + args.steps, total):
+        booster._boost_one_round(r, total)
+    booster._drain()
+    barrier()
+    lib.pb_profile_enable(0)
+    B.check(lib.pb_profile_collect(ms5, n5))
+    # algorithmic bytes of those rounds' histogram launches (this rank's features only)
     f_loc = F_s / world
     for entry in booster._depth_logs[logs0:]:
         hist_bytes += (n_rows * f_loc * code_bytes + n_rows * (4 + 2) + (n_eras + 1) * 4
                        + int(entry["nodes_processed"]) * f_loc * n_eras * CFG["max_bins"] * 12)
-    clocks = sampler.stop() if rank == 0 else None
-    lib.pb_profile_enable(0)
-    B.check(lib.pb_profile_collect(ms5, n5))
-    launches = int(lib.pb_launch_count()) - launches0
     t = torch.tensor([ms], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -305,6 +318,8 @@ def main():
             "roofline": {"bound": "hbm", "kernel": "hist_lane_kernel", "achieved": achieved, "peak": peak, "unit": "GB/s",
                          "frac": achieved / peak, "traffic": traffic, "traffic_source": traffic_src,
                          "peak_source": peak_src,
+                         "timing": "CUDA events around every launch in a second pass of the same number of rounds "
+                                   "with the round graph off",
                          "launches": hist_launches, "avg_launch_ms": hist_ms / max(hist_launches, 1),
                          "algorithmic_bytes_per_launch": hist_bytes / max(hist_launches, 1)},
             "cpu_baseline": cpu_baseline, "e2e": e2e, "gpu_launches": launches, "clocks": clocks, "phases": phases,

@@ -274,6 +274,13 @@ class _DeviceTrainer:
         self.feat_dev = torch.empty((D, 3, max(k_sampled, 1)), dtype=torch.int32, device=self.dev)
         self.enqueued = 0
         self.rounds_done = 0
+        # CUDA graph of one round (PACKBOOST_CUDA_GRAPH=0 disables it).  With the memory-sharded
+        # layout the local feature counts change from round to round, so it stays off there.
+        self.use_graph = os.getenv("PACKBOOST_CUDA_GRAPH") != "0" and (world == 1 or self.replicated)
+        self.graph = None
+        self.graph_signature = None
+        self.graph_launches = 0
+        self.graph_replays = 0
         self.pending_delta = False
 
     def n_sampled(self) -> int:
@@ -300,14 +307,58 @@ class _DeviceTrainer:
         for d in range(D):
             s = subsets[d]
             fh[d, 0, :k] = torch.from_numpy(s)
-            rows, pos = local_part(s, self.rank, self.world)
             if self.replicated and self.world > 1:
-                rows = s[pos].astype(np.int32)  # all feature rows are held locally: row == feature id
+                # every feature row is held locally (row == feature id): deal the sampled list
+                # round-robin by position, which gives every rank the same share at every depth
+                pos = np.arange(self.rank, k, self.world, dtype=np.int32)
+                rows = s[pos].astype(np.int32)
+            else:
+                rows, pos = local_part(s, self.rank, self.world)
             n_local.append(int(pos.shape[0]))
             fh[d, 1, : pos.shape[0]] = torch.from_numpy(rows)
             fh[d, 2, : pos.shape[0]] = torch.from_numpy(pos)
         self.feat_dev.copy_(fh, non_blocking=True)
-        B.check(lib.pb_round_begin(st, 1 if (self.pending_delta and not redo) else 0, stream))
+        apply_previous = 1 if (self.pending_delta and not redo) else 0
+        # The phases of a round are the same launches every round (the feature lists change only as
+        # data in feat_dev), so from the second round on they are replayed as one CUDA graph.  The
+        # graph is tied to the per-depth local feature counts; any other round runs eagerly.
+        signature = (k, tuple(n_local))
+        if self.use_graph and apply_previous == 1:
+            if self.graph is None:
+                try:
+                    self._capture(k, n_local, signature)
+                except RuntimeError as exc:  # e.g. a collective that cannot be captured: launch eagerly
+                    logging.getLogger(__name__).warning("round graph capture failed (%s); launching eagerly", exc)
+                    self.use_graph = False
+            if self.graph_signature == signature:
+                self.graph.replay()
+                self.graph_replays += 1
+                return self._round_enqueued(slot, redo)
+        self._enqueue_phases(k, n_local, apply_previous)
+        return self._round_enqueued(slot, redo)
+
+    def _capture(self, k: int, n_local: list[int], signature) -> None:
+        before = int(self.lib.pb_launch_count())
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, capture_error_mode="thread_local"):
+            self._enqueue_phases(k, n_local, 1)
+        self.graph, self.graph_signature = graph, signature
+        self.graph_launches = int(self.lib.pb_launch_count()) - before  # kernels per replay
+
+    def _round_enqueued(self, slot: int, redo: bool) -> int:
+        self.pending_delta = True
+        self.log_host[slot].copy_(self.log_dev, non_blocking=True)
+        self.log_event[slot].record()
+        self.enqueued += 1
+        if not redo:
+            self.rounds_done += 1
+        return self.enqueued - 1
+
+    def _enqueue_phases(self, k: int, n_local: list[int], apply_previous: int) -> None:
+        lib, st = self.lib, C.byref(self.st)
+        stream = torch.cuda.current_stream().cuda_stream
+        D = self.D
+        B.check(lib.pb_round_begin(st, apply_previous, stream))
         for d in range(D):
             sampled = self.feat_dev[d, 0].data_ptr()
             rows = self.feat_dev[d, 1].data_ptr()
@@ -325,13 +376,6 @@ class _DeviceTrainer:
             else:
                 B.check(lib.pb_depth_partition(st, d, stream))
         B.check(lib.pb_round_end(st, stream))
-        self.pending_delta = True
-        self.log_host[slot].copy_(self.log_dev, non_blocking=True)
-        self.log_event[slot].record()
-        self.enqueued += 1
-        if not redo:
-            self.rounds_done += 1
-        return ticket
 
     def _allreduce_candidates(self, depth: int, k: int) -> None:
         ptr, nbytes = C.c_void_p(), C.c_int64()

@@ -53,8 +53,14 @@ static cudaEvent_t take_event() {
     return e;
 }
 
+// (no timing inside a stream capture: the events would become graph dependencies)
+static bool capturing(cudaStream_t stream) {
+    cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
+    return cudaStreamIsCapturing(stream, &cs) == cudaSuccess && cs != cudaStreamCaptureStatusNone;
+}
+
 void prof_begin(int kind, cudaStream_t stream) {
-    if (!g_prof_on) return;
+    if (!g_prof_on || capturing(stream)) return;
     std::lock_guard<std::mutex> lk(g_prof_mu);
     cudaEvent_t e = take_event();
     cudaEventRecord(e, stream);
@@ -62,7 +68,7 @@ void prof_begin(int kind, cudaStream_t stream) {
 }
 
 void prof_end(int kind, cudaStream_t stream) {
-    if (!g_prof_on) return;
+    if (!g_prof_on || capturing(stream)) return;
     std::lock_guard<std::mutex> lk(g_prof_mu);
     cudaEvent_t e = take_event();
     cudaEventRecord(e, stream);
