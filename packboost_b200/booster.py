@@ -345,6 +345,13 @@ class _DeviceTrainer:
         self.graph, self.graph_signature = graph, signature
         self.graph_launches = int(self.lib.pb_launch_count()) - before  # kernels per replay
 
+    def release_graph(self) -> None:
+        """Drop the captured round graph (it is captured again if more rounds are enqueued)."""
+        if self.graph is not None:
+            torch.cuda.current_stream().synchronize()
+            self.graph = None
+            self.graph_signature = None
+
     def _round_enqueued(self, slot: int, redo: bool) -> int:
         self.pending_delta = True
         self.log_host[slot].copy_(self.log_dev, non_blocking=True)
@@ -710,6 +717,9 @@ class PackBoost:
     def _finish(self) -> None:
         self._drain()
         self._flush_pending_tree()
+        # a graph that holds captured collectives must be gone before the process group is torn
+        # down (communicator destruction waits for it otherwise)
+        self._trainer.release_graph()
         self._trainer.flush_predictions()
         torch.cuda.current_stream().synchronize()
 

@@ -1,5 +1,6 @@
 """Feature-sharded training on 2 GPUs reproduces the single-GPU trees bit for bit."""
 
+import datetime
 import os
 import socket
 
@@ -27,7 +28,8 @@ def _worker(rank, world, port, name, shard, out):
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
     torch.cuda.set_device(rank)
-    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank),
+                            timeout=datetime.timedelta(seconds=120))  # a stuck collective fails instead of hanging
     from packboost_b200 import PackBoost, PackBoostConfig
     X, y, era, cfg, rounds, Xh = cases.CASES[name]()
     b = PackBoost(PackBoostConfig(device="cuda", **cfg))
