@@ -287,23 +287,27 @@ __global__ void __launch_bounds__(kLaneWarps * 32, 2) hist_lane_kernel(HistKerne
     int c = c0 + warp;
     if (c < c1) load_chunk(c, w, raw_s, raw_g);
     for (; c < c1; c += kLaneWarps) {
+        bool any_ok = false;
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
             const int r = c * kLaneRows + 2 * lane + h;
             const bool ok = (r >= r0) & (r < r1) & (raw_s[h] < n_nodes);
+            any_ok |= ok;
+            // a row that is not accumulated adds zero to the cells of node 0: the row steps below
+            // carry no branch, so the rows of a batch and the tuples of a lane interleave freely
             uint4 rec;
-            rec.x = ok ? (uint32_t)(raw_s[h] * cpn) * kLaneCellBytes : 0xFFFFFFFFu;
-            rec.y = (((uint32_t)raw_g[h] & lo_mask) << CB) + 1u;
-            rec.z = (uint32_t)(raw_g[h] >> LB);
+            rec.x = ok ? (uint32_t)(raw_s[h] * cpn) * kLaneCellBytes : 0u;
+            rec.y = ok ? (((uint32_t)raw_g[h] & lo_mask) << CB) + 1u : 0u;
+            rec.z = ok ? (uint32_t)(raw_g[h] >> LB) : 0u;
             rec.w = 0u;
             st[2 * lane + h] = rec;
         }
-        __syncwarp();
+        const bool chunk_on = __any_sync(0xFFFFFFFFu, any_ok);  // (also orders the staging stores)
         uint32_t wn[FPL][8];
         int nraw_s[2], nraw_g[2];
         const int cn = c + kLaneWarps;
         if (cn < c1) load_chunk(cn, wn, nraw_s, nraw_g);
-        if (n_mine > 0) {
+        if (n_mine > 0 && chunk_on) {
 #pragma unroll
             for (int jb = 0; jb < kLaneRows; jb += 4) {
                 uint4 rec[4];
@@ -312,7 +316,7 @@ __global__ void __launch_bounds__(kLaneWarps * 32, 2) hist_lane_kernel(HistKerne
 #pragma unroll
                 for (int q = 0; q < 4; ++q) {
                     const int j = jb + q;
-                    if (rec[q].x != 0xFFFFFFFFu) {
+                    {
                         const int bit = (j & 7) * 4;
 #pragma unroll
                         for (int t = 0; t < T; ++t) {
@@ -356,17 +360,17 @@ __global__ void __launch_bounds__(kLaneWarps * 32, 2) hist_lane_kernel(HistKerne
         const int above = cpn / (below * nb);
         const uint32_t* tcells = cells + (size_t)t * n_cells * 64;
         for (int b = 0; b < nb; ++b) {
-            uint32_t count = 0;
-            long long lo_sum = 0, hi_sum = 0;
+            // The packed words of the joint cells are added as they are: the rows behind them are
+            // disjoint subsets of the tile, so neither field can overflow; decode once per bin.
+            uint32_t a_sum = 0, b_sum = 0;
             for (int hi = 0; hi < above; ++hi)
                 for (int lo = 0; lo < below; ++lo) {
                     const uint32_t cell = (uint32_t)(n * cpn + (hi * nb + b) * below + lo) * 64u + lane;
-                    const uint32_t Aw = tcells[cell];
-                    count += Aw & cmask;
-                    lo_sum += (long long)(Aw >> CB);
-                    hi_sum += (long long)(int32_t)tcells[cell + 32];
+                    a_sum += tcells[cell];
+                    b_sum += tcells[cell + 32];
                 }
-            const long long gs = hi_sum * (1ll << LB) + lo_sum;
+            const uint32_t count = a_sum & cmask;
+            const long long gs = (long long)(int32_t)b_sum * (1ll << LB) + (long long)(a_sum >> CB);
             const size_t o = (((size_t)(feat0 + fl) * a.n_eras + era) * a.node_stride + n) * nb + b;
             if (a.use_atomics) {
                 if (count) atomicAdd(a.cnt + o, count);
