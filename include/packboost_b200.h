@@ -235,6 +235,14 @@ int pb_depth_apply_bits(const pb_train_state* st, int64_t depth, const uint32_t*
 int pb_round_end(const pb_train_state* st, void* stream);
 int pb_apply_leaf_delta(const pb_train_state* st, void* stream);
 
+/* Per-era Pearson correlation of `preds` and `y` (device float32[n_rows], rows ordered by era,
+ * `era_offsets` device int32[n_eras+1]) into `corr_out` (device float64[n_eras]); replaces the
+ * host loop of packboost/booster.py:909-929 (`_era_correlation_np`), which needs both arrays on
+ * the host every round.  An era the reference skips (fewer than two rows, a standard deviation
+ * <= 1e-12, a non-finite quotient) yields NaN; the metric is the mean of the other entries. */
+int pb_era_correlation(const float* y, const float* preds, const int32_t* era_offsets, int64_t n_eras,
+                       double* corr_out, void* stream);
+
 /* Device address and size of the round's decision log (copy it to the host after
  * pb_round_end; layout: pb_round_log below). */
 int pb_round_log_buffer(const pb_train_state* st, void** ptr, int64_t* bytes);

@@ -88,6 +88,7 @@ _PROTOS: dict[str, tuple[Any, list[Any]]] = {
     "pb_depth_apply_bits": (C.c_int, [C.POINTER(TrainState), i64, vp, vp]),
     "pb_round_end": (C.c_int, [C.POINTER(TrainState), vp]),
     "pb_apply_leaf_delta": (C.c_int, [C.POINTER(TrainState), vp]),
+    "pb_era_correlation": (C.c_int, [vp, vp, vp, i64, vp, vp]),
     "pb_round_log_buffer": (C.c_int, [C.POINTER(TrainState), C.POINTER(vp), C.POINTER(i64)]),
     "pb_hist_build": (C.c_int, [C.POINTER(TrainState), vp, i64, i64, i64, vp, vp, vp]),
     "pb_predict_rows": (C.c_int, [vp, i64, i64, i64, vp, vp, vp, vp, vp, vp, vp, vp, i64, C.c_float, vp, vp, vp]),

@@ -272,6 +272,7 @@ class _DeviceTrainer:
         self.feat_host = [torch.empty((D, 3, max(k_sampled, 1)), dtype=torch.int32).pin_memory() for _ in range(_RING)]
         self.log_event = [torch.cuda.Event() for _ in range(_RING)]
         self.feat_dev = torch.empty((D, 3, max(k_sampled, 1)), dtype=torch.int32, device=self.dev)
+        self.corr_dev = None
         self.enqueued = 0
         self.rounds_done = 0
         # CUDA graph of one round (PACKBOOST_CUDA_GRAPH=0 disables it).  With the memory-sharded
@@ -396,6 +397,18 @@ class _DeviceTrainer:
         if self.pending_delta:
             B.check(self.lib.pb_apply_leaf_delta(C.byref(self.st), torch.cuda.current_stream().cuda_stream))
             self.pending_delta = False
+
+    def era_correlation(self) -> float:
+        """Mean per-era correlation of the training predictions with the targets, computed on the
+        device (``packboost/booster.py:909-929``); only ``n_eras`` doubles travel to the host."""
+        if self.corr_dev is None:
+            self.corr_dev = torch.empty(self.E, dtype=torch.float64, device=self.dev)
+        B.check(self.lib.pb_era_correlation(self.y.data_ptr(), self.preds.data_ptr(), self.era_offsets.data_ptr(),
+                                            self.E, self.corr_dev.data_ptr(),
+                                            torch.cuda.current_stream().cuda_stream))
+        c = self.corr_dev.cpu().numpy()
+        c = c[np.isfinite(c)]
+        return float(c.mean()) if c.size else float("nan")
 
     def read_log(self, ticket: int) -> tuple[np.ndarray, np.ndarray]:
         """Wait for the round behind ``ticket`` and return its decision log (views of pinned memory)."""
@@ -658,7 +671,7 @@ class PackBoost:
         metrics: dict[str, float] = {"round": round_idx + 1}
         if want_metrics:
             trainer.flush_predictions()
-            metrics["train_corr"] = _era_correlation_np(ctx["era_sorted"], ctx["y_sorted"], trainer.preds.cpu().numpy())
+            metrics["train_corr"] = trainer.era_correlation()
         else:
             metrics["train_corr"] = float("nan")
         try:

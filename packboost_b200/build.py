@@ -17,7 +17,7 @@ CSRC = os.path.join(HERE, "csrc")
 LIB_NAME = "libpackboost_b200.so"
 LIB_PATH = os.path.join(HERE, LIB_NAME)
 
-SOURCES = ["api.cu", "hist.cu", "score.cu", "frontier.cu", "pack.cu", "predict.cu"]
+SOURCES = ["api.cu", "hist.cu", "score.cu", "frontier.cu", "pack.cu", "predict.cu", "metrics.cu"]
 # The scorer must round every product and sum separately (no fused multiply-add) to keep the
 # float32 operation order of the algorithm it implements.
 EXTRA = {"score.cu": ["-fmad=false"]}

@@ -162,3 +162,29 @@ def test_superseded_frontier_calls_say_so():
     for fn in (B.find_best_splits_batched_cuda, B.partition_frontier_cuda, B.find_best_splits_batched):
         with pytest.raises(RuntimeError):
             fn()
+
+
+def test_era_correlation_matches_host_formula():
+    """Device per-era correlation against the reference's numpy loop, with the eras it skips:
+    a single-row era, an era of constant predictions and an era of constant targets."""
+    import ctypes as C
+    from packboost_b200 import backends as B
+    from packboost_b200.booster import _era_correlation_np
+    rng = np.random.default_rng(5)
+    sizes = [700, 1, 333, 50, 1200, 64]
+    era = np.repeat(np.arange(len(sizes)), sizes).astype(np.int16)
+    n = era.shape[0]
+    y = rng.integers(0, 5, size=n).astype(np.float32) / 4
+    p = (0.05 * y + 0.02 * rng.standard_normal(n)).astype(np.float32)
+    p[era == 3] = 0.125          # constant predictions
+    y[era == 5] = 0.5            # constant targets
+    offs = np.concatenate([[0], np.cumsum(sizes)]).astype(np.int32)
+    dev = torch.device("cuda", 0)
+    yd, pd, od = (torch.from_numpy(a).to(dev) for a in (y, p, offs))
+    out = torch.empty(len(sizes), dtype=torch.float64, device=dev)
+    B.check(B.lib().pb_era_correlation(yd.data_ptr(), pd.data_ptr(), od.data_ptr(), len(sizes), out.data_ptr(),
+                                       torch.cuda.current_stream().cuda_stream))
+    c = out.cpu().numpy()
+    assert np.isnan(c[[1, 3, 5]]).all() and np.isfinite(c[[0, 2, 4]]).all()
+    want = _era_correlation_np(era, y, p)
+    np.testing.assert_allclose(c[np.isfinite(c)].mean(), want, rtol=1e-5)
