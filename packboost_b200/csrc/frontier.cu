@@ -131,6 +131,7 @@ struct SelectArgs {
     int n_sampled;
     int block_size;
     const int32_t* thr_ids;
+    int n_thr;
     int min_leaf;
     double lambda;
 };
@@ -143,6 +144,7 @@ struct BlockBest {
     long long lg;
     int p;
     int k;
+    int f;  // global feature id of the candidate
 };
 
 __device__ __forceinline__ bool block_better(const BlockBest& x, const BlockBest& y) {
@@ -154,7 +156,7 @@ __device__ __forceinline__ bool block_better(const BlockBest& x, const BlockBest
     return x.p > y.p;
 }
 
-__global__ void __launch_bounds__(1024) select_kernel(SelectArgs a) {
+__global__ void __launch_bounds__(512) select_kernel(SelectArgs a) {
     Ctl& c = a.c;
     __shared__ int s_flag[kMaxCtx];   // bit 0: split, bit 1: left child stays active, bit 2: right child
     __shared__ int s_ids[kMaxCtx];    // exclusive count of splits before the node
@@ -170,22 +172,18 @@ __global__ void __launch_bounds__(1024) select_kernel(SelectArgs a) {
     const bool keep_frontier = (a.depth + 1) < a.max_depth;
     if (threadIdx.x == 0) s_any_dir = 0;
 
+    // threshold ids in shared memory: the cross-block merge looks one up per block
+    __shared__ int s_thr[256];
+    for (int i = threadIdx.x; i < a.n_thr && i < 256; i += blockDim.x) s_thr[i] = a.thr_ids[i];
+    __syncthreads();
+
     // ---- A. one warp per node: in-block winner (lanes stride the block), cross-block merge ----
     for (int n = warp; n < n_ctx; n += n_warps) {
         float best_s = -INFINITY;
         long long best_c = -1, best_lg = 0;
         int best_f = -1, best_t = -1;
-        for (int b0 = 0; b0 < a.n_sampled; b0 += a.block_size) {
-            const int b1 = min(a.n_sampled, b0 + a.block_size);
-            BlockBest mine{-INFINITY, -1, 0, -1, -1};
-            bool has_nan = false;
-            for (int p = b0 + lane; p < b1; p += 32) {
-                const Cand cd = a.cand[(size_t)p * a.node_stride + n];
-                if (cd.flags & 1u) has_nan = true;
-                if (cd.k < 0) continue;
-                const BlockBest x{cd.score, (long long)cd.left_count, cd.left_gq, p, cd.k};
-                if (block_better(x, mine)) mine = x;
-            }
+        // butterfly over the lanes' own bests of one block, then the merge across blocks
+        auto merge_block = [&](BlockBest mine, bool has_nan) {
             has_nan = __any_sync(0xFFFFFFFFu, has_nan);
             for (int d = 16; d > 0; d >>= 1) {
                 BlockBest o;
@@ -194,15 +192,62 @@ __global__ void __launch_bounds__(1024) select_kernel(SelectArgs a) {
                 o.lg = __shfl_xor_sync(0xFFFFFFFFu, mine.lg, d);
                 o.p = __shfl_xor_sync(0xFFFFFFFFu, mine.p, d);
                 o.k = __shfl_xor_sync(0xFFFFFFFFu, mine.k, d);
+                o.f = __shfl_xor_sync(0xFFFFFFFFu, mine.f, d);
                 if (block_better(o, mine)) mine = o;
             }
-            if (has_nan || mine.p < 0) continue;
-            const int feat = a.sampled[mine.p];
-            const int thr = a.thr_ids[mine.k];
+            if (has_nan || mine.p < 0) return;
+            const int feat = mine.f;
+            const int thr = s_thr[mine.k];
             const bool upd = (mine.s > best_s) ||
                              (mine.s == best_s && ((mine.c > best_c) ||
                                                    (mine.c == best_c && ((feat > best_f) || (feat == best_f && thr > best_t)))));
             if (upd) { best_s = mine.s; best_c = mine.c; best_lg = mine.lg; best_f = feat; best_t = thr; }
+        };
+        if (a.block_size <= 32) {
+            // a lane holds at most one candidate per block: the loads of eight blocks go out together
+            constexpr int kGroup = 8;
+            const int n_blocks = (a.n_sampled + a.block_size - 1) / a.block_size;
+            for (int g0 = 0; g0 < n_blocks; g0 += kGroup) {
+                Cand cd[kGroup];
+                int ft[kGroup];
+#pragma unroll
+                for (int j = 0; j < kGroup; ++j) {
+                    const int p = (g0 + j) * a.block_size + lane;
+                    const bool in = (g0 + j < n_blocks) && (lane < a.block_size) && (p < a.n_sampled);
+                    cd[j].score = 0.f;
+                    cd[j].k = -1;
+                    cd[j].left_count = 0u;
+                    cd[j].flags = 0u;
+                    cd[j].left_gq = 0ll;
+                    ft[j] = -1;
+                    if (in) {
+                        cd[j] = a.cand[(size_t)p * a.node_stride + n];
+                        ft[j] = a.sampled[p];
+                    }
+                }
+#pragma unroll
+                for (int j = 0; j < kGroup; ++j) {
+                    if (g0 + j >= n_blocks) break;
+                    const int p = (g0 + j) * a.block_size + lane;
+                    BlockBest mine{-INFINITY, -1, 0, -1, -1, -1};
+                    if (cd[j].k >= 0) mine = BlockBest{cd[j].score, (long long)cd[j].left_count, cd[j].left_gq, p, cd[j].k, ft[j]};
+                    merge_block(mine, (cd[j].flags & 1u) != 0u);
+                }
+            }
+        } else {
+            for (int b0 = 0; b0 < a.n_sampled; b0 += a.block_size) {
+                const int b1 = min(a.n_sampled, b0 + a.block_size);
+                BlockBest mine{-INFINITY, -1, 0, -1, -1, -1};
+                bool has_nan = false;
+                for (int p = b0 + lane; p < b1; p += 32) {
+                    const Cand cd = a.cand[(size_t)p * a.node_stride + n];
+                    if (cd.flags & 1u) has_nan = true;
+                    if (cd.k < 0) continue;
+                    const BlockBest x{cd.score, (long long)cd.left_count, cd.left_gq, p, cd.k, a.sampled[p]};
+                    if (block_better(x, mine)) mine = x;
+                }
+                merge_block(mine, has_nan);
+            }
         }
         if (lane == 0) {
             const FrontierNode fn = cur[n];
@@ -669,10 +714,11 @@ extern "C" int pb_depth_select(const pb_train_state* st, int64_t depth, const in
     if (blk <= 0 || blk > n_sampled) blk = (int)n_sampled;
     a.block_size = blk;
     a.thr_ids = st->thr_ids;
+    a.n_thr = (int)st->n_thresholds;
     a.min_leaf = (int)st->min_samples_leaf;
     a.lambda = st->lambda_l2;
     prof_begin(kProfSelect, (cudaStream_t)stream_);
-    select_kernel<<<1, 1024, 0, (cudaStream_t)stream_>>>(a);
+    select_kernel<<<1, 512, 0, (cudaStream_t)stream_>>>(a);
     prof_end(kProfSelect, (cudaStream_t)stream_);
     count_launch(1);
     PB_LAUNCH_CHECK("select_kernel");

@@ -218,15 +218,16 @@ constexpr int kLaneWarps = 8;
 constexpr int kLaneRows = 64;              // rows per warp step: 32 bytes of 4-bit codes per feature
 
 // All lanes of a warp walk the same rows, so the row state is warp-uniform.  It is staged per
-// warp as one 16-byte record per row {byte offset of the node's first cell (0xFFFFFFFF: skip),
-// word A addend, word B addend, unused}, computed once per row by one lane and read by all lanes
-// with a single broadcast load, so the per-lane work of a row step is just code extraction, one
-// three-input add and the two atomics of each tuple.  A lane owns T tuples of A features (T*A
-// consecutive sampled features), each tuple with its own set of cells.  The codes and the raw
-// row state of the warp's next chunk are loaded while the current chunk is accumulated.
+// warp as one 8-byte record per row {byte offset of the node's first cell | 1 when the row is
+// accumulated, fixed-point gradient}, written once per row by one lane and read by all lanes with
+// a single broadcast load; the two addends follow from it with three integer operations.  A row
+// that is not accumulated has an all-zero record: it adds zero to the cells of node 0, so the row
+// steps carry no branch.  A lane owns T tuples of A features (T*A consecutive sampled features),
+// each tuple with its own set of cells.  The codes and the raw row state of the warp's next chunk
+// are loaded while the current chunk is accumulated.
 template <int A, int T>
 __global__ void __launch_bounds__(kLaneWarps * 32, 2) hist_lane_kernel(HistKernelArgs a) {
-    extern __shared__ __align__(16) unsigned char smb[];  // cells [T][n_cells] | staging [warps][64] uint4
+    extern __shared__ __align__(16) unsigned char smb[];  // cells [T][n_cells] | staging [warps][64] uint2
     const int n_nodes = a.n_nodes_ptr ? min(*a.n_nodes_ptr, a.n_nodes) : a.n_nodes;
     if (n_nodes <= 0) return;
     const int era = blockIdx.x / a.tiles_per_era;
@@ -244,7 +245,7 @@ __global__ void __launch_bounds__(kLaneWarps * 32, 2) hist_lane_kernel(HistKerne
     const int n_cells = a.n_nodes * cpn;  // per tuple, sized for the upper bound of nodes
     const uint32_t slot_bytes = (uint32_t)n_cells * kLaneCellBytes;
     uint32_t* cells = reinterpret_cast<uint32_t*>(smb);
-    uint4* staging = reinterpret_cast<uint4*>(smb + (size_t)T * slot_bytes);
+    uint2* staging = reinterpret_cast<uint2*>(smb + (size_t)T * slot_bytes);
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int CB = a.count_bits, LB = a.lo_bits;
     const uint32_t lo_mask = (1u << LB) - 1u;
@@ -262,7 +263,7 @@ __global__ void __launch_bounds__(kLaneWarps * 32, 2) hist_lane_kernel(HistKerne
     __syncthreads();
 
     unsigned char* lane_base = smb + lane * 4;
-    uint4* st = staging + warp * kLaneRows;
+    uint2* st = staging + warp * kLaneRows;
     const int c0 = r0 / kLaneRows, c1 = (r1 + kLaneRows - 1) / kLaneRows;
     const uint32_t nb_scaled = (uint32_t)nb * kLaneCellBytes;
 
@@ -294,12 +295,12 @@ __global__ void __launch_bounds__(kLaneWarps * 32, 2) hist_lane_kernel(HistKerne
             const bool ok = (r >= r0) & (r < r1) & (raw_s[h] < n_nodes);
             any_ok |= ok;
             // a row that is not accumulated adds zero to the cells of node 0: the row steps below
-            // carry no branch, so the rows of a batch and the tuples of a lane interleave freely
-            uint4 rec;
-            rec.x = ok ? (uint32_t)(raw_s[h] * cpn) * kLaneCellBytes : 0u;
-            rec.y = ok ? (((uint32_t)raw_g[h] & lo_mask) << CB) + 1u : 0u;
-            rec.z = ok ? (uint32_t)(raw_g[h] >> LB) : 0u;
-            rec.w = 0u;
+            // carry no branch, so the rows of a batch and the tuples of a lane interleave freely.
+            // Record: {byte offset of the node's cells | 1 when the row counts, gradient}: 8 bytes, so
+            // that the broadcast load of a row step is two shared-memory wavefronts, not four.
+            uint2 rec;
+            rec.x = ok ? ((uint32_t)(raw_s[h] * cpn) * kLaneCellBytes) | 1u : 0u;
+            rec.y = ok ? (uint32_t)raw_g[h] : 0u;
             st[2 * lane + h] = rec;
         }
         const bool chunk_on = __any_sync(0xFFFFFFFFu, any_ok);  // (also orders the staging stores)
@@ -310,9 +311,16 @@ __global__ void __launch_bounds__(kLaneWarps * 32, 2) hist_lane_kernel(HistKerne
         if (n_mine > 0 && chunk_on) {
 #pragma unroll
             for (int jb = 0; jb < kLaneRows; jb += 4) {
-                uint4 rec[4];
+                uint2 raw[4];
 #pragma unroll
-                for (int q = 0; q < 4; ++q) rec[q] = st[jb + q];  // broadcast loads, issued together
+                for (int q = 0; q < 4; ++q) raw[q] = st[jb + q];  // broadcast loads, issued together
+                uint4 rec[4];  // {cell offset, word A addend, word B addend}
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    rec[q].x = raw[q].x & ~1u;
+                    rec[q].y = ((raw[q].y & lo_mask) << CB) + (raw[q].x & 1u);
+                    rec[q].z = (uint32_t)((int32_t)raw[q].y >> LB);
+                }
 #pragma unroll
                 for (int q = 0; q < 4; ++q) {
                     const int j = jb + q;
@@ -469,7 +477,7 @@ int launch_hist(const HistLaunch& h, cudaStream_t stream) {
         a.feats_per_cta = 32 * arity * tuples;
         a.group = arity;
         a.copies = 1;
-        const size_t smem = slot * tuples + (size_t)kLaneWarps * kLaneRows * sizeof(uint4);
+        const size_t smem = slot * tuples + (size_t)kLaneWarps * kLaneRows * sizeof(uint2);
         prof_begin(kProfHist, stream);
         int rc;
         if (arity == 3) rc = launch_lane<3, 1>(a, smem, stream);
