@@ -94,7 +94,7 @@ struct PredictPackedArgs {
 // loads overlap, and the leaf terms are then added in tree order by passing them to the row's
 // first thread with shuffles — the float32 sum stays the sequential one.
 constexpr int kTpr = 4;
-constexpr int kWay = 2;
+constexpr int kWay = 4;
 
 constexpr int kStageNodes = 4096;  // nodes per staged batch of trees (32 KB), two buffers
 
@@ -207,6 +207,137 @@ __global__ void __launch_bounds__(512) predict_rows_packed_kernel(PredictPackedA
         if (has_row && q == 0) a.out[row0 + lr] = acc;
     }
 }
+
+// The common case of the packed predictor — rows and tree batches both staged in shared memory —
+// with every address a 32-bit shared-memory address (the generic form above resolves the address
+// space on each of its two loads per node visit and carries 64-bit pointers) and the tree offsets
+// of a batch staged next to its nodes, so that a node visit is two shared loads and a handful of
+// integer instructions.  Same traversal and the same ordered accumulation as above.
+__device__ __forceinline__ uint32_t lds_u8(uint32_t addr) {
+    uint32_t v;
+    asm volatile("ld.shared.u8 %0, [%1];\n" : "=r"(v) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ uint32_t lds_u32(uint32_t addr) {
+    uint32_t v;
+    asm volatile("ld.shared.u32 %0, [%1];\n" : "=r"(v) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ uint2 lds_v2(uint32_t addr) {
+    uint2 v;
+    asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];\n" : "=r"(v.x), "=r"(v.y) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ void cp_async4(void* smem_dst, const void* gmem_src) {
+    const unsigned d = (unsigned)__cvta_generic_to_shared(smem_dst);
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"(d), "l"(gmem_src) : "memory");
+}
+
+constexpr int kStageTrees = 1024;  // most trees of one staged batch (their offsets are staged too)
+
+template <int BITS>
+__global__ void __launch_bounds__(512) predict_rows_packed_smem_kernel(PredictPackedArgs a) {
+    extern __shared__ __align__(16) uint8_t s_rows[];  // rows | nodes [2][kStageNodes] | offsets [2][kStageTrees + 1]
+    const int64_t row0 = (int64_t)blockIdx.x * a.rows_per_cta;
+    const int nr = (int)min((int64_t)a.rows_per_cta, a.n_rows - row0);
+    if (nr <= 0) return;
+    uint2* s_nodes = reinterpret_cast<uint2*>(s_rows + (size_t)a.rows_per_cta * a.pitch_row);
+    int32_t* s_offs = reinterpret_cast<int32_t*>(s_nodes + 2 * kStageNodes);
+    {
+        const int64_t n16 = (int64_t)nr * a.pitch_row / 16;
+        const uint4* src = reinterpret_cast<const uint4*>(a.codes + row0 * a.pitch_row);
+        uint4* dst = reinterpret_cast<uint4*>(s_rows);
+        for (int64_t i = threadIdx.x; i < n16; i += blockDim.x) dst[i] = __ldg(src + i);
+    }
+    const uint32_t rows_addr = (uint32_t)__cvta_generic_to_shared(s_rows);
+    const uint32_t nodes_addr = (uint32_t)__cvta_generic_to_shared(s_nodes);
+    const uint32_t offs_addr = (uint32_t)__cvta_generic_to_shared(s_offs);
+    const int TB = a.trees_per_batch;
+    const int q = threadIdx.x % kTpr;
+    const int lane = threadIdx.x & 31;
+    const int quad_base = lane - q;
+    const int rows_per_pass = blockDim.x / kTpr;
+    const int n_batches = (a.n_trees + TB - 1) / TB;
+
+    auto prefetch = [&](int b) {
+        const int ta = b * TB, tb = min(a.n_trees, ta + TB);
+        const int o0 = __ldg(a.tree_offsets + ta), o1 = __ldg(a.tree_offsets + tb);
+        uint2* dst = s_nodes + (size_t)(b & 1) * kStageNodes;
+        for (int i = threadIdx.x; i < o1 - o0; i += blockDim.x) cp_async8(dst + i, a.nodes + o0 + i);
+        int32_t* od = s_offs + (size_t)(b & 1) * (kStageTrees + 1);
+        for (int i = threadIdx.x; i <= tb - ta; i += blockDim.x) cp_async4(od + i, a.tree_offsets + ta + i);
+        cp_async_commit();
+    };
+
+    for (int lr0 = 0; lr0 < nr; lr0 += rows_per_pass) {
+        const int lr_raw = lr0 + threadIdx.x / kTpr;
+        const bool has_row = lr_raw < nr;
+        const int lr = has_row ? lr_raw : 0;
+        const uint32_t row = rows_addr + (uint32_t)lr * (uint32_t)a.pitch_row;
+        float acc = a.init ? a.init[row0 + lr] : 0.f;
+        prefetch(0);
+        for (int b = 0; b < n_batches; ++b) {
+            const int ta = b * TB, tb = min(a.n_trees, ta + TB);
+            if (b + 1 < n_batches) {
+                prefetch(b + 1);
+                cp_async_wait<1>();
+            } else {
+                cp_async_wait<0>();
+            }
+            __syncthreads();  // batch b (and, on the first batch, the rows) are in shared memory
+            const uint32_t nbase = nodes_addr + (uint32_t)(b & 1) * (kStageNodes * 8u);
+            const uint32_t obase = offs_addr + (uint32_t)(b & 1) * ((kStageTrees + 1) * 4u);
+            const uint32_t off_shift = lds_u32(obase);
+            for (int t0 = ta; t0 < tb; t0 += kTpr * kWay) {
+                uint32_t base[kWay];
+                uint2 nd[kWay];
+#pragma unroll
+                for (int u = 0; u < kWay; ++u) {
+                    const int t = min(t0 + u * kTpr + q, tb - 1);
+                    base[u] = nbase + (lds_u32(obase + (uint32_t)(t - ta) * 4u) - off_shift) * 8u;
+                    nd[u] = lds_v2(base[u]);
+                }
+                bool any = true;
+                while (any) {
+                    any = false;
+#pragma unroll
+                    for (int u = 0; u < kWay; ++u) {
+                        if (!(nd[u].x >> 31)) {
+                            const uint32_t f = nd[u].x & 0xFFFFu;
+                            const uint32_t thr = (nd[u].x >> 16) & 0xFFu;
+                            uint32_t code;
+                            if (BITS == 4) code = (lds_u8(row + (f >> 1)) >> ((f & 1u) * 4u)) & 0xFu;
+                            else code = lds_u8(row + f);
+                            const uint32_t child = nd[u].y + ((code > thr) ? 1u : 0u);
+                            nd[u] = lds_v2(base[u] + child * 8u);
+                            any = true;
+                        }
+                    }
+                }
+#pragma unroll
+                for (int u = 0; u < kWay; ++u) {
+                    const float mine = __fmul_rn(a.weight, __uint_as_float(nd[u].y));
+#pragma unroll
+                    for (int qq = 0; qq < kTpr; ++qq) {
+                        const float term = __shfl_sync(0xFFFFFFFFu, mine, quad_base + qq);
+                        const int t = t0 + u * kTpr + qq;
+                        if (t < tb) {
+                            if (a.repeat) {
+                                const int rep = __ldg(a.repeat + t);
+                                for (int k = 0; k < rep; ++k) acc = __fadd_rn(acc, term);
+                            } else {
+                                acc = __fadd_rn(acc, term);
+                            }
+                        }
+                    }
+                }
+            }
+            __syncthreads();  // the buffers of batch b may be overwritten by the prefetch of batch b + 2
+        }
+        if (has_row && q == 0) a.out[row0 + lr] = acc;
+    }
+}
+
 
 __global__ void __launch_bounds__(256) predict_bins_fm_kernel(
     const uint8_t* __restrict__ bins, int64_t n_rows, const int32_t* __restrict__ feature,
@@ -348,8 +479,9 @@ extern "C" int pb_predict_rows_packed(const uint8_t* codes, int64_t n_rows, int6
     // trees per staged batch: a multiple of the group walked at once, as many as the buffer holds
     const int group = kTpr * kWay;
     int tb = (int)(kStageNodes / max_tree_nodes) / group * group;
+    if (tb > kStageTrees) tb = kStageTrees / group * group;
     a.trees_per_batch = tb;  // 0: no staging
-    const size_t stage_bytes = tb ? (size_t)2 * kStageNodes * sizeof(uint2) : 0;
+    const size_t stage_bytes = tb ? (size_t)2 * kStageNodes * sizeof(uint2) + (size_t)2 * (kStageTrees + 1) * 4 : 0;
     const int64_t budget = 224 * 1024 - (int64_t)stage_bytes;
     int rows = (int)(budget / pitch_row);
     if (rows > 128) rows = 128;
@@ -364,7 +496,19 @@ extern "C" int pb_predict_rows_packed(const uint8_t* codes, int64_t n_rows, int6
     }
     const unsigned grid = (unsigned)((n_rows + a.rows_per_cta - 1) / a.rows_per_cta);
     const int threads = (a.rows_per_cta * kTpr + 31) / 32 * 32;
-    if (code_bits == 4) {
+    if (a.stage && tb > 0) {  // rows and trees both staged: the all-shared-memory form
+        if (code_bits == 4) {
+            if (smem > 48 * 1024)
+                PB_CUDA_TRY(cudaFuncSetAttribute(predict_rows_packed_smem_kernel<4>,
+                                                 cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            predict_rows_packed_smem_kernel<4><<<grid, threads, smem, stream>>>(a);
+        } else {
+            if (smem > 48 * 1024)
+                PB_CUDA_TRY(cudaFuncSetAttribute(predict_rows_packed_smem_kernel<8>,
+                                                 cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            predict_rows_packed_smem_kernel<8><<<grid, threads, smem, stream>>>(a);
+        }
+    } else if (code_bits == 4) {
         if (smem > 48 * 1024)
             PB_CUDA_TRY(cudaFuncSetAttribute(predict_rows_packed_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         predict_rows_packed_kernel<4><<<grid, threads, smem, stream>>>(a);
