@@ -42,7 +42,7 @@ import torch
 
 from . import backends as B
 from .config import PackBoostConfig
-from .sharding import feature_map, local_part
+from .sharding import dealt_part, feature_map, local_part
 from .data import (BinningResult, PackedMatrix, PackedRows, code_bits_for, detect_prebinned, pack_feature_major,
                    pack_row_major, quantile_edges)
 
@@ -309,10 +309,7 @@ class _DeviceTrainer:
             s = subsets[d]
             fh[d, 0, :k] = torch.from_numpy(s)
             if self.replicated and self.world > 1:
-                # every feature row is held locally (row == feature id): deal the sampled list
-                # round-robin by position, which gives every rank the same share at every depth
-                pos = np.arange(self.rank, k, self.world, dtype=np.int32)
-                rows = s[pos].astype(np.int32)
+                rows, pos = dealt_part(s, self.rank, self.world)
             else:
                 rows, pos = local_part(s, self.rank, self.world)
             n_local.append(int(pos.shape[0]))

@@ -144,12 +144,12 @@ struct HistLaunch {
     int node_stride;
     int count_bits;              // CB: tile rows < 2^CB
     int lo_bits;                 // LB = 32 - 2*CB
-    int max_arity;               // largest feature tuple of the lane kernel (1..3)
+    int max_arity;               // largest feature tuple of the lane kernel (1 or 2)
     uint32_t* cnt;
     int64_t* gsum;
 };
 int launch_hist(const HistLaunch& h, cudaStream_t stream);
-int hist_max_arity();  // default tuple-size cap of the lane kernel (PACKBOOST_HIST_MAX_ARITY overrides, 1..3)
+int hist_max_arity();  // default tuple-size cap of the lane kernel (PACKBOOST_HIST_MAX_ARITY=1 lowers it)
 
 // ---- scorer launch (score.cu) -------------------------------------------------------------
 

@@ -405,7 +405,7 @@ int launch_lane(const HistKernelArgs& a, size_t smem, cudaStream_t stream) {
 
 int hist_max_arity() {
     const char* e = getenv("PACKBOOST_HIST_MAX_ARITY");
-    if (e && e[0] >= '1' && e[0] <= '3' && e[1] == 0) return e[0] - '0';
+    if (e && e[0] >= '1' && e[0] <= '2' && e[1] == 0) return e[0] - '0';
     return 2;
 }
 
@@ -456,7 +456,7 @@ int launch_hist(const HistLaunch& h, cudaStream_t stream) {
         // Pick the tuple width A (joint code) and the tuples per lane T that minimise the
         // shared-memory pipe time: a row step costs about one record load plus two atomics per
         // tuple, and a launch walks the rows once per block of 32*A*T features.
-        const int cap = h.max_arity < 2 ? h.max_arity : 2;
+        const int cap = h.max_arity < 2 ? h.max_arity : 2;  // wider joint codes measured slower
         int arity = 1, tuples = 1;
         int64_t cpn = h.max_bins;
         double best = 1e30;
@@ -480,8 +480,7 @@ int launch_hist(const HistLaunch& h, cudaStream_t stream) {
         const size_t smem = slot * tuples + (size_t)kLaneWarps * kLaneRows * sizeof(uint2);
         prof_begin(kProfHist, stream);
         int rc;
-        if (arity == 3) rc = launch_lane<3, 1>(a, smem, stream);
-        else if (arity == 2) rc = (tuples == 2) ? launch_lane<2, 2>(a, smem, stream) : launch_lane<2, 1>(a, smem, stream);
+        if (arity == 2) rc = (tuples == 2) ? launch_lane<2, 2>(a, smem, stream) : launch_lane<2, 1>(a, smem, stream);
         else rc = (tuples == 4) ? launch_lane<1, 4>(a, smem, stream)
                   : (tuples == 2) ? launch_lane<1, 2>(a, smem, stream) : launch_lane<1, 1>(a, smem, stream);
         prof_end(kProfHist, stream);

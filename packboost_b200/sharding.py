@@ -27,3 +27,13 @@ def local_part(subset: np.ndarray, rank: int, world: int) -> tuple[np.ndarray, n
         return subset.astype(np.int32), np.arange(subset.shape[0], dtype=np.int32)
     pos = np.nonzero(subset % world == rank)[0].astype(np.int32)
     return (subset[pos] // world).astype(np.int32), pos
+
+
+def dealt_part(subset: np.ndarray, rank: int, world: int) -> tuple[np.ndarray, np.ndarray]:
+    """Share of a sampled feature list when every rank holds every feature row: the list is dealt
+    round-robin by position, ``(feature rows == feature ids, positions)``, both int32.  Every
+    rank gets the same number of features (to within one) at every depth and the same number in
+    every round, which is what lets a round be replayed as a fixed CUDA graph."""
+    subset = np.asarray(subset)
+    pos = np.arange(rank, subset.shape[0], max(world, 1), dtype=np.int32)
+    return subset[pos].astype(np.int32), pos

@@ -85,6 +85,26 @@ def test_feature_map_and_local_part_partition_the_features():
     assert np.array_equal(np.sort(np.concatenate(pos_all)), np.arange(11))
 
 
+def test_dealt_part_gives_equal_disjoint_shares():
+    """Replicated-codes layout: the sampled list is dealt by position; shares are disjoint, cover
+    the list, differ by at most one feature and do not depend on which features were drawn."""
+    F, k = 2376, 238
+    for world in (2, 4, 8):
+        sizes = None
+        for seed in range(3):
+            subset = np.random.default_rng(seed).permutation(F)[:k].astype(np.int32)
+            parts = [sharding.dealt_part(subset, r, world) for r in range(world)]
+            pos = np.concatenate([p for _, p in parts])
+            assert np.array_equal(np.sort(pos), np.arange(k))
+            for rows, p in parts:
+                assert rows.dtype == np.int32 and p.dtype == np.int32
+                assert np.array_equal(rows, subset[p])
+            now = [len(p) for _, p in parts]
+            assert max(now) - min(now) <= 1
+            assert sizes is None or sizes == now   # the same in every round: a fixed launch shape
+            sizes = now
+
+
 def _free_port():
     s = socket.socket()
     s.bind(("127.0.0.1", 0))
