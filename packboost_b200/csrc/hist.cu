@@ -225,7 +225,12 @@ constexpr int kLaneRows = 64;              // rows per warp step: 32 bytes of 4-
 // steps carry no branch.  A lane owns T tuples of A features (T*A consecutive sampled features),
 // each tuple with its own set of cells.  The codes and the raw row state of the warp's next chunk
 // are loaded while the current chunk is accumulated.
-template <int A, int T>
+//
+// With few features per launch (a feature shard of a multi-GPU run) the warp is split into R row
+// phases: 32 / R lanes own tuples and phase p of them walks rows [p, p + 1) * 64 / R of the chunk,
+// so a row step of the warp covers R rows.  The R lanes that own the same tuple keep private cell
+// columns as always; the flush adds them up.
+template <int A, int T, int R>
 __global__ void __launch_bounds__(kLaneWarps * 32, 2) hist_lane_kernel(HistKernelArgs a) {
     extern __shared__ __align__(16) unsigned char smb[];  // cells [T][n_cells] | staging [warps][64] uint2
     const int n_nodes = a.n_nodes_ptr ? min(*a.n_nodes_ptr, a.n_nodes) : a.n_nodes;
@@ -254,7 +259,11 @@ __global__ void __launch_bounds__(kLaneWarps * 32, 2) hist_lane_kernel(HistKerne
 
     // features of this lane: T tuples of A consecutive sampled features
     constexpr int FPL = A * T;
-    const int feat0 = (blockIdx.y * 32 + lane) * FPL;
+    constexpr int TL = 32 / R;            // tuple-owning lanes per phase
+    constexpr int PR = kLaneRows / R;     // rows of a chunk walked by one phase
+    constexpr int WPP = PR / 8;           // 32-bit code words per feature and phase
+    const int phase = lane / TL;
+    const int feat0 = (blockIdx.y * TL + (lane - phase * TL)) * FPL;
     const int n_mine = max(0, min(FPL, a.n_feat - feat0));
     const uint8_t* frow[FPL];
 #pragma unroll
@@ -263,13 +272,16 @@ __global__ void __launch_bounds__(kLaneWarps * 32, 2) hist_lane_kernel(HistKerne
     __syncthreads();
 
     unsigned char* lane_base = smb + lane * 4;
-    uint2* st = staging + warp * kLaneRows;
+    // (a phase's records start one entry further apart than its rows, which keeps the R broadcast
+    // addresses of a row step in different banks)
+    uint2* st = staging + warp * (kLaneRows + R);
+    const uint2* st_mine = st + phase * (PR + 1);
     const int c0 = r0 / kLaneRows, c1 = (r1 + kLaneRows - 1) / kLaneRows;
     const uint32_t nb_scaled = (uint32_t)nb * kLaneCellBytes;
 
-    uint32_t w[FPL][8];
+    uint32_t w[FPL][WPP];
     int raw_s[2], raw_g[2];
-    auto load_chunk = [&](int c, uint32_t (&ww)[FPL][8], int (&rs)[2], int (&rg)[2]) {
+    auto load_chunk = [&](int c, uint32_t (&ww)[FPL][WPP], int (&rs)[2], int (&rg)[2]) {
         const int r = c * kLaneRows + 2 * lane;  // lane l stages rows 2l and 2l+1 of the chunk
         const uint32_t sv = *reinterpret_cast<const uint32_t*>(a.slot + r);
         const int2 gv = *reinterpret_cast<const int2*>(a.gq + r);
@@ -279,10 +291,18 @@ __global__ void __launch_bounds__(kLaneWarps * 32, 2) hist_lane_kernel(HistKerne
         rg[1] = gv.y;
 #pragma unroll
         for (int i = 0; i < FPL; ++i) {
-            const uint4* p = reinterpret_cast<const uint4*>(frow[i] + (int64_t)c * (kLaneRows / 2));
-            const uint4 v0 = __ldg(p), v1 = __ldg(p + 1);
-            ww[i][0] = v0.x; ww[i][1] = v0.y; ww[i][2] = v0.z; ww[i][3] = v0.w;
-            ww[i][4] = v1.x; ww[i][5] = v1.y; ww[i][6] = v1.z; ww[i][7] = v1.w;
+            const unsigned char* p = frow[i] + (int64_t)c * (kLaneRows / 2) + phase * (PR / 2);
+            if (R == 1) {
+                const uint4 v0 = __ldg(reinterpret_cast<const uint4*>(p)), v1 = __ldg(reinterpret_cast<const uint4*>(p) + 1);
+                ww[i][0] = v0.x; ww[i][1] = v0.y; ww[i][2] = v0.z; ww[i][3] = v0.w;
+                ww[i][WPP - 4] = v1.x; ww[i][WPP - 3] = v1.y; ww[i][WPP - 2] = v1.z; ww[i][WPP - 1] = v1.w;
+            } else if (R == 2) {
+                const uint4 v0 = __ldg(reinterpret_cast<const uint4*>(p));
+                ww[i][0] = v0.x; ww[i][1] = v0.y; ww[i][WPP - 2] = v0.z; ww[i][WPP - 1] = v0.w;
+            } else {
+                const uint2 v0 = __ldg(reinterpret_cast<const uint2*>(p));
+                ww[i][0] = v0.x; ww[i][WPP - 1] = v0.y;
+            }
         }
     };
     int c = c0 + warp;
@@ -301,19 +321,19 @@ __global__ void __launch_bounds__(kLaneWarps * 32, 2) hist_lane_kernel(HistKerne
             uint2 rec;
             rec.x = ok ? ((uint32_t)(raw_s[h] * cpn) * kLaneCellBytes) | 1u : 0u;
             rec.y = ok ? (uint32_t)raw_g[h] : 0u;
-            st[2 * lane + h] = rec;
+            st[(2 * lane + h) + (2 * lane + h) / PR] = rec;
         }
         const bool chunk_on = __any_sync(0xFFFFFFFFu, any_ok);  // (also orders the staging stores)
-        uint32_t wn[FPL][8];
+        uint32_t wn[FPL][WPP];
         int nraw_s[2], nraw_g[2];
         const int cn = c + kLaneWarps;
         if (cn < c1) load_chunk(cn, wn, nraw_s, nraw_g);
         if (n_mine > 0 && chunk_on) {
 #pragma unroll
-            for (int jb = 0; jb < kLaneRows; jb += 4) {
+            for (int jb = 0; jb < PR; jb += 4) {
                 uint2 raw[4];
 #pragma unroll
-                for (int q = 0; q < 4; ++q) raw[q] = st[jb + q];  // broadcast loads, issued together
+                for (int q = 0; q < 4; ++q) raw[q] = st_mine[jb + q];  // broadcast loads, issued together
                 uint4 rec[4];  // {cell offset, word A addend, word B addend}
 #pragma unroll
                 for (int q = 0; q < 4; ++q) {
@@ -350,16 +370,18 @@ __global__ void __launch_bounds__(kLaneWarps * 32, 2) hist_lane_kernel(HistKerne
 #pragma unroll
             for (int i = 0; i < FPL; ++i)
 #pragma unroll
-                for (int q = 0; q < 8; ++q) w[i][q] = wn[i][q];
+                for (int q = 0; q < WPP; ++q) w[i][q] = wn[i][q];
             raw_s[0] = nraw_s[0]; raw_s[1] = nraw_s[1];
             raw_g[0] = nraw_g[0]; raw_g[1] = nraw_g[1];
         }
     }
     __syncthreads();
 
-    // flush: marginals of this lane's joint tables -> [feature][era][node][bin]
+    // flush: marginals of this lane's joint tables -> [feature][era][node][bin]; the R phases of a
+    // warp take different items and add up the columns of the R lanes that own the tuple
     const uint32_t cmask = (1u << CB) - 1u;
-    for (int item = warp; item < n_nodes * FPL; item += kLaneWarps) {
+    const int col0 = lane - phase * TL;
+    for (int item = warp * R + phase; item < n_nodes * FPL; item += kLaneWarps * R) {
         const int n = item / FPL, fl = item - n * FPL;  // node, feature of the lane
         if (fl >= n_mine) continue;
         const int t = fl / A, fi = fl - t * A;
@@ -373,9 +395,12 @@ __global__ void __launch_bounds__(kLaneWarps * 32, 2) hist_lane_kernel(HistKerne
             uint32_t a_sum = 0, b_sum = 0;
             for (int hi = 0; hi < above; ++hi)
                 for (int lo = 0; lo < below; ++lo) {
-                    const uint32_t cell = (uint32_t)(n * cpn + (hi * nb + b) * below + lo) * 64u + lane;
-                    a_sum += tcells[cell];
-                    b_sum += tcells[cell + 32];
+                    const uint32_t cell = (uint32_t)(n * cpn + (hi * nb + b) * below + lo) * 64u + col0;
+#pragma unroll
+                    for (int ph = 0; ph < R; ++ph) {
+                        a_sum += tcells[cell + ph * TL];
+                        b_sum += tcells[cell + ph * TL + 32];
+                    }
                 }
             const uint32_t count = a_sum & cmask;
             const long long gs = (long long)(int32_t)b_sum * (1ll << LB) + (long long)(a_sum >> CB);
@@ -391,14 +416,23 @@ __global__ void __launch_bounds__(kLaneWarps * 32, 2) hist_lane_kernel(HistKerne
     }
 }
 
-template <int A, int T>
-int launch_lane(const HistKernelArgs& a, size_t smem, cudaStream_t stream) {
+template <int A, int T, int R>
+int launch_lane_r(const HistKernelArgs& a, size_t cell_bytes, cudaStream_t stream) {
+    const size_t smem = cell_bytes + (size_t)kLaneWarps * (kLaneRows + R) * sizeof(uint2);
     if (smem > 48 * 1024)
-        PB_CUDA_TRY(cudaFuncSetAttribute(hist_lane_kernel<A, T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    const int per_cta = 32 * A * T;
+        PB_CUDA_TRY(cudaFuncSetAttribute(hist_lane_kernel<A, T, R>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)smem));
+    const int per_cta = (32 / R) * A * T;
     dim3 grid((unsigned)(a.n_eras * a.tiles_per_era), (unsigned)((a.n_feat + per_cta - 1) / per_cta), 1);
-    hist_lane_kernel<A, T><<<grid, kLaneWarps * 32, smem, stream>>>(a);
+    hist_lane_kernel<A, T, R><<<grid, kLaneWarps * 32, smem, stream>>>(a);
     return PB_OK;
+}
+
+template <int A, int T>
+int launch_lane(const HistKernelArgs& a, size_t cell_bytes, int phases, cudaStream_t stream) {
+    if (phases == 4) return launch_lane_r<A, T, 4>(a, cell_bytes, stream);
+    if (phases == 2) return launch_lane_r<A, T, 2>(a, cell_bytes, stream);
+    return launch_lane_r<A, T, 1>(a, cell_bytes, stream);
 }
 
 }  // namespace
@@ -453,36 +487,50 @@ int launch_hist(const HistLaunch& h, cudaStream_t stream) {
     // lane-private kernel when a lane's cells are few: tuples of A features (joint code) as wide as
     // the cells allow, then T tuples per lane while shared memory lasts (A * T <= 4)
     if (h.code_bits == 4 && (int64_t)h.n_nodes * h.max_bins * kLaneCellBytes <= kLaneSmemMax) {
-        // Pick the tuple width A (joint code) and the tuples per lane T that minimise the
-        // shared-memory pipe time: a row step costs about one record load plus two atomics per
-        // tuple, and a launch walks the rows once per block of 32*A*T features.
+        // Pick the tuple width A (joint code), the tuples per lane T and the row phases R by a cost
+        // model fitted to measured launches (microseconds for a tile of 4 700 rows): a CTA spends
+        // 28.7 * (0.9 + T) / R per tile on the row steps (0.9: staging and record load, 1 per tuple:
+        // its two atomics and code extraction) plus 0.08 per KB of cells for zeroing and flushing
+        // them, and CTAs beyond two per SM queue up.
         const int cap = h.max_arity < 2 ? h.max_arity : 2;  // wider joint codes measured slower
-        int arity = 1, tuples = 1;
+        int arity = 1, tuples = 1, phases = 1;
+        static const int max_phases = [] {  // PACKBOOST_HIST_PHASES=1|2 lowers the row-phase cap (tuning)
+            const char* e = getenv("PACKBOOST_HIST_PHASES");
+            return (e && (e[0] == '1' || e[0] == '2') && e[1] == 0) ? e[0] - '0' : 4;
+        }();
         int64_t cpn = h.max_bins;
         double best = 1e30;
         {
+            const double tile_scale = (double)max_tile / 4700.0;
             int64_t c = h.max_bins;
             for (int a_try = 1; a_try <= cap; ++a_try, c *= h.max_bins) {
                 for (int t_try = 1; t_try * a_try <= 4; t_try *= 2) {
                     const size_t bytes = (size_t)h.n_nodes * c * kLaneCellBytes * t_try;
                     if (bytes > (size_t)kLaneSmemMax) continue;
-                    const int blocks = (h.n_feat + 32 * a_try * t_try - 1) / (32 * a_try * t_try);
-                    const double cost = blocks * (2.2 + 5.6 * t_try);
-                    if (cost < best - 1e-9) { best = cost; arity = a_try; tuples = t_try; cpn = c; }
+                    for (int r_try = 1; r_try <= max_phases; r_try *= 2) {
+                        const int per_cta = (32 / r_try) * a_try * t_try;
+                        const int blocks = (h.n_feat + per_cta - 1) / per_cta;
+                        const double ctas = (double)h.n_eras * a.tiles_per_era * blocks;
+                        const double waves = ctas > 296.0 ? ctas / 296.0 : 1.0;
+                        // (a few per cent against more phases: equal estimates favour whole-warp tuples)
+                        const double cost = (r_try == 1 ? 1.0 : r_try == 2 ? 1.04 : 1.08) * waves *
+                                            (tile_scale * 28.7 * (0.9 + t_try) / r_try + 0.08 * (double)bytes / 1024.0);
+                        if (cost < best * (1.0 - 1e-9)) { best = cost; arity = a_try; tuples = t_try; phases = r_try; cpn = c; }
+                    }
                 }
             }
         }
         const size_t slot = (size_t)h.n_nodes * cpn * kLaneCellBytes;
         a.nodes_per_chunk = h.n_nodes;
-        a.feats_per_cta = 32 * arity * tuples;
+        a.feats_per_cta = (32 / phases) * arity * tuples;
         a.group = arity;
         a.copies = 1;
-        const size_t smem = slot * tuples + (size_t)kLaneWarps * kLaneRows * sizeof(uint2);
+        const size_t smem = slot * tuples;  // cells; the launcher adds the per-warp staging
         prof_begin(kProfHist, stream);
         int rc;
-        if (arity == 2) rc = (tuples == 2) ? launch_lane<2, 2>(a, smem, stream) : launch_lane<2, 1>(a, smem, stream);
-        else rc = (tuples == 4) ? launch_lane<1, 4>(a, smem, stream)
-                  : (tuples == 2) ? launch_lane<1, 2>(a, smem, stream) : launch_lane<1, 1>(a, smem, stream);
+        if (arity == 2) rc = (tuples == 2) ? launch_lane<2, 2>(a, smem, phases, stream) : launch_lane<2, 1>(a, smem, phases, stream);
+        else rc = (tuples == 4) ? launch_lane<1, 4>(a, smem, phases, stream)
+                  : (tuples == 2) ? launch_lane<1, 2>(a, smem, phases, stream) : launch_lane<1, 1>(a, smem, phases, stream);
         prof_end(kProfHist, stream);
         if (rc) return rc;
         count_launch(1);
