@@ -287,6 +287,7 @@ struct ChainArgs {
     int nodes_per_cta;
     int unit_weights;  // 1: era weights are 0/1 and n_eras fits the reciprocal table
     int era_chunk;     // eras per staged chunk of the (gain, weight) table
+    int slot_pow2;     // unit kernel with fewer than 32 slots per CTA: slots rounded up to a power of two, else 0
 };
 
 constexpr int kInvTable = 4096;
@@ -303,6 +304,10 @@ __device__ __forceinline__ void welford_step(float gn, float w, float& wsum, flo
 __device__ __forceinline__ void cp_async8(void* smem_dst, const void* gmem_src) {
     const unsigned d = (unsigned)__cvta_generic_to_shared(smem_dst);
     asm volatile("cp.async.ca.shared.global [%0], [%1], 8;\n" ::"r"(d), "l"(gmem_src) : "memory");
+}
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gmem_src) {
+    const unsigned d = (unsigned)__cvta_generic_to_shared(smem_dst);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(d), "l"(gmem_src) : "memory");
 }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
 template <int N>
@@ -498,15 +503,22 @@ __global__ void __launch_bounds__(kChainThreads) chain_kernel(ChainArgs a) {
 //   consumers (first half)  one thread per (node, threshold) slot; per era only a shared load and
 //                           the mean / M2 updates, so the dependent float chain sets the pace;
 //   producers (second half) stream the (gain, weight) table of the CTA into a ring of three
-//                           chunks with asynchronous copies (chunk c + 2), and rewrite chunk
-//                           c + 1 in place to (gain, factor), one thread per slot counting the
-//                           valid eras seen so far, while the consumers walk chunk c.
-// One block-wide barrier per chunk hands the buffers on.
+//                           chunks with asynchronous copies (chunk c + 2, 16-byte units dealt over
+//                           all producer threads), and rewrite chunk c + 1 in place to
+//                           (gain, factor) while the consumers walk chunk c.
+// The rewrite counts the valid eras seen so far per slot.  With 32 or more slots a producer thread
+// owns a slot and walks the chunk's eras; with fewer there is a single producer warp, which is
+// split into P era phases of S2 lanes (S2: slots rounded up to a power of two): each phase counts
+// and rewrites a contiguous part of the chunk and a shuffle scan joins the counts.
+// Chunks are walked in groups of eight eras without bounds checks: the rows between the end of the
+// last chunk and the next multiple of eight are zero-filled (gain 0, weight 0 leave every state
+// unchanged).  One block-wide barrier per chunk hands the buffers on.
 constexpr int kUnitSlotsMax = 128;  // consumer threads per CTA
+constexpr int kSub = 8;             // eras per unrolled group
 
 __global__ void __launch_bounds__(2 * kUnitSlotsMax) chain_unit_kernel(ChainArgs a) {
     const ScoreLaunch& s = a.s;
-    extern __shared__ unsigned char smem_raw[];
+    extern __shared__ __align__(16) unsigned char smem_raw[];
     const int n_nodes = min(*s.n_nodes_ptr, s.n_nodes_max);
     const int npc = a.nodes_per_cta;
     const int node0 = blockIdx.y * npc;
@@ -515,11 +527,12 @@ __global__ void __launch_bounds__(2 * kUnitSlotsMax) chain_unit_kernel(ChainArgs
     const int f = blockIdx.x;
     const int E = s.n_eras, K = s.n_thr;
 
-    // shared layout: res_lg int64 [npck] | ring float2 [3][EC][npck] | res_score, res_cnt, s_nv [npck] | s_inv [E+1]
+    // shared layout: res_lg int64 [npck2] | ring float2 [3][EC][npck] | res_score, res_cnt, s_nv [npck] | s_inv [E+1]
     const int npck = npc * K;
-    const int EC = a.era_chunk;
+    const int npck2 = (npck + 1) & ~1;  // keeps the ring on a 16-byte boundary
+    const int EC = a.era_chunk;         // multiple of kSub
     long long* res_lg = reinterpret_cast<long long*>(smem_raw);
-    float2* ring = reinterpret_cast<float2*>(res_lg + npck);
+    float2* ring = reinterpret_cast<float2*>(res_lg + npck2);
     float* res_score = reinterpret_cast<float*>(ring + (size_t)3 * EC * npck);
     uint32_t* res_cnt = reinterpret_cast<uint32_t*>(res_score + npck);
     int* s_nv = reinterpret_cast<int*>(res_cnt + npck);
@@ -528,7 +541,7 @@ __global__ void __launch_bounds__(2 * kUnitSlotsMax) chain_unit_kernel(ChainArgs
 
     const int half = blockDim.x >> 1;
     const bool producer = (threadIdx.x >= half);
-    const int t = producer ? threadIdx.x - half : threadIdx.x;  // slot of this thread in its half
+    const int t = producer ? threadIdx.x - half : threadIdx.x;  // index of this thread in its half
     const int slots = nn * K;
     const bool active = (t < slots);
     const int my_i = t / K;
@@ -537,64 +550,114 @@ __global__ void __launch_bounds__(2 * kUnitSlotsMax) chain_unit_kernel(ChainArgs
     const size_t e_stride = (size_t)s.node_stride * K;
     const int n_chunks = (E + EC - 1) / EC;
 
-    // producers only
+    // ---- producers ----
+    // 16-byte copies need both sides on 16 bytes: an even slot count, row pitch and table row
+    const bool wide = ((slots | npck | (int)(e_stride & 1) | (int)((node0 * K) & 1)) & 1) == 0;
+    const int units = wide ? slots >> 1 : slots;  // copy units per era
+    const int step_e = half / units, step_u = half - step_e * units;
     auto load_chunk = [&](int c) {  // always commits a group, possibly an empty one
         if (c < n_chunks) {
             const int e0 = c * EC, ec = min(EC, E - e0);
             float2* dst = ring + (size_t)(c % 3) * EC * npck;
-            if (active)  // a producer copies and rewrites its own slot column only
-                for (int e = 0; e < ec; ++e)
-                    cp_async8(dst + (size_t)e * npck + t, gw_cta + (size_t)(e0 + e) * e_stride + t);
+            const float2* src = gw_cta + (size_t)e0 * e_stride;
+            int e = t / units, u = t - e * units;
+            while (e < ec) {
+                if (wide) cp_async16(dst + (size_t)e * npck + 2 * u, src + (size_t)e * e_stride + 2 * u);
+                else cp_async8(dst + (size_t)e * npck + u, src + (size_t)e * e_stride + u);
+                e += step_e;
+                u += step_u;
+                if (u >= units) {
+                    u -= units;
+                    ++e;
+                }
+            }
+            // rows up to the next multiple of kSub: zero
+            const int ec8 = (ec + kSub - 1) / kSub * kSub;
+            for (int i = t; i < (ec8 - ec) * slots; i += half)
+                dst[(size_t)(ec + i / slots) * npck + (i % slots)] = make_float2(0.f, 0.f);
         }
         cp_async_commit();
     };
+    // (a slot's column of a chunk is copied by several producers: each waits for its own copies,
+    // then all meet at a barrier of the producer half before anyone rewrites)
+    auto producers_sync = [&]() { asm volatile("bar.sync 1, %0;\n" ::"r"(half) : "memory"); };
+
+    const int S2 = a.slot_pow2;              // 0: one producer thread per slot
+    const int P = S2 ? 32 / S2 : 1;          // era phases of the single producer warp
+    const int pj = S2 ? (t & (S2 - 1)) : t;  // slot of this producer thread
+    const int pp = S2 ? t / S2 : 0;          // its era phase
+    const bool col = producer && (pj < slots);
     int n_valid = 0;
     auto rewrite_chunk = [&](int c) {
-        if (!active || c >= n_chunks) return;
+        if (c >= n_chunks) return;
         const int ec = min(EC, E - c * EC);
-        float2* buf = ring + (size_t)(c % 3) * EC * npck + t;
-        constexpr int kSub = 8;
-        for (int e0 = 0; e0 < ec; e0 += kSub) {
+        const int ec8 = (ec + kSub - 1) / kSub * kSub;
+        float2* buf = ring + (size_t)(c % 3) * EC * npck + pj;
+        const int L = EC / P;  // multiple of kSub (checked by the launcher)
+        const int e_lo = min(ec8, pp * L), e_hi = min(ec8, e_lo + L);
+        int base = n_valid;
+        if (S2) {
+            // valid eras of this phase's part, then an inclusive scan over the phases of the slot
+            int cnt = 0;
+            if (col)
+                for (int e0 = e_lo; e0 < e_hi; e0 += kSub) {
+                    float w[kSub];
+#pragma unroll
+                    for (int q = 0; q < kSub; ++q) w[q] = buf[(size_t)(e0 + q) * npck].y;
+#pragma unroll
+                    for (int q = 0; q < kSub; ++q) cnt += (w[q] > 0.f) ? 1 : 0;
+                }
+            int incl = cnt;
+            for (int d = S2; d < 32; d <<= 1) {
+                const int up = __shfl_up_sync(0xFFFFFFFFu, incl, d);
+                if ((int)(threadIdx.x & 31) >= d) incl += up;
+            }
+            const int total = __shfl_sync(0xFFFFFFFFu, incl, (pj + (P - 1) * S2) & 31);
+            base = n_valid + incl - cnt;
+            n_valid += total;
+        }
+        if (!col) return;
+        int n = base;
+        for (int e0 = e_lo; e0 < e_hi; e0 += kSub) {
             float2 v[kSub];
 #pragma unroll
-            for (int q = 0; q < kSub; ++q)
-                v[q] = (e0 + q < ec) ? buf[(size_t)(e0 + q) * npck] : make_float2(0.f, 0.f);
+            for (int q = 0; q < kSub; ++q) v[q] = buf[(size_t)(e0 + q) * npck];
 #pragma unroll
             for (int q = 0; q < kSub; ++q) {
                 const bool on = v[q].y > 0.f;
-                n_valid += on ? 1 : 0;
-                v[q].y = on ? s_inv[n_valid] : 0.f;
+                n += on ? 1 : 0;
+                v[q].y = on ? s_inv[n] : 0.f;
             }
 #pragma unroll
-            for (int q = 0; q < kSub; ++q)
-                if (e0 + q < ec) buf[(size_t)(e0 + q) * npck] = v[q];
+            for (int q = 0; q < kSub; ++q) buf[(size_t)(e0 + q) * npck] = v[q];
         }
+        if (!S2) n_valid = n;
     };
 
     if (producer) {
         load_chunk(0);
         load_chunk(1);
-        cp_async_wait<1>();  // chunk 0 of this thread has landed
+        cp_async_wait<1>();  // this thread's copies of chunk 0 have landed
     }
-    __syncthreads();  // the reciprocal table is visible
+    __syncthreads();  // chunk 0 and the reciprocal table are visible
     if (producer) rewrite_chunk(0);
     __syncthreads();
 
     float mean = 0.f, m2 = 0.f;
     for (int c = 0; c < n_chunks; ++c) {
         if (producer) {
-            load_chunk(c + 2);  // its buffer held chunk c - 1, released by the last barrier
-            cp_async_wait<1>();  // chunk c + 1 (this thread's column) has landed
+            load_chunk(c + 2);   // its buffer held chunk c - 1, released by the last barrier
+            cp_async_wait<1>();  // this thread's copies of chunk c + 1 have landed
+            producers_sync();
             rewrite_chunk(c + 1);
         } else if (active) {
             const int ec = min(EC, E - c * EC);
+            const int ec8 = (ec + kSub - 1) / kSub * kSub;
             const float2* src = ring + (size_t)(c % 3) * EC * npck + t;
-            constexpr int kSub = 8;
-            for (int e0 = 0; e0 < ec; e0 += kSub) {
+            for (int e0 = 0; e0 < ec8; e0 += kSub) {
                 float2 v[kSub];
 #pragma unroll
-                for (int q = 0; q < kSub; ++q)
-                    v[q] = (e0 + q < ec) ? src[(size_t)(e0 + q) * npck] : make_float2(0.f, 0.f);
+                for (int q = 0; q < kSub; ++q) v[q] = src[(size_t)(e0 + q) * npck];
 #pragma unroll
                 for (int q = 0; q < kSub; ++q) {
                     // padding and invalid eras carry factor 0 and weight 0: the state is unchanged
@@ -607,7 +670,7 @@ __global__ void __launch_bounds__(2 * kUnitSlotsMax) chain_unit_kernel(ChainArgs
         }
         __syncthreads();
     }
-    if (producer && active) s_nv[t] = n_valid;
+    if (col && pp == 0) s_nv[pj] = n_valid;
     __syncthreads();
     const bool scorer = !producer && active;
     const float wsum = scorer ? (float)s_nv[t] : 0.f;
@@ -668,12 +731,20 @@ int launch_score(const ScoreLaunch& s, cudaStream_t stream) {
         int npc = kUnitSlotsMax / K;
         if (npc > s.n_nodes_max) npc = s.n_nodes_max;
         c.nodes_per_cta = npc;
-        int ec = (int)((16 * 1024) / ((size_t)npc * K * sizeof(float2)));
+        int ec = (int)((16 * 1024) / ((size_t)npc * K * sizeof(float2))) / 8 * 8;  // multiple of the unrolled group
         if (ec < 8) ec = 8;
         if (ec > 64) ec = 64;
-        if (ec > s.n_eras) ec = s.n_eras;
         c.era_chunk = ec;
-        const size_t smem = (size_t)npc * K * 20 + (size_t)3 * ec * npc * K * sizeof(float2) + (size_t)(s.n_eras + 1) * 4;
+        // fewer than 32 slots: the single producer warp works in 32 / S2 era phases of ec / P eras
+        c.slot_pow2 = 0;
+        if (npc * K < 32) {
+            int s2 = 1;
+            while (s2 < npc * K) s2 *= 2;
+            if (ec % (8 * (32 / s2)) == 0) c.slot_pow2 = s2;
+        }
+        const int npck2 = (npc * K + 1) & ~1;
+        const size_t smem = (size_t)npck2 * 8 + (size_t)npc * K * 12 + (size_t)3 * ec * npc * K * sizeof(float2) +
+                            (size_t)(s.n_eras + 1) * 4;
         if (smem > 48 * 1024)
             PB_CUDA_TRY(cudaFuncSetAttribute(chain_unit_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         dim3 grid((unsigned)s.n_feat, (unsigned)((s.n_nodes_max + npc - 1) / npc));
