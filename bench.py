@@ -306,7 +306,7 @@ def main():
 
     cpu_baseline = None
     if world == 1 and not args.no_cpu:
-        se = 8
+        se = 32   # ~10 s of CPU work on the box
         rps, secs, srows = cpu_port_rounds_per_sec(n_rows, n_feat, n_eras, min(se, n_eras), 3, 1)
         cpu_baseline = {"value": rps, "unit": UNIT, "cores": os.cpu_count() or 1, "kind": "port",
                         "sample": f"3 timed rounds (1 warm-up) of the oracle on the first {min(se, n_eras)} of {n_eras} eras "
