@@ -402,54 +402,68 @@ __global__ void __launch_bounds__(kRowThreads) partition_kernel(PartArgs a) {
     if (n_ctx <= 0) return;
     for (int i = threadIdx.x; i < n_ctx; i += blockDim.x) tab[i] = a.c.part[i];
     __syncthreads();
-    // each thread takes kPer rows spaced one grid apart, so that its dependent loads
-    // (slot -> table entry -> code) of different rows overlap
-    constexpr int kPer = 4;
-    const int64_t n_round = (a.n + 31) / 32 * 32;
+    // A thread owns eight consecutive rows: their slots and leaves move as one 16-byte word each
+    // way, and rows that share a node share code bytes.  (The row arrays are padded past n with
+    // slot "none", so the last group needs no special case.)
+    constexpr int kRows = 8;
+    const int64_t n_groups = (a.n + kRows - 1) / kRows;
+    const int64_t n_groups_round = (n_groups + 31) / 32 * 32;  // whole warps: MODE 1 shuffles
     const int64_t stride = (int64_t)gridDim.x * blockDim.x;
-    for (int64_t r0 = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; r0 < n_round; r0 += stride * kPer) {
-        int s[kPer];
-        PartEntry pe[kPer];
-        int frow[kPer];
-        bool left[kPer];
-#pragma unroll
-        for (int u = 0; u < kPer; ++u) {
-            const int64_t r = r0 + u * stride;
-            s[u] = (r < a.n) ? a.slot[r] : kSlotNone;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n_groups_round; i += stride) {
+        const int64_t r8 = i * kRows;
+        const bool in = i < n_groups;
+        uint4 sv = make_uint4(0xFFFFFFFFu, 0xFFFFFFFFu, 0xFFFFFFFFu, 0xFFFFFFFFu);
+        uint4 lv = make_uint4(0u, 0u, 0u, 0u);
+        if (in) {
+            sv = *reinterpret_cast<const uint4*>(a.slot + r8);
+            if (MODE != 1) lv = *reinterpret_cast<const uint4*>(a.leaf + r8);
         }
+        const uint32_t sw[4] = {sv.x, sv.y, sv.z, sv.w};
+        uint32_t lw[4] = {lv.x, lv.y, lv.z, lv.w};
+        uint32_t nsw[4];
+        uint32_t in_byte = 0u;
+        if (MODE == 2 && in) in_byte = reinterpret_cast<const uint8_t*>(a.bits_in)[i];
+        uint32_t left_mask = 0u;
 #pragma unroll
-        for (int u = 0; u < kPer; ++u) {
-            pe[u].feature = -1;
-            frow[u] = -1;
-            if (s[u] != kSlotNone && s[u] < n_ctx) {
-                pe[u] = tab[s[u]];
-                if (pe[u].feature >= 0 && MODE != 2) frow[u] = a.feat_local[pe[u].feature];
-            }
-        }
-#pragma unroll
-        for (int u = 0; u < kPer; ++u) {
-            const int64_t r = r0 + u * stride;
-            left[u] = false;
-            if (r < n_round && pe[u].feature >= 0) {
-                if (MODE == 2) left[u] = (a.bits_in[r >> 5] >> (r & 31)) & 1u;
-                else if (frow[u] >= 0) left[u] = load_code<BITS>(a.codes, a.pitch, frow[u], r) <= pe[u].threshold;
-            }
-        }
-#pragma unroll
-        for (int u = 0; u < kPer; ++u) {
-            const int64_t r = r0 + u * stride;
-            if (r >= n_round) continue;  // uniform per warp: n_round and the strides are multiples of 32
-            if (MODE == 1) {
-                const unsigned m = __ballot_sync(0xFFFFFFFFu, left[u]);
-                if ((threadIdx.x & 31) == 0) a.bits[r >> 5] = m;
-            } else if (s[u] != kSlotNone) {
-                if (s[u] < n_ctx && pe[u].feature >= 0) {
-                    a.slot[r] = left[u] ? pe[u].slot_left : pe[u].slot_right;
-                    a.leaf[r] = left[u] ? pe[u].leaf_left : pe[u].leaf_right;
-                } else {
-                    a.slot[r] = kSlotNone;
+        for (int u = 0; u < kRows; ++u) {
+            const uint32_t sl = (sw[u >> 1] >> ((u & 1) * 16)) & 0xFFFFu;
+            uint32_t new_slot = sl, new_leaf = (lw[u >> 1] >> ((u & 1) * 16)) & 0xFFFFu;
+            if (sl != kSlotNone) {
+                new_slot = kSlotNone;  // a slot past the frontier, or a node that does not split
+                if ((int)sl < n_ctx) {
+                    const PartEntry pe = tab[sl];
+                    if (pe.feature >= 0) {
+                        bool left = false;
+                        if (MODE == 2) {
+                            left = (in_byte >> u) & 1u;
+                        } else {
+                            const int frow = a.feat_local[pe.feature];
+                            if (frow >= 0) left = load_code<BITS>(a.codes, a.pitch, frow, r8 + u) <= pe.threshold;
+                        }
+                        left_mask |= (left ? 1u : 0u) << u;
+                        new_slot = left ? pe.slot_left : pe.slot_right;
+                        new_leaf = left ? pe.leaf_left : pe.leaf_right;
+                    }
                 }
             }
+            if ((u & 1) == 0) {
+                nsw[u >> 1] = new_slot;
+                lw[u >> 1] = (lw[u >> 1] & 0xFFFF0000u) | new_leaf;
+            } else {
+                nsw[u >> 1] |= new_slot << 16;
+                lw[u >> 1] = (lw[u >> 1] & 0x0000FFFFu) | (new_leaf << 16);
+            }
+        }
+        if (MODE == 1) {
+            // four threads hold the 32 go-left bits of one word
+            const int lane = threadIdx.x & 31;
+            uint32_t word = left_mask << ((lane & 3) * 8);
+            word |= __shfl_xor_sync(0xFFFFFFFFu, word, 1);
+            word |= __shfl_xor_sync(0xFFFFFFFFu, word, 2);
+            if ((lane & 3) == 0 && in) a.bits[i >> 2] = word;
+        } else if (in) {
+            *reinterpret_cast<uint4*>(a.slot + r8) = make_uint4(nsw[0], nsw[1], nsw[2], nsw[3]);
+            *reinterpret_cast<uint4*>(a.leaf + r8) = make_uint4(lw[0], lw[1], lw[2], lw[3]);
         }
     }
 }
@@ -506,8 +520,9 @@ static int check_state(const pb_train_state* st) {
     PB_REQUIRE(st->count_bits >= 1 && st->count_bits <= 13 && st->lo_bits == 32 - 2 * st->count_bits &&
                    st->gq_bits >= st->lo_bits && st->gq_bits <= kGqBitsMax && st->gq_bits <= 63 - 3 * st->count_bits,
                "accumulator widths are not set: call pb_train_prepare first");
-    PB_REQUIRE(((uintptr_t)st->codes % 16 == 0) && ((uintptr_t)st->gq % 16 == 0) && ((uintptr_t)st->slot % 16 == 0),
-               "codes, gq and slot must be 16-byte aligned");
+    PB_REQUIRE(((uintptr_t)st->codes % 16 == 0) && ((uintptr_t)st->gq % 16 == 0) && ((uintptr_t)st->slot % 16 == 0) &&
+                   ((uintptr_t)st->leaf % 16 == 0),
+               "codes, gq, slot and leaf must be 16-byte aligned");
     return PB_OK;
 }
 
@@ -743,7 +758,7 @@ static int launch_partition(const pb_train_state* st, int64_t depth, uint32_t* b
     a.bits = bits;
     a.bits_in = bits_in;
     const size_t smem = sizeof(PartEntry) * (size_t)(1 << depth);
-    const int g = row_grid(st->n_rows);
+    const int g = row_grid((st->n_rows + 7) / 8);  // a thread takes eight rows
     cudaStream_t stream = (cudaStream_t)stream_;
     prof_begin(kProfPartition, stream);
     if (st->code_bits == 4)
