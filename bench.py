@@ -52,22 +52,8 @@ def workload_name(n_rows, n_feat, n_eras):
 # ---------------------------------------------------------------------------------------------
 
 def make_device_data(n_rows, n_feat, n_eras, device, seed=3):
-    import torch
-    g = torch.Generator(device=device)
-    g.manual_seed(seed)
-    X = torch.empty((n_rows, n_feat), dtype=torch.uint8, device=device)
-    step = 1 << 18
-    for a in range(0, n_rows, step):
-        b = min(n_rows, a + step)
-        X[a:b] = torch.randint(0, 5, (b - a, n_feat), generator=g, device=device, dtype=torch.uint8)
-    era = (torch.arange(n_rows, device=device, dtype=torch.int64) * n_eras // n_rows)
-    sel = torch.randperm(n_feat, generator=g, device=device)[:50]
-    w = 0.02 + 0.02 * torch.randn((n_eras, 50), generator=g, device=device)
-    latent = ((X[:, sel].float() - 2.0) * w[era]).sum(1)
-    latent = latent + torch.randn(n_rows, generator=g, device=device) * (latent.std() / 0.02)
-    ranks = torch.argsort(torch.argsort(latent))
-    y = (torch.floor(ranks.float() * 5.0 / n_rows).clamp_(0, 4) * 0.25).float()
-    return X, y, era.to(torch.int16)
+    from packboost_b200.workloads import config3_device
+    return config3_device(n_rows, n_feat, n_eras, device, seed)
 
 
 # ---------------------------------------------------------------------------------------------

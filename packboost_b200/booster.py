@@ -792,6 +792,17 @@ class PackBoost:
     def _pack_rows(self, X: np.ndarray) -> PackedRows:
         if self._binner is None:
             raise RuntimeError("Model must be fitted before predict()")
+        if isinstance(X, torch.Tensor) and X.is_cuda:
+            # device input is consumed where it is (codes: range-checked on the device)
+            Xd = X.detach()
+            if self._binner.bin_edges is None:
+                if Xd.dtype not in (torch.uint8, torch.int8):
+                    raise ValueError("Input must already be prebinned when no edges are provided")
+                Xd = Xd.view(torch.uint8)
+                if Xd.numel() and int(Xd.max()) >= int(self.config.max_bins):
+                    raise ValueError("Input must already be prebinned when no edges are provided")
+                return pack_row_major(Xd, None, self.config.max_bins)
+            return pack_row_major(Xd.to(torch.float32), self._binner.bin_edges, self.config.max_bins)
         X_np = X.detach().cpu().numpy() if isinstance(X, torch.Tensor) else np.asarray(X)
         if self._binner.bin_edges is None:
             if not detect_prebinned(X_np, self.config.max_bins):

@@ -100,6 +100,28 @@ def config3(seed: int = 3, n_rows: int = 2_700_000, n_features: int = 2376, n_er
                     notes="learning_rate fixed at 0.4/pack_size: the pack is summed, not averaged")
 
 
+def config3_device(n_rows: int = 2_700_000, n_features: int = 2376, n_eras: int = 574, device=None, seed: int = 3):
+    """The config-3 table generated on a GPU (same shape, bin count, era structure and signal
+    strength as :func:`config3`, from the device generator): ``(X uint8 [n, F], y float32 [n],
+    era int16 [n])`` as device tensors."""
+    import torch
+    g = torch.Generator(device=device)
+    g.manual_seed(seed)
+    X = torch.empty((n_rows, n_features), dtype=torch.uint8, device=device)
+    step = 1 << 18
+    for a in range(0, n_rows, step):
+        b = min(n_rows, a + step)
+        X[a:b] = torch.randint(0, 5, (b - a, n_features), generator=g, device=device, dtype=torch.uint8)
+    era = (torch.arange(n_rows, device=device, dtype=torch.int64) * n_eras // n_rows)
+    sel = torch.randperm(n_features, generator=g, device=device)[:50]
+    w = 0.02 + 0.02 * torch.randn((n_eras, 50), generator=g, device=device)
+    latent = ((X[:, sel].float() - 2.0) * w[era]).sum(1)
+    latent = latent + torch.randn(n_rows, generator=g, device=device) * (latent.std() / 0.02)
+    ranks = torch.argsort(torch.argsort(latent))
+    y = (torch.floor(ranks.float() * 5.0 / n_rows).clamp_(0, 4) * 0.25).float()
+    return X, y, era.to(torch.int16)
+
+
 def config4(seed: int = 11, n_rows: int = 1_000_000, n_features: int = 500, n_eras: int = 200,
             num_rounds: int = 200, max_bins: int = 128, tree_depth: int = 8) -> Workload:
     """Deep frontier: target is a seeded random depth-8 tree over the features."""
