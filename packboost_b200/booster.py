@@ -44,7 +44,7 @@ from . import backends as B
 from .config import PackBoostConfig
 from .sharding import dealt_part, feature_map, local_part
 from .data import (BinningResult, PackedMatrix, PackedRows, code_bits_for, detect_prebinned, pack_feature_major,
-                   pack_row_major, quantile_edges)
+                   pack_row_major, quantile_edges_device)
 
 # ------------------------------ tree containers ------------------------------
 
@@ -582,10 +582,10 @@ class PackBoost:
         else:
             if on_device:
                 X_src = X_np.to(torch.float32)
-                edges = quantile_edges(X_src.cpu().numpy(), cfg.max_bins)
+                edges = quantile_edges_device(X_src, cfg.max_bins)
             else:
                 X_src = X_np.astype(np.float32, copy=False)
-                edges = quantile_edges(X_src, cfg.max_bins)
+                edges = quantile_edges_device(X_src, cfg.max_bins)
             self._binner = BinningResult(bins=None, bin_edges=edges, prebinned=False)
 
         rank, world = 0, 1

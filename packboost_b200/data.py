@@ -56,6 +56,55 @@ def quantile_edges(X: np.ndarray, max_bins: int) -> np.ndarray:
     return np.quantile(X, q, axis=0, method="linear").astype(np.float32)
 
 
+def edges_from_sorted(sorted_cols: torch.Tensor, max_bins: int) -> np.ndarray:
+    """Interior quantile edges of columns that are already sorted ascending (NaN last), with the
+    arithmetic of ``np.quantile(..., method="linear")`` step for step: virtual index
+    ``(n - 1) * q`` in float64, the two neighbours taken from the float32 column, their float32
+    difference, then ``a + d * t`` (``b - d * (1 - t)`` where ``t >= 0.5``) in float64.  A column
+    that holds a NaN gets NaN edges.  Only the two gathers touch the big array; the interpolation
+    runs on the host on ``2 * (max_bins - 1) * F`` numbers.  ``float64 [max_bins - 1, F]``."""
+    n = int(sorted_cols.shape[0])
+    q = np.linspace(0.0, 1.0, max_bins + 1, dtype=np.float64)[1:-1]
+    virtual = (n - 1) * q
+    prev = np.floor(virtual).astype(np.int64)
+    nxt = prev + 1
+    above = virtual >= n - 1
+    prev[above] = n - 1
+    nxt[above] = n - 1
+    below = virtual < 0
+    prev[below] = 0
+    nxt[below] = 0
+    dev = sorted_cols.device
+    a = sorted_cols[torch.from_numpy(prev).to(dev)].cpu().numpy()
+    b = sorted_cols[torch.from_numpy(nxt).to(dev)].cpu().numpy()
+    has_nan = torch.isnan(sorted_cols[-1]).cpu().numpy()
+    t = (virtual - prev).reshape(-1, 1)
+    d = np.subtract(b, a)                      # float32, as in numpy's _lerp
+    with np.errstate(invalid="ignore"):
+        out = np.add(a, d * t)
+        np.subtract(b, d * (1 - t), out=out, where=np.broadcast_to(t >= 0.5, out.shape))
+    out[:, has_nan] = np.nan
+    return out
+
+
+def quantile_edges_device(X: np.ndarray | torch.Tensor, max_bins: int) -> np.ndarray:
+    """``quantile_edges`` with the sort on the GPU (a column sort of 500 000 x 256 floats takes
+    seconds on the host and milliseconds on the device); same result bit for bit up to the sign
+    of a zero.  ``X``: float32 ``[N, F]``, host array or tensor on either side."""
+    dev = _device()
+    n, f = X.shape
+    cols = max(1, min(f, (256 << 20) // max(4 * n, 1)))   # about 256 MB of floats per sort
+    out = np.empty((max_bins - 1, f), dtype=np.float64)
+    for c0 in range(0, f, cols):
+        c1 = min(f, c0 + cols)
+        if isinstance(X, torch.Tensor):
+            block = X[:, c0:c1].to(device=dev, dtype=torch.float32)
+        else:
+            block = torch.from_numpy(np.ascontiguousarray(X[:, c0:c1], dtype=np.float32)).to(dev)
+        out[:, c0:c1] = edges_from_sorted(torch.sort(block, dim=0).values, max_bins)
+    return out.astype(np.float32)
+
+
 def code_bits_for(max_bins: int) -> int:
     return 4 if max_bins <= 16 else 8
 

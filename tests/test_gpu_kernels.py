@@ -188,3 +188,15 @@ def test_era_correlation_matches_host_formula():
     assert np.isnan(c[[1, 3, 5]]).all() and np.isfinite(c[[0, 2, 4]]).all()
     want = _era_correlation_np(era, y, p)
     np.testing.assert_allclose(c[np.isfinite(c)].mean(), want, rtol=1e-5)
+
+
+def test_device_quantile_edges_equal_host_quantile_edges():
+    from packboost_b200.data import quantile_edges, quantile_edges_device
+    rng = np.random.default_rng(3)
+    X = rng.normal(size=(60_001, 33)).astype(np.float32)
+    X[:, 4] = np.round(X[:, 4] * 2)
+    X[:, 9] = np.exp(X[:, 9])
+    for nb in (5, 128):
+        want = quantile_edges(X, nb)
+        assert np.array_equal(quantile_edges_device(X, nb), want)
+        assert np.array_equal(quantile_edges_device(torch.from_numpy(X).cuda(), nb), want)

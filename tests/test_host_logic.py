@@ -85,6 +85,26 @@ def test_feature_map_and_local_part_partition_the_features():
     assert np.array_equal(np.sort(np.concatenate(pos_all)), np.arange(11))
 
 
+def test_edges_from_sorted_columns_equal_numpy_quantile():
+    """The interpolation that follows the device sort of the binning step against
+    ``np.quantile(method="linear")``: ties, a binary column, a column with NaNs, tiny inputs."""
+    import torch
+    from packboost_b200.data import edges_from_sorted
+    rng = np.random.default_rng(0)
+    for n, f, nb in [(1000, 7, 128), (1537, 5, 64), (20000, 9, 128), (17, 4, 5), (2, 2, 16), (1, 2, 4), (5000, 6, 255)]:
+        X = rng.normal(size=(n, f)).astype(np.float32)
+        if f > 2:
+            X[:, 1] = np.round(X[:, 1])
+            X[:, 2] = X[:, 2] > 0
+        if f > 3:
+            X[::7, 3] = np.nan
+        with np.errstate(all="ignore"):
+            want = np.quantile(X, np.linspace(0.0, 1.0, nb + 1, dtype=np.float64)[1:-1], axis=0, method="linear")
+        got = edges_from_sorted(torch.sort(torch.from_numpy(X), dim=0).values, nb)
+        assert got.dtype == np.float64 and got.shape == want.shape
+        assert np.array_equal(got, want, equal_nan=True)
+
+
 def test_dealt_part_gives_equal_disjoint_shares():
     """Replicated-codes layout: the sampled list is dealt by position; shares are disjoint, cover
     the list, differ by at most one feature and do not depend on which features were drawn."""
