@@ -68,7 +68,7 @@ __device__ __forceinline__ float2 gain_of(uint32_t lc, long long lgq, uint32_t t
 }
 
 // ---- few bins: a thread scans the bins of its (era, node) in registers ---------------------------
-template <int KT>  // compile-time bound of the threshold count
+template <int KT, int NBT>  // compile-time bounds of the threshold count and of the bin count
 __global__ void __launch_bounds__(kGainThreads) gain_kernel_small(GainArgs a) {
     const ScoreLaunch& s = a.s;
     __shared__ uint32_t s_lc[32 * kSmallBins];
@@ -106,8 +106,21 @@ __global__ void __launch_bounds__(kGainThreads) gain_kernel_small(GainArgs a) {
     }
 
     if (node < n_nodes) {
-        for (int e = e_begin + e_lane; e < e_end; e += e_step) {
+        // The histogram row of the next era is loaded while the current one is worked on: the rows
+        // come from HBM and a thread has little else to overlap their latency with.
+        uint32_t hc[NBT], hc_next[NBT];
+        long long hg[NBT], hg_next[NBT];
+        auto load_row = [&](int e, uint32_t (&rc)[NBT], long long (&rg)[NBT]) {
             const size_t base = (((size_t)f * E + e) * s.node_stride + node) * NB;
+#pragma unroll
+            for (int b = 0; b < NBT; ++b) {
+                rc[b] = (b < NB) ? s.cnt[base + b] : 0u;
+                rg[b] = (b < NB) ? s.gsum[base + b] : 0ll;
+            }
+        };
+        if (e_begin + e_lane < e_end) load_row(e_begin + e_lane, hc, hg);
+        for (int e = e_begin + e_lane; e < e_end; e += e_step) {
+            if (e + e_step < e_end) load_row(e + e_step, hc_next, hg_next);
             // running prefix over the bins; threshold k keeps the prefix at its bin (selects with
             // static indices, so everything stays in registers)
             uint32_t lcs[KT];
@@ -120,10 +133,10 @@ __global__ void __launch_bounds__(kGainThreads) gain_kernel_small(GainArgs a) {
             uint32_t c = 0;
             long long g = 0;
 #pragma unroll
-            for (int b = 0; b < kSmallBins; ++b) {
+            for (int b = 0; b < NBT; ++b) {
                 if (b < NB) {
-                    c += s.cnt[base + b];
-                    g += s.gsum[base + b];
+                    c += hc[b];
+                    g += hg[b];
 #pragma unroll
                     for (int k = 0; k < KT; ++k) {
                         const bool at = (k < K) && (thr[k] == b);
@@ -158,6 +171,11 @@ __global__ void __launch_bounds__(kGainThreads) gain_kernel_small(GainArgs a) {
 #pragma unroll
                 for (int k = 0; k < KT; ++k)
                     if (k < K) out[k] = gk[k];
+            }
+#pragma unroll
+            for (int b = 0; b < NBT; ++b) {
+                hc[b] = hc_next[b];
+                hg[b] = hg_next[b];
             }
         }
     }
@@ -707,8 +725,8 @@ int launch_score(const ScoreLaunch& s, cudaStream_t stream) {
         g.era_splits = splits;
         dim3 grid((unsigned)s.n_feat, (unsigned)groups, (unsigned)splits);
         if (grid.y > 65535u) return fail_arg("scorer grid too large");
-        if (K <= 4) gain_kernel_small<4><<<grid, kGainThreads, 0, stream>>>(g);
-        else gain_kernel_small<kSmallBins><<<grid, kGainThreads, 0, stream>>>(g);
+        if (K <= 4 && NB <= 5) gain_kernel_small<4, 5><<<grid, kGainThreads, 0, stream>>>(g);
+        else gain_kernel_small<kSmallBins, kSmallBins><<<grid, kGainThreads, 0, stream>>>(g);
     } else {
         const int warps = kGainThreads / 32;
         const int groups = (s.n_nodes_max + warps - 1) / warps;
