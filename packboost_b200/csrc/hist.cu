@@ -293,7 +293,11 @@ __global__ void __launch_bounds__(kLaneWarps * 32, 2) hist_lane_kernel(HistKerne
         for (int i = 0; i < FPL; ++i) {
             const unsigned char* p = frow[i] + (int64_t)c * (kLaneRows / 2) + phase * (PR / 2);
             if (R == 1) {
-                const uint4 v0 = __ldg(reinterpret_cast<const uint4*>(p)), v1 = __ldg(reinterpret_cast<const uint4*>(p) + 1);
+                // one 32-byte sector per lane in a single 256-bit load
+                uint4 v0, v1;
+                asm("ld.global.nc.v8.u32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];\n"
+                    : "=r"(v0.x), "=r"(v0.y), "=r"(v0.z), "=r"(v0.w), "=r"(v1.x), "=r"(v1.y), "=r"(v1.z), "=r"(v1.w)
+                    : "l"(p));
                 ww[i][0] = v0.x; ww[i][1] = v0.y; ww[i][2] = v0.z; ww[i][3] = v0.w;
                 ww[i][WPP - 4] = v1.x; ww[i][WPP - 3] = v1.y; ww[i][WPP - 2] = v1.z; ww[i][WPP - 1] = v1.w;
             } else if (R == 2) {
