@@ -237,8 +237,22 @@ __global__ void __launch_bounds__(kGainThreads) gain_kernel_wide(GainArgs a) {
         lg_sum[i] = 0ll;
     }
 
-    for (int e = e_begin; e < e_end; ++e) {
+    // the histogram row of the next era is loaded while the current one is scanned and scored
+    uint32_t rc[8], rc_next[8];
+    long long rg[8], rg_next[8];
+    auto load_row = [&](int e, uint32_t (&oc)[8], long long (&og)[8]) {
         const size_t base = (((size_t)f * E + e) * s.node_stride + node) * NB;
+#pragma unroll
+        for (int it = 0; it < 8; ++it) {
+            const int b = it * 32 + lane;
+            const bool in = (it < iters) && (b < NB);
+            oc[it] = in ? s.cnt[base + b] : 0u;
+            og[it] = in ? s.gsum[base + b] : 0ll;
+        }
+    };
+    if (e_begin < e_end) load_row(e_begin, rc, rg);
+    for (int e = e_begin; e < e_end; ++e) {
+        if (e + 1 < e_end) load_row(e + 1, rc_next, rg_next);
         uint32_t pc[8];
         long long pg[8];
         uint32_t carry_c = 0;
@@ -246,9 +260,8 @@ __global__ void __launch_bounds__(kGainThreads) gain_kernel_wide(GainArgs a) {
 #pragma unroll
         for (int it = 0; it < 8; ++it) {
             if (it < iters) {
-                const int b = it * 32 + lane;
-                uint32_t c = (b < NB) ? s.cnt[base + b] : 0u;
-                long long g = (b < NB) ? s.gsum[base + b] : 0ll;
+                uint32_t c = rc[it];
+                long long g = rg[it];
                 for (int d = 1; d < 32; d <<= 1) {
                     const uint32_t c2 = __shfl_up_sync(full, c, d);
                     const long long g2 = __shfl_up_sync(full, g, d);
@@ -282,6 +295,11 @@ __global__ void __launch_bounds__(kGainThreads) gain_kernel_wide(GainArgs a) {
                     lg_sum[it] += pg[it];
                 }
             }
+        }
+#pragma unroll
+        for (int it = 0; it < 8; ++it) {
+            rc[it] = rc_next[it];
+            rg[it] = rg_next[it];
         }
     }
 #pragma unroll
