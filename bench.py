@@ -122,6 +122,55 @@ def pick_sample_eras(steps, warmup, n_eras, budget_s=90.0, per_era_round_s=0.2):
     return max(2, min(e, 24, n_eras))
 
 
+def predict_bench(n_rows, n_rounds, steps, warmup):
+    """Side benchmark of the ensemble predictor (one GPU): a seeded random ensemble in the
+    8-byte node format scored through pb_predict_rows_packed; prints one JSON line."""
+    import numpy as np
+    import torch
+    from packboost_b200 import backends as B, workloads
+    from packboost_b200.data import pack_row_major
+    steps, warmup = max(1, min(steps, 10)), max(1, min(warmup, 3))
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(0)
+    w = workloads.config5(seed=5, n_rows=8, n_features=N_FEAT, n_rounds=n_rounds, pack_size=32, depth=6)
+    feature, threshold, leaf = w.extra["feature"], w.extra["threshold"], w.extra["leaf"]
+    T, n_int = feature.shape
+    idx = np.arange(n_int, dtype=np.uint32)   # heap order: children of node i are 2i+1 and 2i+2
+    w0 = np.concatenate([(feature.astype(np.uint32) & 0xFFFF) | (threshold.astype(np.uint32) << 16),
+                         np.full(leaf.shape, 1 << 31, np.uint32)], axis=1)
+    w1 = np.concatenate([np.broadcast_to(2 * idx + 1, (T, n_int)), leaf.view(np.uint32)], axis=1)
+    per_tree = w0.shape[1]
+    packed = torch.from_numpy(np.stack([w0, w1], axis=2).reshape(-1, 2).view(np.int32).copy()).to(dev)
+    offs = torch.arange(T + 1, dtype=torch.int32, device=dev) * per_tree
+    g = torch.Generator(device=dev)
+    g.manual_seed(1)
+    X = torch.randint(0, 5, (n_rows, N_FEAT), generator=g, device=dev, dtype=torch.uint8)
+    rows = pack_row_major(X, None, 5)
+    out = torch.empty(n_rows, dtype=torch.float32, device=dev)
+    lib = B.lib()
+
+    def run():
+        B.check(lib.pb_predict_rows_packed(rows.codes.data_ptr(), n_rows, rows.pitch_row, rows.code_bits,
+                                           packed.data_ptr(), offs.data_ptr(), 0, T, per_tree, 1.0, out.data_ptr(), 0,
+                                           torch.cuda.current_stream().cuda_stream))
+    for _ in range(warmup):
+        run()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        run()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / steps
+    print(json.dumps({"metric": "predictor_node_visits_per_sec", "value": n_rows * T * 6 / (ms / 1000.0), "unit": "visits/s",
+                      "n_gpus": 1, "steps": steps, "warmup": warmup, "ms_per_step": ms, "higher_is_better": True,
+                      "dtype": "f32", "data": "synthetic",
+                      "config": {"workload": f"ensemble inference: {n_rows} rows x {N_FEAT} five-level features, "
+                                             f"{T} complete depth-6 trees"},
+                      "rows_per_sec": n_rows / (ms / 1000.0)}))
+
+
 # ---------------------------------------------------------------------------------------------
 
 def main():
@@ -133,7 +182,13 @@ def main():
     ap.add_argument("--scale", type=float, default=1.0, help="row/era scale of the workload (profiling captures use < 1)")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--predict", type=int, nargs=2, metavar=("ROWS", "ROUNDS"),
+                    help="time the ensemble predictor instead: ROWS rows x 2376 five-level features scored by "
+                         "ROUNDS x 32 complete depth-6 trees (the inference-only workload is 5 000 000 x 2000)")
     args = ap.parse_args()
+    if args.predict:
+        predict_bench(args.predict[0], args.predict[1], args.steps, args.warmup)
+        return
 
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
