@@ -230,6 +230,32 @@ constexpr int kLaneRows = 64;              // rows per warp step: 32 bytes of 4-
 // phases: 32 / R lanes own tuples and phase p of them walks rows [p, p + 1) * 64 / R of the chunk,
 // so a row step of the warp covers R rows.  The R lanes that own the same tuple keep private cell
 // columns as always; the flush adds them up.
+constexpr int kLaneBinsMax = 16;  // 4-bit codes
+
+// The nb bins of one (feature, node) are contiguous in both output arrays but start on an odd or
+// even element: they are written as pairs (8 bytes of counts, 16 bytes of sums) from the first
+// even element on, which takes three stores per array for five bins instead of five.  The lanes
+// of a warp write to 32 different features, so every store of a lane is a memory wavefront of its
+// own and their number is what the flush costs.
+template <int ODD>
+__device__ __forceinline__ void store_bins(uint32_t* cnt, int64_t* gsum, const uint32_t (&cb)[kLaneBinsMax],
+                                           const long long (&gb)[kLaneBinsMax], int nb) {
+    if (ODD) {
+        cnt[0] = cb[0];
+        gsum[0] = gb[0];
+    }
+#pragma unroll
+    for (int k = ODD; k < kLaneBinsMax; k += 2) {
+        if (k + 1 < nb) {
+            *reinterpret_cast<uint2*>(cnt + k) = make_uint2(cb[k], cb[(k + 1) % kLaneBinsMax]);
+            *reinterpret_cast<longlong2*>(gsum + k) = make_longlong2(gb[k], gb[(k + 1) % kLaneBinsMax]);
+        } else if (k < nb) {
+            cnt[k] = cb[k];
+            gsum[k] = gb[k];
+        }
+    }
+}
+
 template <int A, int T, int R>
 __global__ void __launch_bounds__(kLaneWarps * 32, 2) hist_lane_kernel(HistKernelArgs a) {
     extern __shared__ __align__(16) unsigned char smb[];  // cells [T][n_cells] | staging [warps][64] uint2
@@ -393,7 +419,14 @@ __global__ void __launch_bounds__(kLaneWarps * 32, 2) hist_lane_kernel(HistKerne
         for (int i = 0; i < fi; ++i) below *= nb;
         const int above = cpn / (below * nb);
         const uint32_t* tcells = cells + (size_t)t * n_cells * 64;
-        for (int b = 0; b < nb; ++b) {
+        const size_t o0 = (((size_t)(feat0 + fl) * a.n_eras + era) * a.node_stride + n) * nb;
+        uint32_t cb[kLaneBinsMax];   // the bins of this (feature, node), stored together below
+        long long gb[kLaneBinsMax];
+#pragma unroll
+        for (int b = 0; b < kLaneBinsMax; ++b) {
+            cb[b] = 0u;
+            gb[b] = 0ll;
+            if (b >= nb) continue;
             // The packed words of the joint cells are added as they are: the rows behind them are
             // disjoint subsets of the tile, so neither field can overflow; decode once per bin.
             uint32_t a_sum = 0, b_sum = 0;
@@ -406,16 +439,20 @@ __global__ void __launch_bounds__(kLaneWarps * 32, 2) hist_lane_kernel(HistKerne
                         b_sum += tcells[cell + ph * TL + 32];
                     }
                 }
-            const uint32_t count = a_sum & cmask;
-            const long long gs = (long long)(int32_t)b_sum * (1ll << LB) + (long long)(a_sum >> CB);
-            const size_t o = (((size_t)(feat0 + fl) * a.n_eras + era) * a.node_stride + n) * nb + b;
-            if (a.use_atomics) {
-                if (count) atomicAdd(a.cnt + o, count);
-                if (gs) atomicAdd(reinterpret_cast<unsigned long long*>(a.gsum + o), (unsigned long long)gs);
-            } else {
-                a.cnt[o] = count;
-                a.gsum[o] = gs;
+            cb[b] = a_sum & cmask;
+            gb[b] = (long long)(int32_t)b_sum * (1ll << LB) + (long long)(a_sum >> CB);
+        }
+        if (a.use_atomics) {
+#pragma unroll
+            for (int b = 0; b < kLaneBinsMax; ++b) {
+                if (b >= nb) continue;
+                if (cb[b]) atomicAdd(a.cnt + o0 + b, cb[b]);
+                if (gb[b]) atomicAdd(reinterpret_cast<unsigned long long*>(a.gsum + o0 + b), (unsigned long long)gb[b]);
             }
+        } else if (o0 & 1) {
+            store_bins<1>(a.cnt + o0, a.gsum + o0, cb, gb, nb);
+        } else {
+            store_bins<0>(a.cnt + o0, a.gsum + o0, cb, gb, nb);
         }
     }
 }
