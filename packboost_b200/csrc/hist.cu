@@ -411,36 +411,15 @@ __global__ void __launch_bounds__(kLaneWarps * 32, 2) hist_lane_kernel(HistKerne
     // warp take different items and add up the columns of the R lanes that own the tuple
     const uint32_t cmask = (1u << CB) - 1u;
     const int col0 = lane - phase * TL;
-    for (int item = warp * R + phase; item < n_nodes * FPL; item += kLaneWarps * R) {
-        const int n = item / FPL, fl = item - n * FPL;  // node, feature of the lane
-        if (fl >= n_mine) continue;
-        const int t = fl / A, fi = fl - t * A;
-        int below = 1;  // bins^fi
-        for (int i = 0; i < fi; ++i) below *= nb;
-        const int above = cpn / (below * nb);
-        const uint32_t* tcells = cells + (size_t)t * n_cells * 64;
+    // decode the packed sums of the bins of one (feature, node) and write them out
+    auto emit = [&](int fl, int n, const uint32_t (&aw)[kLaneBinsMax], const uint32_t (&bw)[kLaneBinsMax]) {
         const size_t o0 = (((size_t)(feat0 + fl) * a.n_eras + era) * a.node_stride + n) * nb;
-        uint32_t cb[kLaneBinsMax];   // the bins of this (feature, node), stored together below
+        uint32_t cb[kLaneBinsMax];
         long long gb[kLaneBinsMax];
 #pragma unroll
         for (int b = 0; b < kLaneBinsMax; ++b) {
-            cb[b] = 0u;
-            gb[b] = 0ll;
-            if (b >= nb) continue;
-            // The packed words of the joint cells are added as they are: the rows behind them are
-            // disjoint subsets of the tile, so neither field can overflow; decode once per bin.
-            uint32_t a_sum = 0, b_sum = 0;
-            for (int hi = 0; hi < above; ++hi)
-                for (int lo = 0; lo < below; ++lo) {
-                    const uint32_t cell = (uint32_t)(n * cpn + (hi * nb + b) * below + lo) * 64u + col0;
-#pragma unroll
-                    for (int ph = 0; ph < R; ++ph) {
-                        a_sum += tcells[cell + ph * TL];
-                        b_sum += tcells[cell + ph * TL + 32];
-                    }
-                }
-            cb[b] = a_sum & cmask;
-            gb[b] = (long long)(int32_t)b_sum * (1ll << LB) + (long long)(a_sum >> CB);
+            cb[b] = aw[b] & cmask;
+            gb[b] = (long long)(int32_t)bw[b] * (1ll << LB) + (long long)(aw[b] >> CB);
         }
         if (a.use_atomics) {
 #pragma unroll
@@ -454,6 +433,130 @@ __global__ void __launch_bounds__(kLaneWarps * 32, 2) hist_lane_kernel(HistKerne
         } else {
             store_bins<0>(a.cnt + o0, a.gsum + o0, cb, gb, nb);
         }
+    };
+    if (nb == 5 && !a.use_atomics && ((a.n_nodes | a.node_stride) & 3) == 0 && A <= 2 &&
+        ((reinterpret_cast<uintptr_t>(a.cnt) | reinterpret_cast<uintptr_t>(a.gsum)) & 15) == 0) {
+        // Five-level codes, four nodes at a time: the 20 bins of a feature in four consecutive nodes
+        // are contiguous in both output arrays and start on 16 bytes, so they leave as five 16-byte
+        // stores of counts and ten of sums (3.75 store wavefronts per node instead of 6).  Nodes
+        // past the live frontier have empty cells and write zeros into rows nobody reads.
+        auto emit20 = [&](int fl, int n0, const uint32_t (&aw)[20], const uint32_t (&bw)[20]) {
+            const size_t o0 = (((size_t)(feat0 + fl) * a.n_eras + era) * a.node_stride + n0) * 5;
+            uint4* pc = reinterpret_cast<uint4*>(a.cnt + o0);
+            longlong2* pg = reinterpret_cast<longlong2*>(a.gsum + o0);
+#pragma unroll
+            for (int i = 0; i < 5; ++i)
+                pc[i] = make_uint4(aw[4 * i] & cmask, aw[4 * i + 1] & cmask, aw[4 * i + 2] & cmask, aw[4 * i + 3] & cmask);
+#pragma unroll
+            for (int i = 0; i < 10; ++i)
+                pg[i] = make_longlong2((long long)(int32_t)bw[2 * i] * (1ll << LB) + (long long)(aw[2 * i] >> CB),
+                                       (long long)(int32_t)bw[2 * i + 1] * (1ll << LB) + (long long)(aw[2 * i + 1] >> CB));
+        };
+        const int groups = (n_nodes + 3) >> 2;
+        for (int item = warp * R + phase; item < groups * T; item += kLaneWarps * R) {
+            const int g = item / T, t = item - g * T;
+            if (A * t >= n_mine) continue;
+            const int n0 = 4 * g;
+            const uint32_t* tc = cells + (size_t)t * n_cells * 64 + col0;
+            uint32_t a0[20], b0[20], a1[20], b1[20];
+#pragma unroll
+            for (int i = 0; i < 20; ++i) a0[i] = b0[i] = a1[i] = b1[i] = 0u;
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                if (A == 1) {
+#pragma unroll
+                    for (int c0 = 0; c0 < 5; ++c0) {
+#pragma unroll
+                        for (int ph = 0; ph < R; ++ph) {
+                            a0[q * 5 + c0] += tc[((n0 + q) * 5 + c0) * 64 + ph * TL];
+                            b0[q * 5 + c0] += tc[((n0 + q) * 5 + c0) * 64 + ph * TL + 32];
+                        }
+                    }
+                } else {
+                    // every joint cell is read once and added to the row sum of one feature and the
+                    // column sum of the other; the reads are independent
+#pragma unroll
+                    for (int c1 = 0; c1 < 5; ++c1)
+#pragma unroll
+                        for (int c0 = 0; c0 < 5; ++c0) {
+                            uint32_t aw = 0, bw = 0;
+#pragma unroll
+                            for (int ph = 0; ph < R; ++ph) {
+                                aw += tc[((n0 + q) * 25 + c1 * 5 + c0) * 64 + ph * TL];
+                                bw += tc[((n0 + q) * 25 + c1 * 5 + c0) * 64 + ph * TL + 32];
+                            }
+                            a0[q * 5 + c0] += aw;
+                            b0[q * 5 + c0] += bw;
+                            a1[q * 5 + c1] += aw;
+                            b1[q * 5 + c1] += bw;
+                        }
+                }
+            }
+            emit20(A * t, n0, a0, b0);
+            if (A == 2 && 2 * t + 1 < n_mine) emit20(2 * t + 1, n0, a1, b1);
+        }
+        return;
+    }
+    if (A == 2 && nb == 5) {
+        // Five-level pairs, the common case: every joint cell is read once and added to the row sum
+        // of one feature and the column sum of the other; the 25 reads are independent.
+        for (int item = warp * R + phase; item < n_nodes * T; item += kLaneWarps * R) {
+            const int n = item / T, t = item - n * T;
+            if (2 * t >= n_mine) continue;
+            const uint32_t* tc = cells + (size_t)t * n_cells * 64 + (size_t)(n * 25) * 64 + col0;
+            uint32_t a0[kLaneBinsMax], b0[kLaneBinsMax], a1[kLaneBinsMax], b1[kLaneBinsMax];
+#pragma unroll
+            for (int b = 0; b < kLaneBinsMax; ++b) a0[b] = b0[b] = a1[b] = b1[b] = 0u;
+#pragma unroll
+            for (int c1 = 0; c1 < 5; ++c1)
+#pragma unroll
+                for (int c0 = 0; c0 < 5; ++c0) {
+                    uint32_t aw = 0, bw = 0;
+#pragma unroll
+                    for (int ph = 0; ph < R; ++ph) {
+                        aw += tc[(c1 * 5 + c0) * 64 + ph * TL];
+                        bw += tc[(c1 * 5 + c0) * 64 + ph * TL + 32];
+                    }
+                    a0[c0] += aw;
+                    b0[c0] += bw;
+                    a1[c1] += aw;
+                    b1[c1] += bw;
+                }
+            emit(2 * t, n, a0, b0);
+            if (2 * t + 1 < n_mine) emit(2 * t + 1, n, a1, b1);
+        }
+        return;
+    }
+    for (int item = warp * R + phase; item < n_nodes * FPL; item += kLaneWarps * R) {
+        const int n = item / FPL, fl = item - n * FPL;  // node, feature of the lane
+        if (fl >= n_mine) continue;
+        const int t = fl / A, fi = fl - t * A;
+        int below = 1;  // bins^fi
+        for (int i = 0; i < fi; ++i) below *= nb;
+        const int above = cpn / (below * nb);
+        const uint32_t* tcells = cells + (size_t)t * n_cells * 64;
+        uint32_t aw[kLaneBinsMax], bw[kLaneBinsMax];   // packed sums of the bins of this (feature, node)
+#pragma unroll
+        for (int b = 0; b < kLaneBinsMax; ++b) {
+            aw[b] = 0u;
+            bw[b] = 0u;
+            if (b >= nb) continue;
+            // The packed words of the joint cells are added as they are: the rows behind them are
+            // disjoint subsets of the tile, so neither field can overflow; decoded once per bin.
+            uint32_t a_sum = 0, b_sum = 0;
+            for (int hi = 0; hi < above; ++hi)
+                for (int lo = 0; lo < below; ++lo) {
+                    const uint32_t cell = (uint32_t)(n * cpn + (hi * nb + b) * below + lo) * 64u + col0;
+#pragma unroll
+                    for (int ph = 0; ph < R; ++ph) {
+                        a_sum += tcells[cell + ph * TL];
+                        b_sum += tcells[cell + ph * TL + 32];
+                    }
+                }
+            aw[b] = a_sum;
+            bw[b] = b_sum;
+        }
+        emit(fl, n, aw, bw);
     }
 }
 
