@@ -543,8 +543,15 @@ class PackBoost:
             era_np = np.asarray(era, dtype=np.int16)
             if era_np.shape[0] != N:
                 raise ValueError("era must align with X rows")
-            uniq, inv = np.unique(era_np, return_inverse=True)
-            era_encoded = inv.astype(np.int16)
+            if N > 1 and np.all(era_np[1:] >= era_np[:-1]):
+                # eras already contiguous and ascending: their runs give the unique values directly
+                starts = np.concatenate([[0], np.flatnonzero(era_np[1:] != era_np[:-1]) + 1])
+                uniq = era_np[starts]
+                era_encoded = np.repeat(np.arange(starts.shape[0], dtype=np.int16),
+                                        np.diff(np.concatenate([starts, [N]])))
+            else:
+                uniq, inv = np.unique(era_np, return_inverse=True)
+                era_encoded = inv.astype(np.int16)
         self._era_unique = uniq
         E = int(uniq.shape[0])
         self._feature_names = list(feature_names) if feature_names is not None else [f"f{i}" for i in range(F)]
