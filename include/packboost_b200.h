@@ -129,9 +129,9 @@ typedef struct pb_train_state {
     const int32_t* feat_local;   /* [n_features_total] local row of a global feature, -1 if not held */
     const float* y;              /* [n_rows] */
     float* preds;                /* [n_rows] */
-    int32_t* gq;                 /* [rows_padded] */
-    uint16_t* slot;              /* [rows_padded] */
-    uint16_t* leaf;              /* [rows_padded] */
+    int32_t* gq;                 /* [rows_padded], 16-byte aligned */
+    uint16_t* slot;              /* [rows_padded], 16-byte aligned; pb_round_begin sets the entries past n_rows to 0xFFFF */
+    uint16_t* leaf;              /* [rows_padded], 16-byte aligned */
     void* ctl;                   /* control block, pb_ctl_bytes() bytes, zero-initialised once */
     void* workspace;             /* histogram + candidate scratch */
     int64_t workspace_bytes;
