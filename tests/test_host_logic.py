@@ -172,3 +172,97 @@ def test_two_rank_exchange_merges_disjoint_tables_and_bitmasks():
     out = mp.Manager().dict()
     mp.spawn(_worker, args=(world, _free_port(), out), nprocs=world, join=True)
     assert [out[r] for r in range(world)] == [1, 1]
+
+
+# ---- the round loop of the booster against a scripted device ----------------------------------
+
+class _ScriptedTrainer:
+    """Stands in for the device: round r (counted by accepted enqueues) has live nodes at the first
+    ``used[r]`` depths, every live node splits, and the log is delivered when asked for."""
+
+    def __init__(self, depth, k, used):
+        self.D, self.k, self.used = depth, k, used
+        self.attempts = []          # (round index, subsets, redo)
+        self.round_of_ticket = {}
+        self.next_round = 0
+
+    def n_sampled(self):
+        return self.k
+
+    def run_round(self, subsets, redo=False):
+        if redo:
+            self.next_round -= 1
+        ticket = len(self.attempts)
+        self.attempts.append((self.next_round, [s.copy() for s in subsets], redo))
+        self.round_of_ticket[ticket] = self.next_round
+        self.next_round += 1
+        return ticket
+
+    def read_log(self, ticket):
+        used = self.used[self.round_of_ticket[ticket]]
+        n_ctx = [(1 << d) if d < used else 0 for d in range(self.D + 1)]
+        rows = {}
+        nid = 0
+        for d in range(used):
+            for i in range(1 << d):
+                node = (1 << d) - 1 + i
+                rows[(d, i)] = dict(feature=d, threshold=1, tree_node=node, left_id=2 * node + 1, right_id=2 * node + 2,
+                                    left_value=0.25, right_value=-0.25)
+                nid = max(nid, 2 * node + 2)
+        return _log(rows, n_ctx, n_nodes=nid + 1, depth=self.D)
+
+    def flush_predictions(self):
+        pass
+
+    def release_graph(self):
+        pass
+
+
+def _scripted_booster(monkeypatch, trainer, seed, n_features):
+    from packboost_b200 import booster as bm
+    from packboost_b200.config import PackBoostConfig
+    monkeypatch.setattr(bm.B, "cuda_available", lambda: True)
+    monkeypatch.setattr(torch.cuda, "current_device", lambda: 0)
+    b = bm.PackBoost(PackBoostConfig(device="cuda", max_depth=trainer.D, pack_size=2, random_state=seed,
+                                     layer_feature_fraction=trainer.k / n_features))
+    b._trainer = trainer
+    b._fit_ctx = {"F": n_features, "era_sorted": None, "y_sorted": None}
+    return b
+
+
+@pytest.mark.parametrize("run_ahead", ["1", "0"])
+def test_round_loop_draws_features_like_the_reference_when_rounds_end_early(run_ahead, monkeypatch):
+    """The reference draws one feature subset per depth and only while nodes are live.  The round
+    loop draws all depths up front (and, running ahead, the next round too), so after a round that
+    ends early it must rewind the generator and enqueue the following round again: the subsets of
+    the rounds that count must be exactly the reference's draws, in both loop modes."""
+    monkeypatch.setenv("PACKBOOST_RUN_AHEAD", run_ahead)
+    D, F, k, seed = 3, 40, 9, 123
+    used = [3, 1, 3, 2, 0, 3, 3, 1]            # live depths per round; 0: even the root has no split
+    trainer = _ScriptedTrainer(D, k, used)
+    b = _scripted_booster(monkeypatch, trainer, seed, F)
+    for r in range(len(used)):
+        b._boost_one_round(r, len(used))
+    b._drain()                                 # (what _finish does, without the device synchronisation)
+    b._flush_pending_tree()
+    # reference order of draws
+    g = torch.Generator(device="cpu")
+    g.manual_seed(seed)
+    want = []
+    for r, u in enumerate(used):
+        want.append([torch.randperm(F, generator=g)[:k].numpy().astype(np.int32) for _ in range(u)])
+    accepted = {}
+    for rnd, subsets, _redo in trainer.attempts:
+        accepted[rnd] = subsets                   # the last attempt of a round is the one that counts
+    assert sorted(accepted) == list(range(len(used)))
+    for r, u in enumerate(used):
+        for d in range(u):
+            np.testing.assert_array_equal(accepted[r][d], want[r][d], err_msg=f"round {r} depth {d}")
+    # one tree per round, recorded pack_size times, with the scripted shape
+    assert len(b.trees) == 2 * len(used)
+    sizes = [len(t.nodes) for t in b.trees[::2]]
+    assert sizes == [(1 << (u + 1)) - 1 for u in used]
+    if run_ahead == "1":
+        assert any(redo for _, _, redo in trainer.attempts)
+    else:
+        assert not any(redo for _, _, redo in trainer.attempts)
