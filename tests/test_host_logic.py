@@ -169,7 +169,7 @@ def test_two_rank_exchange_merges_disjoint_tables_and_bitmasks():
     a SUM all-reduce over int32 words merges disjoint candidate records exactly, and a SUM of
     disjoint go-left bit words equals their OR."""
     world = 2
-    out = mp.Manager().dict()
+    out = mp.get_context("spawn").Manager().dict()   # (no fork of this multi-threaded process)
     mp.spawn(_worker, args=(world, _free_port(), out), nprocs=world, join=True)
     assert [out[r] for r in range(world)] == [1, 1]
 
