@@ -69,7 +69,7 @@ __device__ __forceinline__ float2 gain_of(uint32_t lc, long long lgq, uint32_t t
 
 // ---- few bins: a thread scans the bins of its (era, node) in registers ---------------------------
 template <int KT, int NBT>  // compile-time bounds of the threshold count and of the bin count
-__global__ void __launch_bounds__(kGainThreads) gain_kernel_small(GainArgs a) {
+__global__ void __launch_bounds__(kGainThreads, (KT <= 4 && NBT <= 5) ? 3 : 2) gain_kernel_small(GainArgs a) {
     const ScoreLaunch& s = a.s;
     __shared__ uint32_t s_lc[32 * kSmallBins];
     __shared__ unsigned long long s_lg[32 * kSmallBins];
