@@ -19,7 +19,9 @@
  *  codes       feature-major bin codes, one row of `pitch` bytes per (locally owned)
  *              feature.  `code_bits == 8`: one byte per row.  `code_bits == 4` (max_bins
  *              <= 16): two rows per byte, even row in the low nibble.  `pitch` is a
- *              multiple of 128 and covers `rows_padded = roundup(n_rows, 256)` rows.
+ *              multiple of 128 and covers `rows_padded = roundup(n_rows, 256)` rows; the
+ *              buffer starts on a 32-byte boundary (the histogram kernel reads whole
+ *              32-byte sectors with one 256-bit load).
  *  gq          int32 fixed-point gradient per row, `gq = rint(g * scale)` with `scale` a
  *              power of two chosen per round so that `max|gq| <= 2^gq_bits`; gq_bits is 30
  *              when no era tile exceeds 2047 rows, 27 up to 4095 rows and 24 up to 8160 rows
@@ -123,7 +125,7 @@ typedef struct pb_train_state {
     double era_alpha;
     double learning_rate;
     /* device buffers owned by the caller */
-    const uint8_t* codes;        /* [n_features_local][pitch] */
+    const uint8_t* codes;        /* [n_features_local][pitch], 32-byte aligned */
     const int32_t* era_offsets;  /* [n_eras + 1] */
     const int32_t* thr_ids;      /* [n_thresholds] threshold (bin) ids, ascending */
     const int32_t* feat_local;   /* [n_features_total] local row of a global feature, -1 if not held */
@@ -133,7 +135,8 @@ typedef struct pb_train_state {
     uint16_t* slot;              /* [rows_padded], 16-byte aligned; pb_round_begin sets the entries past n_rows to 0xFFFF */
     uint16_t* leaf;              /* [rows_padded], 16-byte aligned */
     void* ctl;                   /* control block, pb_ctl_bytes() bytes, zero-initialised once */
-    void* workspace;             /* histogram + candidate scratch */
+    void* workspace;             /* histogram + candidate scratch; NULL (with workspace_bytes 0) for a host that
+                                    cannot allocate one: see pb_depth_hist_score_static */
     int64_t workspace_bytes;
     /* tiling of the rows computed by pb_train_prepare (host side, read-only afterwards) */
     int64_t max_era_rows;
@@ -192,16 +195,20 @@ int pb_depth_clear_candidates(const pb_train_state* st, int64_t depth, int64_t n
  * they cannot allocate device memory at all: processes whose device memory is reserved in full
  * by another component's pool at start-up, or deployments that forbid device allocation once
  * they are running.  This entry point has no counterpart in the reference.  The per-block
- * histograms live in a fixed 64 MiB array inside the library image (pb_static_scratch_bytes();
- * every GPU that loads the library holds it until the process exits); `st->workspace` is not
- * touched and the candidate table is written to the caller's `cand_out`
- * (24-byte records, `n_sampled` x (1 << depth), same layout as pb_candidates_buffer).
- * Nothing is allocated or freed.  A shape whose single-feature scratch at `depth`
- * (`(1 << depth) * n_eras * (max_bins * 12 + n_thresholds * 8)` bytes of histogram and scorer
- * tables) exceeds the array is rejected with PB_ERR_ARG.  The first call on a device looks up the array's device address
- * (cudaGetSymbolAddress) with that device current; make that first call outside any stream
- * capture.  All calls in a process share the one array, which keeps whatever the previous call
- * left in it: the kernels rewrite every cell they later read, but two calls whose kernels
+ * histograms and scorer tables live in a fixed 64 MiB array inside the library image
+ * (pb_static_scratch_bytes(); every GPU that loads the library holds it until the process
+ * exits); `st->workspace` is not touched and may be NULL (with `workspace_bytes` 0, which
+ * pb_train_prepare accepts).  The candidate table is written to the caller's `cand_out`
+ * (24-byte records, `n_sampled` x (1 << depth), same layout as pb_candidates_buffer); hand the
+ * same buffer to pb_depth_select_cand for the next phase.  pb_round_begin, pb_depth_partition,
+ * pb_round_end and pb_apply_leaf_delta never use the workspace, so a whole round runs without one.
+ * Nothing is allocated or freed.  A shape whose single-feature scratch at `depth`,
+ *   (1 << depth) * (n_eras * (max_bins * 12 + n_thresholds * 8) + n_thresholds * 12) + 1280 bytes
+ * (histogram, per-era gain table, era-summed left counts and gradient sums, alignment), exceeds
+ * the array is rejected with PB_ERR_ARG.  The first call on a device looks up the array's device
+ * address (cudaGetSymbolAddress) with that device current; make that first call outside any
+ * stream capture.  All calls in a process share the one array, which keeps whatever the previous
+ * call left in it: the kernels rewrite every cell they later read, but two calls whose kernels
  * overlap on the GPU (different streams) race on it — serialise them. */
 int64_t pb_static_scratch_bytes(void);
 int pb_depth_hist_score_static(const pb_train_state* st, int64_t depth, const int32_t* feat_rows,
@@ -217,6 +224,11 @@ int pb_depth_hist_score_static(const pb_train_state* st, int64_t depth, const in
  * ids in sampled order. */
 int pb_depth_select(const pb_train_state* st, int64_t depth, const int32_t* sampled_features,
                     int64_t n_sampled, void* stream);
+/* The same with the candidate table passed explicitly (`cand`: 24-byte records, `n_sampled` x
+ * (1 << depth)) instead of being read from the workspace: the table pb_depth_hist_score_static
+ * wrote, or one assembled by the caller from several devices. */
+int pb_depth_select_cand(const pb_train_state* st, int64_t depth, const int32_t* sampled_features,
+                         int64_t n_sampled, const void* cand, void* stream);
 
 /* Route every frontier row to its child (packboost/booster.py:2172-2188: left when
  * code <= threshold) and update `slot` / `leaf`.  Single-device form. */

@@ -83,6 +83,7 @@ _PROTOS: dict[str, tuple[Any, list[Any]]] = {
     "pb_candidates_buffer": (C.c_int, [C.POINTER(TrainState), i64, i64, C.POINTER(vp), C.POINTER(i64)]),
     "pb_depth_clear_candidates": (C.c_int, [C.POINTER(TrainState), i64, i64, vp]),
     "pb_depth_select": (C.c_int, [C.POINTER(TrainState), i64, vp, i64, vp]),
+    "pb_depth_select_cand": (C.c_int, [C.POINTER(TrainState), i64, vp, i64, vp, vp]),
     "pb_depth_partition": (C.c_int, [C.POINTER(TrainState), i64, vp]),
     "pb_depth_goleft_bits": (C.c_int, [C.POINTER(TrainState), i64, vp, vp]),
     "pb_depth_apply_bits": (C.c_int, [C.POINTER(TrainState), i64, vp, vp]),
@@ -201,6 +202,9 @@ def predict_bins_cuda(bins_fm, feature, threshold, left, right, value, is_leaf):
     is_leaf = is_leaf.to(torch.uint8).contiguous()
     _need_cuda(bins_fm, feature, threshold, left, right, value, is_leaf)
     F, N = bins_fm.shape
+    from ..forest import validate_forest
+    validate_forest(feature.cpu().numpy(), threshold.cpu().numpy(), left.cpu().numpy(), right.cpu().numpy(),
+                    is_leaf.cpu().numpy(), [0, feature.numel()], n_features=F)
     out = torch.empty(N, dtype=torch.float32, device=bins_fm.device)
     check(lib().pb_predict_bins_fm(_ptr(bins_fm), F, N, _ptr(feature), _ptr(threshold), _ptr(left), _ptr(right),
                                    _ptr(value), _ptr(is_leaf), feature.numel(), _ptr(out), _stream()))
@@ -220,6 +224,9 @@ def predict_pack_cuda(bins_fm, feature, threshold, left_abs, right_abs, value, i
     is_leaf = is_leaf.to(torch.uint8).contiguous()
     _need_cuda(bins_fm, feature, threshold, left_abs, right_abs, value, is_leaf, offsets)
     F, N = bins_fm.shape
+    from ..forest import validate_forest
+    validate_forest(feature.cpu().numpy(), threshold.cpu().numpy(), left_abs.cpu().numpy(), right_abs.cpu().numpy(),
+                    is_leaf.cpu().numpy(), offsets.cpu().numpy(), n_features=F, absolute_children=True)
     out = torch.empty(N, dtype=torch.float32, device=bins_fm.device)
     check(lib().pb_predict_pack_fm(_ptr(bins_fm), F, N, _ptr(feature), _ptr(threshold), _ptr(left_abs),
                                    _ptr(right_abs), _ptr(value), _ptr(is_leaf), _ptr(offsets), offsets.numel() - 1,

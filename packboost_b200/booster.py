@@ -42,7 +42,8 @@ import torch
 
 from . import backends as B
 from .config import PackBoostConfig
-from .sharding import dealt_part, feature_map, local_part
+from .forest import validate_forest
+from .sharding import choose_replicated, dealt_part, feature_map, local_part
 from .data import (BinningResult, PackedMatrix, PackedRows, code_bits_for, detect_prebinned, pack_feature_major,
                    pack_row_major, quantile_edges_device)
 
@@ -482,6 +483,7 @@ class PackBoost:
         self._fit_ctx: dict | None = None
         self._eval_states: list = []
         self._last_n_ctx: list[int] = []
+        self._split_log: list[np.ndarray] = []
         self._pending_log = None
         self._predrawn = None
         self._inflight = None  # (log ticket, generator state at the round's start) of the enqueued round
@@ -603,11 +605,14 @@ class PackBoost:
         # memory it is kept on every rank anyway: each rank can then route rows itself and the
         # per-depth go-left bitmask exchange disappears (one all-reduce per depth instead of two).
         # PACKBOOST_SHARD_CODES=1 forces the memory-sharded layout.
+        # The choice is agreed by all ranks (their GPUs may have different amounts of free memory,
+        # and the two layouts issue different collectives).
         replicate = False
-        if world > 1 and os.getenv("PACKBOOST_SHARD_CODES") != "1":
+        if world > 1:
             bits = code_bits_for(cfg.max_bins)
             free, _tot = torch.cuda.mem_get_info(self._device)
-            replicate = (N * F * bits // 8) < 0.25 * free
+            replicate = choose_replicated(N * F * bits // 8, free, world,
+                                          os.getenv("PACKBOOST_SHARD_CODES") == "1", self._device)
         if world > 1 and not replicate:
             feat_local = feature_map(F, rank, world)
         else:
@@ -623,6 +628,7 @@ class PackBoost:
         self._fit_ctx = {"era_sorted": era_sorted, "y_sorted": y_sorted, "F": F}
 
         self._depth_logs = []
+        self._split_log = []
         self._round_metrics = []
         self._trees = []
         self._distinct = []
@@ -721,6 +727,8 @@ class PackBoost:
         k = self._trainer.n_sampled()
         for d in range(used):
             self._depth_logs.append(self._depth_log(d, n_ctx[d], k))
+            w = winners[(1 << d) - 1: (1 << d) - 1 + n_ctx[d]]
+            self._split_log.append(w[w["feature"] >= 0].copy())
         self._flush_pending_tree()
         self._pending_log = (head.copy(), winners[: (1 << D) - 1].copy())
         return used == D
@@ -751,6 +759,17 @@ class PackBoost:
         out = np.empty_like(p)
         out[self._row_order] = p
         return out
+
+    def split_records(self) -> dict[str, np.ndarray]:
+        """Every split of the fit in the order the frontier produced it (round, depth, frontier
+        position): tree node, feature, threshold, DES score (the ``SplitDecision.score`` of
+        ``packboost/booster.py:206-217``), rows sent left and rows of the node."""
+        self._drain()
+        rec = (np.concatenate(self._split_log) if self._split_log else np.zeros(0, dtype=_WINNER_DT))
+        return {"node": rec["tree_node"].astype(np.int32), "feature": rec["feature"].astype(np.int32),
+                "threshold": rec["threshold"].astype(np.int32), "score": rec["score"].astype(np.float32),
+                "left_count": rec["left_count"].astype(np.int64),
+                "right_count": (rec["total_count"] - rec["left_count"]).astype(np.int64)}
 
     def _depth_log(self, depth: int, n_nodes: int, k: int) -> dict[str, object]:
         blk = int(self.config.feature_block_size)
@@ -823,10 +842,13 @@ class PackBoost:
         offs = np.zeros(len(arrs) + 1, dtype=np.int32)
         np.cumsum([a["feature"].shape[0] for a in arrs], out=offs[1:])
         cat = {k: np.concatenate([a[k] for a in arrs]) for k in ("feature", "threshold", "left", "right", "value", "is_leaf")}
+        # nothing malformed reaches the device: children inside their tree and after their parent
+        validate_forest(cat["feature"], cat["threshold"], cat["left"], cat["right"], cat["is_leaf"], offs)
         out = {k: torch.from_numpy(v).to(self._device) for k, v in cat.items()}
         out["offsets"] = torch.from_numpy(offs).to(self._device)
         out["repeat"] = torch.tensor([r for _, r in distinct], dtype=torch.int32, device=self._device)
         out["n_trees"] = len(arrs)
+        out["max_feature"] = int(cat["feature"][cat["is_leaf"] == 0].max(initial=-1))
         # packed 8-byte nodes when the trees allow it (right child == left child + 1, small ids)
         internal = cat["is_leaf"] == 0
         ok = (bool(np.all(cat["right"][internal] == cat["left"][internal] + 1))
@@ -846,6 +868,8 @@ class PackBoost:
         if rows.n_rows == 0:
             return out
         f = forest
+        if f["max_feature"] >= rows.n_features:
+            raise ValueError(f"the ensemble splits on feature {f['max_feature']} but the input has {rows.n_features} columns")
         if "packed" in f:
             B.check(B.lib().pb_predict_rows_packed(
                 rows.codes.data_ptr(), rows.n_rows, rows.pitch_row, rows.code_bits, f["packed"].data_ptr(),
@@ -891,6 +915,12 @@ class PackBoost:
                    repeats: Sequence[int] | None = None) -> "PackBoost":
         """Install an externally built ensemble (inference-only use)."""
         reps = list(repeats) if repeats is not None else [1] * len(trees)
+        if len(reps) != len(trees) or any(int(r) < 0 for r in reps):
+            raise ValueError("repeats must hold one non-negative count per tree")
+        for t in trees:  # checked on the host, before any launch
+            a = t.arrays()
+            validate_forest(a["feature"], a["threshold"], a["left"], a["right"], a["is_leaf"],
+                            [0, a["feature"].shape[0]])
         self._distinct = list(zip(trees, reps))
         self._trees = [t for t, r in self._distinct for _ in range(r)]
         self._tree_weight = float(tree_weight)

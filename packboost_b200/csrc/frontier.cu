@@ -514,18 +514,29 @@ static int check_state(const pb_train_state* st) {
                "pitch=%lld does not cover the padded rows", (long long)st->pitch);
     PB_REQUIRE(st->n_thresholds >= 1 && st->n_thresholds < st->max_bins, "n_thresholds out of range");
     PB_REQUIRE(st->codes && st->era_offsets && st->thr_ids && st->feat_local && st->y && st->preds && st->gq &&
-                   st->slot && st->leaf && st->ctl && st->workspace,
+                   st->slot && st->leaf && st->ctl,
                "a device buffer of the training state is null");
+    // (`workspace` may be null: only the entries that use it ask for it, see need_workspace)
+    PB_REQUIRE(st->workspace != nullptr || st->workspace_bytes == 0, "workspace is null but workspace_bytes is not 0");
     PB_REQUIRE(st->lambda_l2 > 0.0, "lambda_l2 must be positive");
     PB_REQUIRE(st->count_bits >= 1 && st->count_bits <= 13 && st->lo_bits == 32 - 2 * st->count_bits &&
                    st->gq_bits >= st->lo_bits && st->gq_bits <= kGqBitsMax && st->gq_bits <= 63 - 3 * st->count_bits,
                "accumulator widths are not set: call pb_train_prepare first");
-    PB_REQUIRE(((uintptr_t)st->codes % 16 == 0) && ((uintptr_t)st->gq % 16 == 0) && ((uintptr_t)st->slot % 16 == 0) &&
-                   ((uintptr_t)st->leaf % 16 == 0),
-               "codes, gq, slot and leaf must be 16-byte aligned");
+    // (the lane histogram kernel reads a 32-byte sector of codes with one 256-bit load)
+    PB_REQUIRE((uintptr_t)st->codes % 32 == 0, "codes must be 32-byte aligned");
+    PB_REQUIRE(((uintptr_t)st->gq % 16 == 0) && ((uintptr_t)st->slot % 16 == 0) && ((uintptr_t)st->leaf % 16 == 0),
+               "gq, slot and leaf must be 16-byte aligned");
     return PB_OK;
 }
 
+
+// Entries that keep their tables in the caller's workspace.  A host that cannot allocate one
+// leaves it null and uses pb_depth_hist_score_static + pb_depth_select_cand instead.
+static int need_workspace(const pb_train_state* st, const char* who) {
+    PB_REQUIRE(st->workspace != nullptr, "%s needs pb_train_state.workspace (hosts without one: "
+               "pb_depth_hist_score_static and pb_depth_select_cand)", who);
+    return PB_OK;
+}
 
 // Carving of the scratch that one block of features needs between the histogram pass and the
 // scorer: gsum | cnt | gain-weight table | era-summed gradient sums | era-summed counts.
@@ -649,8 +660,9 @@ extern "C" int pb_train_prepare(pb_train_state* st, const int32_t* era_offsets_h
     st->gq_bits = (63 - 3 * cb < kGqBitsMax) ? (63 - 3 * cb) : kGqBitsMax;
     int rc = check_state(st);
     if (rc) return rc;
-    PB_REQUIRE(st->workspace_bytes >= pb_workspace_min_bytes(st), "workspace too small: %lld < %lld",
-               (long long)st->workspace_bytes, (long long)pb_workspace_min_bytes(st));
+    if (st->workspace != nullptr)
+        PB_REQUIRE(st->workspace_bytes >= pb_workspace_min_bytes(st), "workspace too small: %lld < %lld",
+                   (long long)st->workspace_bytes, (long long)pb_workspace_min_bytes(st));
     return PB_OK;
 }
 
@@ -677,6 +689,8 @@ extern "C" int pb_candidates_buffer(const pb_train_state* st, int64_t depth, int
                                     int64_t* bytes) {
     PB_REQUIRE(st && ptr && bytes, "null argument");
     PB_REQUIRE(depth >= 0 && depth < st->max_depth, "depth out of range");
+    int rc = need_workspace(st, "pb_candidates_buffer");
+    if (rc) return rc;
     *ptr = st->workspace;
     *bytes = (int64_t)sizeof(Cand) * n_sampled * node_stride_of(depth);
     return PB_OK;
@@ -694,6 +708,8 @@ extern "C" int pb_depth_clear_candidates(const pb_train_state* st, int64_t depth
 extern "C" int pb_depth_hist_score(const pb_train_state* st, int64_t depth, const int32_t* feat_rows,
                                    const int32_t* feat_pos, int64_t n_feat, int64_t n_sampled, void* stream_) {
     int rc = check_state(st);
+    if (rc) return rc;
+    rc = need_workspace(st, "pb_depth_hist_score");
     if (rc) return rc;
     PB_REQUIRE(depth >= 0 && depth < st->max_depth, "depth out of range");
     PB_REQUIRE(n_feat >= 0 && n_feat <= n_sampled && n_sampled <= st->n_features_total, "feature counts out of range");
@@ -715,13 +731,23 @@ extern "C" int pb_depth_select(const pb_train_state* st, int64_t depth, const in
                                int64_t n_sampled, void* stream_) {
     int rc = check_state(st);
     if (rc) return rc;
+    rc = need_workspace(st, "pb_depth_select");
+    if (rc) return rc;
+    return pb_depth_select_cand(st, depth, sampled_features, n_sampled, st->workspace, stream_);
+}
+
+extern "C" int pb_depth_select_cand(const pb_train_state* st, int64_t depth, const int32_t* sampled_features,
+                                    int64_t n_sampled, const void* cand, void* stream_) {
+    int rc = check_state(st);
+    if (rc) return rc;
     PB_REQUIRE(depth >= 0 && depth < st->max_depth, "depth out of range");
     PB_REQUIRE(sampled_features && n_sampled >= 1, "empty feature subset");
+    PB_REQUIRE(cand != nullptr && ((uintptr_t)cand % 8) == 0, "candidate table must be a non-null 8-byte aligned buffer");
     SelectArgs a;
     a.c = ctl_view(st->ctl);
     a.depth = (int)depth;
     a.max_depth = (int)st->max_depth;
-    a.cand = reinterpret_cast<const Cand*>(st->workspace);
+    a.cand = reinterpret_cast<const Cand*>(cand);
     a.node_stride = node_stride_of(depth);
     a.sampled = sampled_features;
     a.n_sampled = (int)n_sampled;

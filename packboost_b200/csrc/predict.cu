@@ -1,4 +1,9 @@
 // Tree routing: a row goes left when its code is <= the node's threshold.
+//
+// Every walk is bounded: it takes at most as many steps as its tree has nodes, a child index must
+// stay inside the tree and a feature index inside the row, and a tree that breaks one of these
+// rules contributes 0 for that row (the guards of packboost/backends/cuda/frontier_cuda.cu:214-231
+// and 953-966).  A malformed ensemble therefore cannot hang the device or read outside its buffers.
 
 #include "common.cuh"
 
@@ -24,6 +29,7 @@ struct PredictRowsArgs {
     const float* init;
     int rows_per_cta;
     int stage;  // 1: the CTA's rows are staged in shared memory
+    int n_codes;  // codes held by one row (pitch_row * 8 / code_bits): bound of a feature index
 };
 
 template <int BITS>
@@ -53,13 +59,17 @@ __global__ void __launch_bounds__(128) predict_rows_kernel(PredictRowsArgs a) {
         float acc = a.init ? a.init[row0 + lr] : 0.f;
         for (int t = 0; t < a.n_trees; ++t) {
             const int base = __ldg(a.tree_offsets + t);
-            int node = 0;
-            while (!__ldg(a.is_leaf + base + node)) {
+            const int n_t = __ldg(a.tree_offsets + t + 1) - base;  // nodes of this tree
+            int node = 0, steps = 0;
+            bool good = n_t > 0;
+            while (good && !__ldg(a.is_leaf + base + node)) {
                 const int f = __ldg(a.feature + base + node);
                 const int thr = __ldg(a.threshold + base + node);
+                if ((unsigned)f >= (unsigned)a.n_codes || ++steps > n_t) { good = false; break; }
                 node = (code_at<BITS>(row, f) <= thr) ? __ldg(a.left + base + node) : __ldg(a.right + base + node);
+                good = (unsigned)node < (unsigned)n_t;
             }
-            const float term = __fmul_rn(a.weight, __ldg(a.value + base + node));
+            const float term = good ? __fmul_rn(a.weight, __ldg(a.value + base + node)) : 0.f;
             const int rep = a.repeat ? __ldg(a.repeat + t) : 1;
             for (int k = 0; k < rep; ++k) acc = __fadd_rn(acc, term);
         }
@@ -87,6 +97,8 @@ struct PredictPackedArgs {
     int rows_per_cta;
     int stage;
     int trees_per_batch;
+    int n_codes;         // codes held by one row: bound of a feature index
+    int max_tree_nodes;  // node count of the largest tree: bound of a walk
 };
 
 // kTpr threads share a row (they sit in the same warp): thread q walks trees t0+q, t0+kTpr+q, ...
@@ -134,7 +146,8 @@ __global__ void __launch_bounds__(512) predict_rows_packed_kernel(PredictPackedA
         const int ta = b * TB, tb = min(a.n_trees, ta + TB);
         const int o0 = __ldg(a.tree_offsets + ta), o1 = __ldg(a.tree_offsets + tb);
         uint2* dst = s_nodes + (size_t)(b & 1) * kStageNodes;
-        for (int i = threadIdx.x; i < o1 - o0; i += blockDim.x) cp_async8(dst + i, a.nodes + o0 + i);
+        const int n_copy = min(o1 - o0, kStageNodes);
+        for (int i = threadIdx.x; i < n_copy; i += blockDim.x) cp_async8(dst + i, a.nodes + o0 + i);
         cp_async_commit();
     };
 
@@ -167,26 +180,37 @@ __global__ void __launch_bounds__(512) predict_rows_packed_kernel(PredictPackedA
             for (int t0 = ta; t0 < tb; t0 += kTpr * kWay) {
                 const uint2* base[kWay];
                 uint2 nd[kWay];
+                uint32_t lim[kWay];  // nodes of the tree
 #pragma unroll
                 for (int u = 0; u < kWay; ++u) {
                     const int t = min(t0 + u * kTpr + q, tb - 1);
-                    base[u] = node_base + (__ldg(a.tree_offsets + t) - off_shift);
-                    nd[u] = base[u][0];
+                    const int o = __ldg(a.tree_offsets + t);
+                    lim[u] = (uint32_t)max(__ldg(a.tree_offsets + t + 1) - o, 0);
+                    if (TB && ((unsigned)(o - off_shift) > (unsigned)kStageNodes ||
+                               lim[u] > (uint32_t)kStageNodes - (uint32_t)(o - off_shift)))
+                        lim[u] = 0u;  // not wholly inside the staged batch
+                    base[u] = node_base + (o - off_shift);
+                    nd[u] = lim[u] ? base[u][0] : make_uint2(0x80000000u, 0u);
                 }
                 bool any = true;
-                while (any) {
+                for (int steps = 0; any && steps <= a.max_tree_nodes; ++steps) {
                     any = false;
 #pragma unroll
                     for (int u = 0; u < kWay; ++u) {
                         if (!(nd[u].x >> 31)) {
                             const int f = nd[u].x & 0xFFFF;
                             const int thr = (nd[u].x >> 16) & 0xFF;
-                            const int child = (int)nd[u].y + ((code_at<BITS>(row, f) > thr) ? 1 : 0);
-                            nd[u] = base[u][child];
+                            const uint32_t child = nd[u].y + ((f < a.n_codes && code_at<BITS>(row, min(f, a.n_codes - 1)) > thr) ? 1u : 0u);
+                            // a child outside the tree or a feature outside the row ends the walk with 0
+                            const bool good = (child < lim[u]) & (f < a.n_codes);
+                            nd[u] = good ? base[u][child] : make_uint2(0x80000000u, 0u);
                             any = true;
                         }
                     }
                 }
+#pragma unroll
+                for (int u = 0; u < kWay; ++u)
+                    if (!(nd[u].x >> 31)) nd[u] = make_uint2(0x80000000u, 0u);  // step cap reached: 0
                 // ordered accumulation: tree t0 + u*kTpr + qq for u, then qq, ascending
 #pragma unroll
                 for (int u = 0; u < kWay; ++u) {
@@ -243,6 +267,8 @@ __global__ void __launch_bounds__(512) predict_rows_packed_smem_kernel(PredictPa
     if (nr <= 0) return;
     uint2* s_nodes = reinterpret_cast<uint2*>(s_rows + (size_t)a.rows_per_cta * a.pitch_row);
     int32_t* s_offs = reinterpret_cast<int32_t*>(s_nodes + 2 * kStageNodes);
+    uint2* s_zero = reinterpret_cast<uint2*>(s_offs + 2 * (kStageTrees + 1));  // a leaf of value 0
+    if (threadIdx.x == 0) *s_zero = make_uint2(0x80000000u, 0u);
     {
         const int64_t n16 = (int64_t)nr * a.pitch_row / 16;
         const uint4* src = reinterpret_cast<const uint4*>(a.codes + row0 * a.pitch_row);
@@ -252,6 +278,8 @@ __global__ void __launch_bounds__(512) predict_rows_packed_smem_kernel(PredictPa
     const uint32_t rows_addr = (uint32_t)__cvta_generic_to_shared(s_rows);
     const uint32_t nodes_addr = (uint32_t)__cvta_generic_to_shared(s_nodes);
     const uint32_t offs_addr = (uint32_t)__cvta_generic_to_shared(s_offs);
+    const uint32_t zero_leaf = (uint32_t)__cvta_generic_to_shared(s_zero);
+    const uint32_t fmax = (uint32_t)a.n_codes - 1u;
     const int TB = a.trees_per_batch;
     const int q = threadIdx.x % kTpr;
     const int lane = threadIdx.x & 31;
@@ -263,7 +291,8 @@ __global__ void __launch_bounds__(512) predict_rows_packed_smem_kernel(PredictPa
         const int ta = b * TB, tb = min(a.n_trees, ta + TB);
         const int o0 = __ldg(a.tree_offsets + ta), o1 = __ldg(a.tree_offsets + tb);
         uint2* dst = s_nodes + (size_t)(b & 1) * kStageNodes;
-        for (int i = threadIdx.x; i < o1 - o0; i += blockDim.x) cp_async8(dst + i, a.nodes + o0 + i);
+        const int n_copy = min(o1 - o0, kStageNodes);  // (a batch larger than the buffer: its tail trees yield 0)
+        for (int i = threadIdx.x; i < n_copy; i += blockDim.x) cp_async8(dst + i, a.nodes + o0 + i);
         int32_t* od = s_offs + (size_t)(b & 1) * (kStageTrees + 1);
         for (int i = threadIdx.x; i <= tb - ta; i += blockDim.x) cp_async4(od + i, a.tree_offsets + ta + i);
         cp_async_commit();
@@ -291,29 +320,41 @@ __global__ void __launch_bounds__(512) predict_rows_packed_smem_kernel(PredictPa
             for (int t0 = ta; t0 < tb; t0 += kTpr * kWay) {
                 uint32_t base[kWay];
                 uint2 nd[kWay];
+                uint32_t lim[kWay];  // nodes of the tree
 #pragma unroll
                 for (int u = 0; u < kWay; ++u) {
                     const int t = min(t0 + u * kTpr + q, tb - 1);
-                    base[u] = nbase + (lds_u32(obase + (uint32_t)(t - ta) * 4u) - off_shift) * 8u;
-                    nd[u] = lds_v2(base[u]);
+                    const uint32_t o = lds_u32(obase + (uint32_t)(t - ta) * 4u);
+                    const uint32_t rel = o - off_shift;
+                    lim[u] = lds_u32(obase + (uint32_t)(t - ta) * 4u + 4u) - o;
+                    // a tree that is empty or not wholly inside the staged batch yields 0
+                    if (rel > (uint32_t)kStageNodes || lim[u] > (uint32_t)kStageNodes - rel) lim[u] = 0u;
+                    base[u] = nbase + rel * 8u;
+                    nd[u] = lds_v2(lim[u] ? base[u] : zero_leaf);
                 }
                 bool any = true;
-                while (any) {
+                for (int steps = 0; any && steps <= a.max_tree_nodes; ++steps) {
                     any = false;
 #pragma unroll
                     for (int u = 0; u < kWay; ++u) {
                         if (!(nd[u].x >> 31)) {
-                            const uint32_t f = nd[u].x & 0xFFFFu;
+                            // a feature index past the row reads the row's last code and ends the walk
+                            const uint32_t f = min(nd[u].x & 0xFFFFu, fmax);
                             const uint32_t thr = (nd[u].x >> 16) & 0xFFu;
                             uint32_t code;
                             if (BITS == 4) code = (lds_u8(row + (f >> 1)) >> ((f & 1u) * 4u)) & 0xFu;
                             else code = lds_u8(row + f);
                             const uint32_t child = nd[u].y + ((code > thr) ? 1u : 0u);
-                            nd[u] = lds_v2(base[u] + child * 8u);
+                            // a child outside the tree (or a bad feature) ends the walk at the zero leaf
+                            const bool good = (child < lim[u]) & ((nd[u].x & 0xFFFFu) <= fmax);
+                            nd[u] = lds_v2(good ? base[u] + child * 8u : zero_leaf);
                             any = true;
                         }
                     }
                 }
+#pragma unroll
+                for (int u = 0; u < kWay; ++u)
+                    if (!(nd[u].x >> 31)) nd[u] = make_uint2(0x80000000u, 0u);  // step cap reached: 0
 #pragma unroll
                 for (int u = 0; u < kWay; ++u) {
                     const float mine = __fmul_rn(a.weight, __uint_as_float(nd[u].y));
@@ -340,21 +381,24 @@ __global__ void __launch_bounds__(512) predict_rows_packed_smem_kernel(PredictPa
 
 
 __global__ void __launch_bounds__(256) predict_bins_fm_kernel(
-    const uint8_t* __restrict__ bins, int64_t n_rows, const int32_t* __restrict__ feature,
+    const uint8_t* __restrict__ bins, int n_features, int64_t n_rows, const int32_t* __restrict__ feature,
     const int32_t* __restrict__ threshold, const int32_t* __restrict__ left, const int32_t* __restrict__ right,
-    const float* __restrict__ value, const uint8_t* __restrict__ is_leaf, float* __restrict__ out) {
+    const float* __restrict__ value, const uint8_t* __restrict__ is_leaf, int n_nodes, float* __restrict__ out) {
     for (int64_t r = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; r < n_rows; r += (int64_t)gridDim.x * blockDim.x) {
-        int node = 0;
+        int node = 0, steps = 0;
+        bool good = true;
         while (!__ldg(is_leaf + node)) {
             const int f = __ldg(feature + node);
+            if ((unsigned)f >= (unsigned)n_features || ++steps > n_nodes) { good = false; break; }
             node = ((int)bins[(int64_t)f * n_rows + r] <= __ldg(threshold + node)) ? __ldg(left + node) : __ldg(right + node);
+            if ((unsigned)node >= (unsigned)n_nodes) { good = false; break; }
         }
-        out[r] = __ldg(value + node);
+        out[r] = good ? __ldg(value + node) : 0.f;
     }
 }
 
 __global__ void __launch_bounds__(256) predict_pack_fm_kernel(
-    const uint8_t* __restrict__ bins, int64_t n_rows, const int32_t* __restrict__ feature,
+    const uint8_t* __restrict__ bins, int n_features, int64_t n_rows, const int32_t* __restrict__ feature,
     const int32_t* __restrict__ threshold, const int32_t* __restrict__ left_abs, const int32_t* __restrict__ right_abs,
     const float* __restrict__ value, const uint8_t* __restrict__ is_leaf, const int32_t* __restrict__ offsets,
     int n_trees, float tree_weight, float* __restrict__ out) {
@@ -364,12 +408,17 @@ __global__ void __launch_bounds__(256) predict_pack_fm_kernel(
             int node = __ldg(offsets + t);
             const int end = __ldg(offsets + t + 1);
             if (node >= end) continue;
+            const int begin = node;
+            int steps = 0;
+            bool good = true;
             while (!__ldg(is_leaf + node)) {
                 const int f = __ldg(feature + node);
+                if ((unsigned)f >= (unsigned)n_features || ++steps > end - begin) { good = false; break; }
                 node = ((int)bins[(int64_t)f * n_rows + r] <= __ldg(threshold + node)) ? __ldg(left_abs + node)
                                                                                        : __ldg(right_abs + node);
+                if (node < begin || node >= end) { good = false; break; }
             }
-            sum = __fadd_rn(sum, __ldg(value + node));
+            if (good) sum = __fadd_rn(sum, __ldg(value + node));
         }
         out[r] = __fmul_rn(tree_weight, sum);
     }
@@ -394,7 +443,8 @@ extern "C" int pb_predict_rows(const uint8_t* codes, int64_t n_rows, int64_t pit
     if (n_rows <= 0) return PB_OK;
     cudaStream_t stream = (cudaStream_t)stream_;
     PredictRowsArgs a{codes, n_rows, pitch_row, feature, threshold, left, right, value, is_leaf,
-                      tree_offsets, repeat, (int)n_trees, weight, out, init, 128, 1};
+                      tree_offsets, repeat, (int)n_trees, weight, out, init, 128, 1,
+                      (int)((pitch_row < (1 << 27) ? pitch_row : (1 << 27)) * (code_bits == 4 ? 2 : 1))};
     const int64_t budget = 160 * 1024;
     int rows = (int)(budget / pitch_row);
     if (rows >= 128) rows = 128;
@@ -435,8 +485,9 @@ extern "C" int pb_predict_bins_fm(const uint8_t* bins, int64_t n_features, int64
     PB_REQUIRE(bins && feature && threshold && left && right && value && is_leaf && out, "null buffer");
     PB_REQUIRE(n_features >= 1 && n_nodes >= 1, "bad shape");
     if (n_rows <= 0) return PB_OK;
-    predict_bins_fm_kernel<<<row_blocks(n_rows), 256, 0, (cudaStream_t)stream>>>(bins, n_rows, feature, threshold, left,
-                                                                                right, value, is_leaf, out);
+    PB_REQUIRE(n_features < (1ll << 31) && n_nodes < (1ll << 31), "bad shape");
+    predict_bins_fm_kernel<<<row_blocks(n_rows), 256, 0, (cudaStream_t)stream>>>(
+        bins, (int)n_features, n_rows, feature, threshold, left, right, value, is_leaf, (int)n_nodes, out);
     count_launch(1);
     PB_LAUNCH_CHECK("predict_bins_fm_kernel");
     return PB_OK;
@@ -450,8 +501,9 @@ extern "C" int pb_predict_pack_fm(const uint8_t* bins, int64_t n_features, int64
                "null buffer");
     PB_REQUIRE(n_features >= 1 && n_trees >= 0, "bad shape");
     if (n_rows <= 0) return PB_OK;
+    PB_REQUIRE(n_features < (1ll << 31) && n_trees < (1ll << 31), "bad shape");
     predict_pack_fm_kernel<<<row_blocks(n_rows), 256, 0, (cudaStream_t)stream>>>(
-        bins, n_rows, feature, threshold, left_abs, right_abs, value, is_leaf, offsets, (int)n_trees, tree_weight, out);
+        bins, (int)n_features, n_rows, feature, threshold, left_abs, right_abs, value, is_leaf, offsets, (int)n_trees, tree_weight, out);
     count_launch(1);
     PB_LAUNCH_CHECK("predict_pack_fm_kernel");
     return PB_OK;
@@ -475,13 +527,15 @@ extern "C" int pb_predict_rows_packed(const uint8_t* codes, int64_t n_rows, int6
     }
     cudaStream_t stream = (cudaStream_t)stream_;
     PredictPackedArgs a{codes, n_rows, pitch_row, static_cast<const uint2*>(nodes), tree_offsets, repeat,
-                        (int)n_trees, weight, out, init, 128, 1, 0};
+                        (int)n_trees, weight, out, init, 128, 1, 0,
+                        (int)((pitch_row < (1 << 27) ? pitch_row : (1 << 27)) * (code_bits == 4 ? 2 : 1)),
+                        (int)(max_tree_nodes < (1 << 30) ? max_tree_nodes : (1 << 30))};
     // trees per staged batch: a multiple of the group walked at once, as many as the buffer holds
     const int group = kTpr * kWay;
     int tb = (int)(kStageNodes / max_tree_nodes) / group * group;
     if (tb > kStageTrees) tb = kStageTrees / group * group;
     a.trees_per_batch = tb;  // 0: no staging
-    const size_t stage_bytes = tb ? (size_t)2 * kStageNodes * sizeof(uint2) + (size_t)2 * (kStageTrees + 1) * 4 : 0;
+    const size_t stage_bytes = tb ? (size_t)2 * kStageNodes * sizeof(uint2) + (size_t)2 * (kStageTrees + 1) * 4 + 8 : 0;
     const int64_t budget = 224 * 1024 - (int64_t)stage_bytes;
     int rows = (int)(budget / pitch_row);
     if (rows > 128) rows = 128;

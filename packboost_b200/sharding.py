@@ -37,3 +37,30 @@ def dealt_part(subset: np.ndarray, rank: int, world: int) -> tuple[np.ndarray, n
     subset = np.asarray(subset)
     pos = np.arange(rank, subset.shape[0], max(world, 1), dtype=np.int32)
     return subset[pos].astype(np.int32), pos
+
+
+def agree_all(flag: bool, device=None) -> bool:
+    """True only when ``flag`` is true on every rank of the default process group (a MIN
+    all-reduce).  Decisions that change the sequence of collectives a rank issues — such as the
+    choice between the replicated and the memory-sharded layout of the packed matrix, which
+    depends on the free memory of each rank's own GPU — must be taken this way: ranks that chose
+    differently would wait for each other's collectives forever."""
+    import torch
+    import torch.distributed as dist
+    if not (dist.is_available() and dist.is_initialized()) or dist.get_world_size() == 1:
+        return bool(flag)
+    if device is None:
+        device = torch.device("cuda", torch.cuda.current_device()) if dist.get_backend() == "nccl" else "cpu"
+    t = torch.tensor([1 if flag else 0], dtype=torch.int32, device=device)
+    dist.all_reduce(t, op=dist.ReduceOp.MIN)
+    return bool(int(t.item()))
+
+
+def choose_replicated(packed_bytes: int, free_bytes: int, world: int, force_sharded: bool, device=None) -> bool:
+    """Layout of the packed matrix on ``world`` GPUs: replicated on every rank when it takes less
+    than a quarter of the free memory of EVERY rank's GPU (and sharding is not forced), else
+    feature-sharded.  Collective: every rank must call it, and every rank gets the same answer."""
+    if world <= 1:
+        return False
+    local = (not force_sharded) and packed_bytes < 0.25 * free_bytes
+    return agree_all(local, device)

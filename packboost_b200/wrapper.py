@@ -16,6 +16,7 @@ from typing import Any, Iterable, Sequence
 import numpy as np
 
 from .config import PackBoostConfig
+from .forest import validate_forest
 
 _CONFIG_FIELDS = [f.name for f in dataclasses.fields(PackBoostConfig)]
 
@@ -92,7 +93,12 @@ class PackBoostPredictor:
     def __init__(self, trees: Sequence[dict[str, np.ndarray]], repeats: Sequence[int], tree_weight: float,
                  bin_edges: np.ndarray | None, max_bins: int, pack_size: int) -> None:
         self.trees = [{k: np.asarray(v) for k, v in t.items()} for t in trees]
+        for t in self.trees:  # a malformed file is refused here, on the host
+            validate_forest(t["feature"], t["threshold"], t["left"], t["right"], t["is_leaf"],
+                            [0, t["feature"].shape[0]])
         self.repeats = [int(r) for r in repeats]
+        if len(self.repeats) != len(self.trees) or any(r < 0 for r in self.repeats):
+            raise ValueError("repeats must hold one non-negative count per tree")
         self.tree_weight = float(tree_weight)
         self.bin_edges = None if bin_edges is None else np.asarray(bin_edges, dtype=np.float32)
         self.max_bins = int(max_bins)

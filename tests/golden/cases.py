@@ -112,6 +112,34 @@ def case_ragged_eras():
     return X, y, eras, cfg, 4, Xh
 
 
+def case_config3_wide():
+    """The era-heavy five-level table at its full width (2 376 features, 10 % sampled per depth =
+    238 features = eight 32-feature blocks, pack of 32) with a tenth of the rows and eras."""
+    w = workloads.config3(seed=3, n_rows=270_000, n_features=2376, n_eras=57, num_rounds=2)
+    rng = np.random.default_rng(1003)
+    Xh = rng.integers(0, 5, size=(256, 2376), dtype=np.uint8)
+    return w.X, w.y, w.era, dict(w.config), 2, Xh
+
+
+def case_config2_full():
+    """The mixed-column configuration at full size (500 000 x 256, 128 bins, 100 eras, pack of 16)."""
+    w = workloads.config2()
+    rng = np.random.default_rng(1004)
+    Xh = w.X[rng.choice(w.X.shape[0], size=512, replace=False)] + 0.0
+    return w.X, w.y, w.era, dict(w.config), 2, Xh
+
+
+def case_config4_deep():
+    """Deep frontier at the real width: 500 features, depth 10 (up to 512 live nodes), 128 bins;
+    rows and eras cut so that the CPU path finishes in minutes."""
+    w = workloads.config4(seed=11, n_rows=100_000, n_features=500, n_eras=10, num_rounds=2, max_bins=128)
+    cfg = dict(w.config)
+    cfg.update(pack_size=8, learning_rate=0.05)
+    rng = np.random.default_rng(1005)
+    Xh = rng.standard_normal((256, 500)).astype(np.float32)
+    return w.X, w.y, w.era, cfg, 2, Xh
+
+
 CASES = {
     "config1": case_config1,
     "interleaved": case_interleaved,
@@ -121,6 +149,15 @@ CASES = {
     "fallthrough": case_fallthrough,
     "era_none": case_era_none,
     "ragged_eras": case_ragged_eras,
+}
+
+
+# Cases at the widths of the benchmark configurations.  The reference needs minutes for them, so
+# only the CUDA path is compared with their fixtures (and the oracle with the first one).
+WIDE_CASES = {
+    "config3_wide": case_config3_wide,
+    "config2_full": case_config2_full,
+    "config4_deep": case_config4_deep,
 }
 
 

@@ -2,8 +2,9 @@
 
 Usage (in a container that has the reference checked out):
 
-    python tests/golden/make_golden.py /path/to/reference
+    python tests/golden/make_golden.py /path/to/reference [case ...]
 
+Without case names every fixture is rewritten (the wide cases take several minutes each).
 The reference is imported read-only (no bytecode is written), driven through
 its public API with ``device="cpu"`` and with its optional native backend
 absent, so the torch frontier is the code that runs.  Outputs are the small
@@ -44,7 +45,27 @@ def _flatten_trees(trees):
     )
 
 
-def main(ref_root: str) -> None:
+def _record_splits(booster, log):
+    """Wrap the booster's frontier call so that the decisions it returns for the first tree of the
+    pack are appended to ``log`` as (call index, tree node, feature, threshold, score, left count,
+    right count).  The wrapped method runs unchanged; nothing else of the reference is touched."""
+    inner = booster._find_best_splits_batched
+    calls = [0]
+
+    def spy(nodes, grad, hess, bins, feature_subset):
+        decisions, stats = inner(nodes, grad, hess, bins, feature_subset)
+        for node, dec in zip(nodes, decisions):
+            if node.tree_id != 0 or dec is None:
+                continue
+            log.append((calls[0], node.node_id, dec.feature, dec.threshold, float(dec.score),
+                        int(dec.left_count), int(dec.right_count)))
+        calls[0] += 1
+        return decisions, stats
+
+    booster._find_best_splits_batched = spy
+
+
+def main(ref_root: str, only: list[str] | None = None) -> None:
     sys.path.insert(0, ref_root)
     os.environ["PACKBOOST_DISABLE_NATIVE_CPU"] = "1"
     import torch
@@ -55,11 +76,26 @@ def main(ref_root: str) -> None:
     sys.path.insert(0, HERE)
     import cases
 
-    for name, make in cases.CASES.items():
+    all_cases = dict(cases.CASES)
+    all_cases.update(cases.WIDE_CASES)
+    for name, make in all_cases.items():
+        if only and name not in only:
+            continue
         X, y, era, cfg, rounds, Xh = make()
         booster = PackBoost(PackBoostConfig(device="cpu", **cfg))
+        splits: list[tuple] = []
+        _record_splits(booster, splits)
         booster.fit(X, y, era, num_rounds=rounds)
         out = _flatten_trees(booster.trees)
+        # every split of the first tree of each pack, in the order the frontier produced them
+        sp = np.asarray(splits, dtype=np.float64).reshape(-1, 7)
+        out["split_call"] = sp[:, 0].astype(np.int32)
+        out["split_node"] = sp[:, 1].astype(np.int32)
+        out["split_feature"] = sp[:, 2].astype(np.int32)
+        out["split_threshold"] = sp[:, 3].astype(np.int32)
+        out["split_score"] = sp[:, 4].astype(np.float32)
+        out["split_left_count"] = sp[:, 5].astype(np.int64)
+        out["split_right_count"] = sp[:, 6].astype(np.int64)
         out["pred_train_head"] = booster.predict(X[:2048])
         out["pred_holdout"] = booster.predict(Xh)
         out["tree_weight"] = np.float64(booster._tree_weight)
@@ -72,6 +108,8 @@ def main(ref_root: str) -> None:
         np.savez_compressed(os.path.join(HERE, f"{name}.npz"), **out)
         print(name, "trees", len(booster.trees), "nodes", out["feature"].shape[0])
 
+    if only:
+        return
     # frontier known answer: hand-built node of the reference's DES test
     grad, hess, codes, era_rows, cfg = cases.des_known_answer_inputs()
     res = {}
@@ -104,6 +142,6 @@ def main(ref_root: str) -> None:
 
 
 if __name__ == "__main__":
-    if len(sys.argv) != 2:
-        sys.exit("usage: python tests/golden/make_golden.py /path/to/reference")
-    main(sys.argv[1])
+    if len(sys.argv) < 2:
+        sys.exit("usage: python tests/golden/make_golden.py /path/to/reference [case ...]")
+    main(sys.argv[1], sys.argv[2:] or None)

@@ -49,6 +49,8 @@ def assert_values_close(got, want, is_leaf, scale=None):
     finite = np.isfinite(want) & (np.abs(want) < 1e30)
     s = np.abs(want[finite]).max() if scale is None and finite.any() else (scale or 1.0)
     np.testing.assert_allclose(got[finite], want[finite], rtol=1e-5, atol=1e-5 * s)
+    # how many values needed the absolute term (reported by the caller where it matters)
+    return int((np.abs(got[finite] - want[finite]) > 1e-5 * np.abs(want[finite])).sum())
 
 
 def leaf_index(tree, codes):

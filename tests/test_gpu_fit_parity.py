@@ -271,3 +271,66 @@ def test_predict_generic_node_arrays_when_children_are_not_adjacent():
     want = po.predict_codes([arr] * 3, codes.astype(np.int8), 0.3)
     np.testing.assert_array_equal(b.predict(codes).view(np.int32), want.view(np.int32))
     assert "packed" not in b._forest_cache
+
+
+def _check_scores(got, want, label):
+    """DES scores within 1e-5 relative.  A score is mean - lambda * std of per-era gains, so it can
+    cancel to far below the gains it is made of; such scores are held to 1e-5 of the largest score
+    of the fit instead, and their number is reported."""
+    got = np.asarray(got, np.float64)
+    want = np.asarray(want, np.float64)
+    finite = np.isfinite(want)
+    np.testing.assert_array_equal(np.isfinite(got), finite)
+    np.testing.assert_array_equal(got[~finite], want[~finite])          # -inf fall-through splits
+    g, w = got[finite], want[finite]
+    scale = np.abs(w).max() if w.size else 1.0
+    rel_ok = np.abs(g - w) <= 1e-5 * np.abs(w)
+    print(f"{label}: {w.size} scores, {int((~rel_ok).sum())} outside 1e-5 relative "
+          f"(max abs diff there {np.abs(g - w)[~rel_ok].max() if (~rel_ok).any() else 0:.3g}, score scale {scale:.3g})")
+    np.testing.assert_allclose(g, w, rtol=1e-5, atol=1e-5 * scale)
+    return int((~rel_ok).sum()), int(w.size)
+
+
+@pytest.mark.parametrize("name", list(cases.CASES))
+def test_split_scores_match_reference(name):
+    """Every split the reference's frontier returned (first tree of each pack): same node,
+    feature, threshold and child counts, DES score within 1e-5."""
+    X, y, era, cfg, rounds, Xh = cases.CASES[name]()
+    gold = np.load(os.path.join(GOLD, f"{name}.npz"))
+    rec = _fit_gpu(X, y, era, cfg, rounds).split_records()
+    for k in ("node", "feature", "threshold", "left_count", "right_count"):
+        np.testing.assert_array_equal(rec[k], gold[f"split_{k}"], err_msg=k)
+    _check_scores(rec["score"], gold["split_score"], name)
+
+
+@pytest.mark.parametrize("name", list(cases.WIDE_CASES))
+def test_wide_cases_match_reference(name):
+    """The benchmark configurations at their real widths (238 sampled features = eight feature
+    blocks; 500 000 x 256 at 128 bins; 500 features at depth 10) against fixtures written by the
+    unmodified reference: split structure exact, scores, leaf values and predictions within 1e-5."""
+    X, y, era, cfg, rounds, Xh = cases.WIDE_CASES[name]()
+    gold = np.load(os.path.join(GOLD, f"{name}.npz"))
+    booster = _fit_gpu(X, y, era, cfg, rounds)
+    rec = booster.split_records()
+    for k in ("node", "feature", "threshold", "left_count", "right_count"):
+        np.testing.assert_array_equal(rec[k], gold[f"split_{k}"], err_msg=k)
+    _check_scores(rec["score"], gold["split_score"], name)
+    off, cols = flatten_trees(booster.trees)
+    np.testing.assert_array_equal(off, gold["tree_offsets"])
+    for k in ("feature", "threshold", "left", "right", "is_leaf"):
+        np.testing.assert_array_equal(cols[k], gold[k], err_msg=k)
+    gcols = {k: gold[k] for k in cols}
+    codes_train, edges = po.preprocess(X, po.OracleParams(**cfg))
+    # (the trees of a pack are identical: the populated-leaf mask of the first one serves all)
+    B = cfg["pack_size"]
+    first = np.arange(0, len(off) - 1, B)
+    populated = np.zeros(cols["feature"].shape[0], dtype=bool)
+    for t in first:
+        sl = slice(off[t], off[t + 1])
+        m = populated_leaves(np.array([0, off[t + 1] - off[t]]), {k: v[sl] for k, v in gcols.items()}, codes_train)
+        for j in range(B):
+            populated[off[t + j]: off[t + j + 1]] = m
+    n_abs = assert_values_close(cols["value"], gold["value"], gold["is_leaf"] & populated)
+    scale = np.abs(gold["pred_train_head"]).max() + 1e-12
+    np.testing.assert_allclose(booster.predict(X[:2048]), gold["pred_train_head"], rtol=1e-5, atol=1e-5 * scale)
+    np.testing.assert_allclose(booster.train_predictions()[:2048], gold["pred_train_head"], rtol=1e-5, atol=1e-5 * scale)

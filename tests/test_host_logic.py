@@ -174,6 +174,30 @@ def test_two_rank_exchange_merges_disjoint_tables_and_bitmasks():
     assert [out[r] for r in range(world)] == [1, 1]
 
 
+def _layout_worker(rank, world, port, out):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    packed = 3 << 30
+    # rank 1's GPU is nearly full: alone it would shard, rank 0 alone would replicate
+    free = (100 << 30) if rank == 0 else (4 << 30)
+    mixed = sharding.choose_replicated(packed, free, world, False, device="cpu")
+    roomy = sharding.choose_replicated(packed, 100 << 30, world, False, device="cpu")
+    forced = sharding.choose_replicated(packed, 100 << 30, world, rank == 1, device="cpu")
+    out[rank] = (mixed, roomy, forced)
+    dist.destroy_process_group()
+
+
+def test_ranks_with_different_free_memory_agree_on_one_layout():
+    """The replicated / sharded choice is collective: one rank short of memory (or one rank with
+    the sharding override set) moves every rank to the sharded layout."""
+    world = 2
+    out = mp.get_context("spawn").Manager().dict()
+    mp.spawn(_layout_worker, args=(world, _free_port(), out), nprocs=world, join=True)
+    assert out[0] == out[1] == (False, True, False)
+    assert sharding.choose_replicated(1, 1 << 40, 1, False) is False   # one GPU: nothing to replicate
+
+
 # ---- the round loop of the booster against a scripted device ----------------------------------
 
 class _ScriptedTrainer:

@@ -6,7 +6,9 @@ cannot supply the workspace that pb_depth_hist_score needs.  The static variant 
 histogram scratch in a fixed 64 MiB array inside the library.  This test drives it through the C
 ABI and requires byte-identical candidate tables to the workspace-based entry point, on two
 consecutive calls with different feature subsets (the second call sees the first call's
-leftovers in the shared array), and checks that an oversized shape is refused.
+leftovers in the shared array), checks that an oversized shape is refused, and grows three levels
+of a tree on a training state that has no workspace at all (static histogram + score, winner
+selection from the caller's candidate buffer, partition) against the workspace-based phases.
 """
 
 import ctypes as C
@@ -84,3 +86,53 @@ def test_static_scratch_variant_refuses_oversized_shapes():
     with pytest.raises(ValueError, match="static scratch too small"):
         B.check(lib.pb_depth_hist_score_static(C.byref(st), 11, rows.data_ptr(), rows.data_ptr(), 1, 1,
                                                out.data_ptr(), torch.cuda.current_stream().cuda_stream))
+
+
+def test_three_levels_without_any_workspace_match_the_workspace_phases():
+    """A host with no workspace: `workspace` NULL, `workspace_bytes` 0.  pb_train_prepare accepts
+    the state, pb_depth_hist_score_static writes the candidates to a caller buffer,
+    pb_depth_select_cand reads them from there, and pb_depth_partition never needed a workspace.
+    Winners, the row -> node map and the leaf ids must equal those of the workspace-based phases,
+    also after an earlier, larger call left other contents in the shared array."""
+    from packboost_b200 import backends as B
+    ref = _trainer()
+    alt = _trainer()
+    lib = ref.lib
+    stream = torch.cuda.current_stream().cuda_stream
+    bare = B.TrainState.from_buffer_copy(alt.st)
+    bare.workspace = None
+    bare.workspace_bytes = 0
+    eo = alt.era_offsets.cpu().numpy().astype(np.int32)
+    B.check(lib.pb_train_prepare(C.byref(bare), eo.ctypes.data))
+    with pytest.raises(ValueError, match="needs pb_train_state.workspace"):
+        B.check(lib.pb_depth_hist_score(C.byref(bare), 0, 0, 0, 0, 1, stream))
+
+    rng = np.random.default_rng(9)
+    # an earlier, larger call fills the shared array with something else
+    B.check(lib.pb_round_begin(C.byref(bare), 0, stream))
+    big = torch.arange(80, dtype=torch.int32, device="cuda")
+    scratch_out = torch.zeros(24 * 80 * 8, dtype=torch.uint8, device="cuda")
+    B.check(lib.pb_depth_hist_score_static(C.byref(bare), 0, big.data_ptr(), big.data_ptr(), 80, 80,
+                                           scratch_out.data_ptr(), stream))
+
+    B.check(lib.pb_round_begin(C.byref(ref.st), 0, stream))
+    B.check(lib.pb_round_begin(C.byref(bare), 0, stream))
+    for depth in range(3):
+        k = 40
+        subset = rng.permutation(80)[:k].astype(np.int32)
+        feats = torch.from_numpy(subset).cuda()
+        pos = torch.arange(k, dtype=torch.int32, device="cuda")
+        B.check(lib.pb_depth_hist_score(C.byref(ref.st), depth, feats.data_ptr(), pos.data_ptr(), k, k, stream))
+        B.check(lib.pb_depth_select(C.byref(ref.st), depth, feats.data_ptr(), k, stream))
+        B.check(lib.pb_depth_partition(C.byref(ref.st), depth, stream))
+        cand = torch.zeros(24 * k * (1 << depth), dtype=torch.uint8, device="cuda")
+        B.check(lib.pb_depth_hist_score_static(C.byref(bare), depth, feats.data_ptr(), pos.data_ptr(), k, k,
+                                               cand.data_ptr(), stream))
+        B.check(lib.pb_depth_select_cand(C.byref(bare), depth, feats.data_ptr(), k, cand.data_ptr(), stream))
+        B.check(lib.pb_depth_partition(C.byref(bare), depth, stream))
+    torch.cuda.synchronize()
+    assert torch.equal(ref.log_dev, alt.log_dev)
+    assert torch.equal(ref.slot, alt.slot) and torch.equal(ref.leaf, alt.leaf)
+    head = ref.log_dev.cpu().numpy()[:88].view(np.uint8)
+    n_ctx = np.frombuffer(head.tobytes(), dtype=np.int32, offset=24, count=4)
+    assert n_ctx[2] >= 2, "the case must reach a frontier of several nodes"
