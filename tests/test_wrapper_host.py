@@ -21,10 +21,14 @@ def test_regressor_params_roundtrip():
 def test_predictor_npz_roundtrip(tmp_path):
     rng = np.random.default_rng(0)
     trees = []
-    for n in (1, 3, 7):
-        trees.append({"feature": rng.integers(-1, 5, n).astype(np.int32), "threshold": rng.integers(0, 4, n).astype(np.int32),
-                      "left": rng.integers(-1, n, n).astype(np.int32), "right": rng.integers(-1, n, n).astype(np.int32),
-                      "value": rng.normal(size=n).astype(np.float32), "is_leaf": rng.integers(0, 2, n).astype(np.uint8)})
+    for n in (1, 3, 7):  # complete trees in heap order: node i has children 2i+1 and 2i+2
+        inner = np.arange(n) < n // 2
+        idx = np.arange(n)
+        trees.append({"feature": np.where(inner, rng.integers(0, 5, n), -1).astype(np.int32),
+                      "threshold": np.where(inner, rng.integers(0, 4, n), 0).astype(np.int32),
+                      "left": np.where(inner, 2 * idx + 1, -1).astype(np.int32),
+                      "right": np.where(inner, 2 * idx + 2, -1).astype(np.int32),
+                      "value": rng.normal(size=n).astype(np.float32), "is_leaf": (~inner).astype(np.uint8)})
     edges = rng.normal(size=(4, 6)).astype(np.float32)
     p = PackBoostPredictor(trees, [2, 1, 5], 0.05, edges, 5, 8)
     path = str(tmp_path / "model.npz")
