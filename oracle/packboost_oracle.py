@@ -57,6 +57,12 @@ class OracleParams:
     feature_block_size: int = 32
     random_state: int | None = None
     prebinned: bool = False
+    # Test-only variant of the arithmetic, not a reference behaviour: gradient sums are taken
+    # exactly (fixed point, ``gq = rint(g * 2^s)`` with the per-round power-of-two scale the CUDA
+    # path uses) and rounded to float32 once, instead of float32 sums in row order.  Everything
+    # after the sums is unchanged, so the CUDA path must reproduce this variant bit for bit; the
+    # difference between the two variants is the reference's own summation noise.
+    exact_sums: bool = False
     # ``max_bins`` above 128 is refused by the reference (int8 storage,
     # ``packboost/booster.py:394-395``, ``packboost/data.py:47-48``).  The
     # widened oracle stores codes as int16 instead and is otherwise identical.
@@ -338,13 +344,17 @@ def find_splits(
     n_eras: int,
     p: OracleParams,
     trace: dict | None = None,
+    fx: tuple[torch.Tensor, float] | None = None,
 ) -> list[NodeSplit | None]:
     """Best split of every frontier node (``booster.py:1598-2133``).
 
     ``node_rows[i]`` holds the node's row ids ordered by (era, row);
     ``node_eras[i]`` the matching era codes.  Nodes below ``2*min_samples_leaf``
     rows get ``None`` (``booster.py:1666-1668``).  ``trace`` (optional dict)
-    receives intermediate tensors for kernel-level parity tests.
+    receives intermediate tensors for kernel-level parity tests.  ``fx`` (the
+    ``exact_sums`` variant, see ``OracleParams``) is ``(gq, inv_scale)``: the fixed-point
+    gradients of all rows as a float64 tensor of integers and the float32 factor that turns a
+    sum of them back into a gradient sum.
     """
     M = len(node_rows)
     out: list[NodeSplit | None] = [None] * M
@@ -374,7 +384,11 @@ def find_splits(
             continue
         g_r = grad.index_select(0, rows)
         h_r = hess.index_select(0, rows)
-        g_t = float(g_r.sum().item())
+        if fx is not None:
+            g_r = fx[0].index_select(0, rows)                      # integers in float64: sums are exact
+            g_t = float((g_r.sum().to(torch.float32) * torch.tensor(fx[1], dtype=torch.float32)).item())
+        else:
+            g_t = float(g_r.sum().item())
         h_t = float(h_r.sum().item())
         p_dir.append(torch.sign(torch.tensor(-g_t / (h_t + lam), dtype=torch.float32)))
         per_era = torch.bincount(node_eras[i].to(torch.int64), minlength=n_eras).to(torch.float32)
@@ -434,6 +448,13 @@ def find_splits(
         Tc = cnt.sum(3, keepdim=True)
         Tg = gh.sum(3, keepdim=True)
         Th = hh.sum(3, keepdim=True)
+        Lg_winner = Lg.sum(dim=2)
+        if fx is not None:
+            # exact integer prefix sums and totals, each rounded to float32 once
+            inv32 = torch.tensor(fx[1], dtype=torch.float32)
+            Lg_winner = Lg_winner.to(torch.float32) * inv32
+            Lg = Lg.to(torch.float32) * inv32
+            Tg = Tg.to(torch.float32) * inv32
 
         # thresholds (booster.py:1790-1802)
         k_user = int(p.k_cuts)
@@ -544,7 +565,7 @@ def find_splits(
             c_thr = thr_ids.gather(0, t_in).to(torch.int32)
         # left grad / hess totals of the winner: float32 sum over eras of the
         # float32 prefix sums (booster.py:1948-1960)
-        lg_flat = Lg.sum(dim=2).gather(2, pick).permute(1, 0, 2).reshape(Nn, -1)
+        lg_flat = Lg_winner.gather(2, pick).permute(1, 0, 2).reshape(Nn, -1)
         lh_flat = Lh.sum(dim=2).gather(2, pick).permute(1, 0, 2).reshape(Nn, -1)
         c_lg = lg_flat.gather(1, gi).squeeze(1)
         c_lh = lh_flat.gather(1, gi).squeeze(1).to(torch.float32)
@@ -611,6 +632,30 @@ class OracleModel:
         return predict_codes(self.trees, codes, self.tree_weight)
 
 
+def fixed_point_bits(max_era_rows: int) -> int:
+    """Bits of the fixed-point gradients of the ``exact_sums`` variant: 30, fewer when an era
+    holds many rows (the CUDA histogram kernel accumulates a tile of at most 8 160 rows of one era
+    in 32-bit words: ``63 - 3 * bits(tile rows)``, at most 30)."""
+    tile = min(int(max_era_rows), 8160)
+    cb = 1
+    while (1 << cb) <= tile:
+        cb += 1
+    return min(63 - 3 * cb, 30)
+
+
+def fixed_point_gradients(grad: torch.Tensor, bits: int) -> tuple[torch.Tensor, float]:
+    """``(gq, inv_scale)`` of the ``exact_sums`` variant: ``gq = rint(g * scale)`` (ties to even,
+    computed in float32) with ``scale`` the power of two that keeps ``max|g| * scale`` below
+    ``2**bits``; ``gq`` is returned as float64 so that sums of up to 2^22 rows stay exact."""
+    m = float(grad.abs().max().item()) if grad.numel() else 0.0
+    if not (m > 0.0) or not np.isfinite(m):
+        return torch.zeros(grad.shape, dtype=torch.float64), 1.0
+    _, ex = np.frexp(np.float32(m))
+    sh = max(-100, min(100, int(bits) - int(ex)))
+    gq = torch.round(grad * torch.tensor(2.0 ** sh, dtype=torch.float32)).to(torch.float64)
+    return gq, float(2.0 ** -sh)
+
+
 def sample_features(rng: torch.Generator, n_features: int, fraction: float) -> torch.Tensor:
     """One ``randperm`` per depth on a CPU generator; the first
     ``max(1, round(fraction*F))`` entries in permutation order
@@ -663,6 +708,7 @@ def fit(
 
     lam = float(p.lambda_l2)
     lr32 = float(p.learning_rate)
+    gq_bits = fixed_point_bits(int(np.bincount(era_codes.astype(np.int64)).max())) if N else 30
     trees: list[dict[str, np.ndarray]] = []
     depth_records: list[dict] = []
     round_seconds: list[float] = []
@@ -672,12 +718,20 @@ def fit(
             t0 = perf_counter()
             grad.copy_(preds - y_t)                                  # booster.py:2149-2151
             hess.fill_(1.0)
+            fx = fixed_point_gradients(grad, gq_bits) if p.exact_sums else None
+
+            def node_grad_sum(rows_: torch.Tensor) -> float:
+                if fx is not None:
+                    tot = fx[0].index_select(0, rows_).sum().to(torch.float32)
+                    return float((tot * torch.tensor(fx[1], dtype=torch.float32)).item())
+                return float(grad[rows_].sum().item())
+
             tree = OracleTree()
             leaves: dict[int, torch.Tensor] = {0: root_rows}
             if root_rows.numel() == 0:
                 tree.set_leaf(0, 0.0)
             else:
-                g = float(grad[root_rows].sum().item())
+                g = node_grad_sum(root_rows)
                 h = float(hess[root_rows].sum().item())
                 tree.set_leaf(0, -g / (h + lam))
             frontier: list[tuple[int, torch.Tensor, torch.Tensor]] = [(0, root_rows, root_eras)]
@@ -688,13 +742,13 @@ def fit(
                     break
                 subset = sample_features(rng, F, p.layer_feature_fraction)
                 splits = find_splits([a[1] for a in active], [a[2] for a in active],
-                                     grad, hess, codes, subset, E, p)
+                                     grad, hess, codes, subset, E, p, fx=fx)
                 nxt: list[tuple[int, torch.Tensor, torch.Tensor]] = []
                 for (nid, rows, eras_r), dec in zip(active, splits):
                     if dec is None:
                         val = 0.0
                         if rows.numel() > 0:
-                            g = float(grad[rows].sum().item())
+                            g = node_grad_sum(rows)
                             h = float(hess[rows].sum().item())
                             val = -g / (h + lam)
                         leaves.setdefault(nid, rows)
@@ -747,9 +801,9 @@ def near_tie_gaps(X, y, era, p: OracleParams, num_rounds: int) -> np.ndarray:
     inner = find_splits
     gaps: list[float] = []
 
-    def spy(node_rows, node_eras, grad, hess, codes, subset, n_eras, params, trace=None):
+    def spy(node_rows, node_eras, grad, hess, codes, subset, n_eras, params, trace=None, fx=None):
         tr: dict = {}
-        out = inner(node_rows, node_eras, grad, hess, codes, subset, n_eras, params, trace=tr)
+        out = inner(node_rows, node_eras, grad, hess, codes, subset, n_eras, params, trace=tr, fx=fx)
         for ctx in range(len(tr.get("context_nodes", []))):
             sc = torch.cat([b["score"][ctx].reshape(-1) for b in tr["blocks"]])
             sc = sc[torch.isfinite(sc)]

@@ -760,6 +760,24 @@ class PackBoost:
         out[self._row_order] = p
         return out
 
+    # -- helpers the reference exposes on the booster (its own tests call them) ----------------
+    def _compute_era_weights(self, counts: torch.Tensor) -> torch.Tensor:
+        """Era weights from per-era row counts (``packboost/booster.py:815-826``): 0 for an absent
+        era, else 1, or ``count + era_alpha`` when ``era_alpha > 0``."""
+        counts = counts.to(torch.float32)
+        alpha = float(self.config.era_alpha)
+        present = counts > 0
+        w = counts + alpha if alpha > 0.0 else torch.ones_like(counts)
+        return torch.where(present, w, torch.zeros_like(counts))
+
+    def _batched_histograms_nodes(self, bins_matrix, grad_rows, hess_rows, era_ids, node_ids, num_nodes, num_eras,
+                                  num_bins):
+        """Counts and gradient / hessian sums ``[feature, node, era, bin]`` of the given rows
+        (``packboost/booster.py:933-977``), built by the histogram kernel."""
+        from .kernels import histograms_nodes
+        return histograms_nodes(bins_matrix, grad_rows, hess_rows, era_ids, node_ids, int(num_nodes), int(num_eras),
+                                int(num_bins))
+
     def split_records(self) -> dict[str, np.ndarray]:
         """Every split of the fit in the order the frontier produced it (round, depth, frontier
         position): tree node, feature, threshold, DES score (the ``SplitDecision.score`` of

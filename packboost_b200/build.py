@@ -18,9 +18,10 @@ LIB_NAME = "libpackboost_b200.so"
 LIB_PATH = os.path.join(HERE, LIB_NAME)
 
 SOURCES = ["api.cu", "hist.cu", "score.cu", "frontier.cu", "pack.cu", "predict.cu", "metrics.cu"]
-# The scorer must round every product and sum separately (no fused multiply-add) to keep the
-# float32 operation order of the algorithm it implements.
-EXTRA = {"score.cu": ["-fmad=false"]}
+# The scorer, and the histogram kernel whose flush computes the per-era gains, must round every
+# product and sum separately (no fused multiply-add) to keep the float32 operation order of the
+# algorithm they implement.
+EXTRA = {"score.cu": ["-fmad=false"], "hist.cu": ["-fmad=false"]}
 
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 COMMON = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "-Xptxas", "-v"]
@@ -44,7 +45,8 @@ def build(force: bool = False, verbose: bool = False) -> str:
     nvcc = _nvcc()
     objdir = os.path.join(HERE, "build")
     os.makedirs(objdir, exist_ok=True)
-    headers = [os.path.join(CSRC, "common.cuh"), os.path.join(HERE, "..", "include", "packboost_b200.h")]
+    headers = [os.path.join(CSRC, "common.cuh"), os.path.join(CSRC, "des_math.cuh"),
+               os.path.join(HERE, "..", "include", "packboost_b200.h")]
     objs = []
     log_lines = []
     for src in SOURCES:

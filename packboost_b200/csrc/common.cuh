@@ -84,6 +84,7 @@ struct CtlHead {
     int64_t root_gq;
     int32_t n_ctx[kMaxDepth + 2];
     int32_t any_dir[kMaxDepth + 2];
+    uint32_t select_ticket;  // CTAs of the running select launch that have written their node (reset by the last)
 };
 
 // Addresses of the sub-tables inside the caller's control block.
@@ -95,6 +96,7 @@ struct Ctl {
     pb_winner* winners;
     double* node_value;
     float* delta;
+    int32_t* sel_flag;  // per frontier node: bit 0 split, bit 1 left child stays active, bit 2 right child
 };
 
 constexpr size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
@@ -107,7 +109,8 @@ constexpr size_t kOffLog = kOffPart + align_up(sizeof(PartEntry) * kMaxCtx, 256)
 constexpr size_t kLogBytes = sizeof(pb_round_log_header) + sizeof(pb_winner) * kMaxWinners;
 constexpr size_t kOffNodeValue = kOffLog + align_up(kLogBytes, 256);
 constexpr size_t kOffDelta = kOffNodeValue + align_up(sizeof(double) * kMaxTreeNodes, 256);
-constexpr size_t kCtlBytes = kOffDelta + align_up(sizeof(float) * kMaxTreeNodes, 256);
+constexpr size_t kOffSelFlag = kOffDelta + align_up(sizeof(float) * kMaxTreeNodes, 256);
+constexpr size_t kCtlBytes = kOffSelFlag + align_up(sizeof(int32_t) * kMaxCtx, 256);
 
 inline __host__ __device__ Ctl ctl_view(void* base) {
     char* p = static_cast<char*>(base);
@@ -120,6 +123,7 @@ inline __host__ __device__ Ctl ctl_view(void* base) {
     c.winners = reinterpret_cast<pb_winner*>(p + kOffLog + sizeof(pb_round_log_header));
     c.node_value = reinterpret_cast<double*>(p + kOffNodeValue);
     c.delta = reinterpret_cast<float*>(p + kOffDelta);
+    c.sel_flag = reinterpret_cast<int32_t*>(p + kOffSelFlag);
     return c;
 }
 
@@ -147,7 +151,26 @@ struct HistLaunch {
     int max_arity;               // largest feature tuple of the lane kernel (1 or 2)
     uint32_t* cnt;
     int64_t* gsum;
+    // Fused flush (null: write the histogram as above).  When set and hist_can_fuse(h) holds, the
+    // histogram is never stored: the flush turns the cells of each (feature, node) of the CTA's era
+    // into the per-threshold (gain, weight) rows and adds the left counts / gradient sums into the
+    // era-summed tables, i.e. it does the work of the scorer's gain kernel.
+    struct HistFuse* fuse;
 };
+struct HistFuse {
+    float2* gw;                  // [n_feat][n_eras][node_stride][n_thr]
+    uint32_t* lc_tot;            // lane layout, see tot_index(); zeroed by launch_hist
+    int64_t* lg_tot;
+    const int32_t* thr_ids;      // device: [n_thr] ascending bin ids
+    int n_thr;
+    int full_sweep;              // thr_ids[k] == k for all k and n_thr == max_bins - 1
+    const float* inv_scale_ptr;
+    float lambda_l2, era_alpha;
+    int tot_fpl, tot_lanes;      // OUT: layout of the totals tables chosen by launch_hist
+};
+// True when launch_hist(h) would run the lane kernel with one tile per era, which is what the
+// fused flush needs (a CTA then holds the complete cells of its era).
+bool hist_can_fuse(const HistLaunch& h);
 int launch_hist(const HistLaunch& h, cudaStream_t stream);
 int hist_max_arity();  // default tuple-size cap of the lane kernel (PACKBOOST_HIST_MAX_ARITY=1 lowers it)
 
@@ -175,6 +198,8 @@ struct ScoreLaunch {
     float2* gw;                  // [n_feat][n_eras][node_stride][n_thr] (gain, validity weight)
     uint32_t* lc_tot;            // [n_feat][node_stride][n_thr] left counts summed over eras
     int64_t* lg_tot;             // [n_feat][node_stride][n_thr] left gradient sums summed over eras
+    int fused;                   // 1: gw and the totals were written by the histogram kernel's fused flush
+    int tot_fpl, tot_lanes;      // layout of lc_tot / lg_tot (tot_index(); 0, 0: the classic layout above)
 };
 int launch_score(const ScoreLaunch& s, cudaStream_t stream);
 size_t score_scratch_bytes_per_feature(int node_stride, int n_eras, int n_thr);

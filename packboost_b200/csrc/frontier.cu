@@ -31,6 +31,7 @@ __global__ void round_reset_kernel(Ctl c) {
         c.head->max_abs_bits = 0u;
         c.head->root_gq = 0;
         c.head->n_tree_nodes = 1;
+        c.head->select_ticket = 0u;
         for (int i = 0; i < kMaxDepth + 2; ++i) {
             c.head->n_ctx[i] = 0;
             c.head->any_dir[i] = 0;
@@ -156,34 +157,49 @@ __device__ __forceinline__ bool block_better(const BlockBest& x, const BlockBest
     return x.p > y.p;
 }
 
-__global__ void __launch_bounds__(512) select_kernel(SelectArgs a) {
+// One CTA per frontier node picks the node's winner: its warps take the feature blocks of the
+// sampled order in turn (a lane per candidate, butterfly inside the block), thread 0 merges the
+// block winners in block order.  The CTA that finishes last (a ticket counter in the control
+// block; nobody waits for anybody) then numbers the children of all nodes, builds the next
+// frontier and the partition table.
+constexpr int kSelThreads = 256;
+constexpr int kSelChunk = 64;  // block winners merged per pass
+
+__global__ void __launch_bounds__(kSelThreads) select_kernel(SelectArgs a) {
     Ctl& c = a.c;
-    __shared__ int s_flag[kMaxCtx];   // bit 0: split, bit 1: left child stays active, bit 2: right child
-    __shared__ int s_ids[kMaxCtx];    // exclusive count of splits before the node
-    __shared__ int s_slots[kMaxCtx];  // exclusive count of active children before the node
-    __shared__ int s_any_dir;
+    __shared__ BlockBest s_best[kSelChunk];
+    __shared__ int s_nan[kSelChunk];
+    __shared__ int s_thr[256];
+    __shared__ int s_last;
     const int n_ctx = c.head->n_ctx[a.depth];
-    if (n_ctx <= 0) return;
+    const int n = blockIdx.x;
+    if (n >= n_ctx) return;
     const FrontierNode* cur = c.frontier[a.depth & 1];
     FrontierNode* nxt = c.frontier[(a.depth + 1) & 1];
     pb_winner* win = c.winners + ((1 << a.depth) - 1);
     const float inv = c.head->inv_scale;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
     const bool keep_frontier = (a.depth + 1) < a.max_depth;
-    if (threadIdx.x == 0) s_any_dir = 0;
-
-    // threshold ids in shared memory: the cross-block merge looks one up per block
-    __shared__ int s_thr[256];
     for (int i = threadIdx.x; i < a.n_thr && i < 256; i += blockDim.x) s_thr[i] = a.thr_ids[i];
-    __syncthreads();
 
-    // ---- A. one warp per node: in-block winner (lanes stride the block), cross-block merge ----
-    for (int n = warp; n < n_ctx; n += n_warps) {
-        float best_s = -INFINITY;
-        long long best_c = -1, best_lg = 0;
-        int best_f = -1, best_t = -1;
-        // butterfly over the lanes' own bests of one block, then the merge across blocks
-        auto merge_block = [&](BlockBest mine, bool has_nan) {
+    // ---- A. this node: in-block winners by the warps, cross-block merge by thread 0 ----
+    float best_s = -INFINITY;
+    long long best_c = -1, best_lg = 0;
+    int best_f = -1, best_t = -1;
+    const int n_blocks = (a.n_sampled + a.block_size - 1) / a.block_size;
+    for (int blk0 = 0; blk0 < n_blocks; blk0 += kSelChunk) {
+        const int blk1 = min(n_blocks, blk0 + kSelChunk);
+        for (int blk = blk0 + warp; blk < blk1; blk += n_warps) {
+            const int b0 = blk * a.block_size, b1 = min(a.n_sampled, b0 + a.block_size);
+            BlockBest mine{-INFINITY, -1, 0, -1, -1, -1};
+            bool has_nan = false;
+            for (int p = b0 + lane; p < b1; p += 32) {
+                const Cand cd = a.cand[(size_t)p * a.node_stride + n];
+                if (cd.flags & 1u) has_nan = true;
+                if (cd.k < 0) continue;
+                const BlockBest x{cd.score, (long long)cd.left_count, cd.left_gq, p, cd.k, a.sampled[p]};
+                if (block_better(x, mine)) mine = x;
+            }
             has_nan = __any_sync(0xFFFFFFFFu, has_nan);
             for (int d = 16; d > 0; d >>= 1) {
                 BlockBest o;
@@ -195,157 +211,146 @@ __global__ void __launch_bounds__(512) select_kernel(SelectArgs a) {
                 o.f = __shfl_xor_sync(0xFFFFFFFFu, mine.f, d);
                 if (block_better(o, mine)) mine = o;
             }
-            if (has_nan || mine.p < 0) return;
-            const int feat = mine.f;
-            const int thr = s_thr[mine.k];
-            const bool upd = (mine.s > best_s) ||
-                             (mine.s == best_s && ((mine.c > best_c) ||
-                                                   (mine.c == best_c && ((feat > best_f) || (feat == best_f && thr > best_t)))));
-            if (upd) { best_s = mine.s; best_c = mine.c; best_lg = mine.lg; best_f = feat; best_t = thr; }
-        };
-        if (a.block_size <= 32) {
-            // a lane holds at most one candidate per block: the loads of eight blocks go out together
-            constexpr int kGroup = 8;
-            const int n_blocks = (a.n_sampled + a.block_size - 1) / a.block_size;
-            for (int g0 = 0; g0 < n_blocks; g0 += kGroup) {
-                Cand cd[kGroup];
-                int ft[kGroup];
-#pragma unroll
-                for (int j = 0; j < kGroup; ++j) {
-                    const int p = (g0 + j) * a.block_size + lane;
-                    const bool in = (g0 + j < n_blocks) && (lane < a.block_size) && (p < a.n_sampled);
-                    cd[j].score = 0.f;
-                    cd[j].k = -1;
-                    cd[j].left_count = 0u;
-                    cd[j].flags = 0u;
-                    cd[j].left_gq = 0ll;
-                    ft[j] = -1;
-                    if (in) {
-                        cd[j] = a.cand[(size_t)p * a.node_stride + n];
-                        ft[j] = a.sampled[p];
-                    }
-                }
-#pragma unroll
-                for (int j = 0; j < kGroup; ++j) {
-                    if (g0 + j >= n_blocks) break;
-                    const int p = (g0 + j) * a.block_size + lane;
-                    BlockBest mine{-INFINITY, -1, 0, -1, -1, -1};
-                    if (cd[j].k >= 0) mine = BlockBest{cd[j].score, (long long)cd[j].left_count, cd[j].left_gq, p, cd[j].k, ft[j]};
-                    merge_block(mine, (cd[j].flags & 1u) != 0u);
-                }
+            if (lane == 0) {
+                s_best[blk - blk0] = mine;
+                s_nan[blk - blk0] = has_nan ? 1 : 0;
             }
+        }
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            // across blocks, in block order: strictly better on (score, left count, feature id, threshold)
+            for (int j = 0; j < blk1 - blk0; ++j) {
+                const BlockBest& m = s_best[j];
+                if (s_nan[j] || m.p < 0) continue;
+                const int feat = m.f;
+                const int thr = s_thr[m.k];
+                const bool upd = (m.s > best_s) ||
+                                 (m.s == best_s && ((m.c > best_c) ||
+                                                    (m.c == best_c && ((feat > best_f) || (feat == best_f && thr > best_t)))));
+                if (upd) { best_s = m.s; best_c = m.c; best_lg = m.lg; best_f = feat; best_t = thr; }
+            }
+        }
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) {
+        const FrontierNode fn = cur[n];
+        pb_winner w;
+        w.feature = best_f;
+        w.threshold = best_t;
+        w.score = best_s;
+        w.tree_node = fn.tree_node;
+        w.left_count = (best_f >= 0) ? best_c : 0;
+        w.total_count = fn.count;
+        w.left_gq = (best_f >= 0) ? best_lg : 0;
+        w.total_gq = fn.gq;
+        w.left_id = -1;
+        w.right_id = -1;
+        const float tg32 = __fmul_rn(__ll2float_rn(fn.gq), inv);
+        const float lg32 = __fmul_rn(__ll2float_rn(w.left_gq), inv);
+        const float th32 = (float)fn.count;
+        const float lh32 = (float)w.left_count;
+        w.left_grad = lg32;
+        w.total_grad = tg32;
+        int flag = 0;
+        if (best_f >= 0) {
+            w.left_value = -(double)lg32 / ((double)lh32 + a.lambda);
+            const double rg = (double)tg32 - (double)lg32;
+            const double rh = (double)th32 - (double)lh32;
+            w.right_value = -rg / (rh + a.lambda);
+            flag = 1;
+            if (keep_frontier && w.left_count >= 2ll * a.min_leaf) flag |= 2;
+            if (keep_frontier && (w.total_count - w.left_count) >= 2ll * a.min_leaf) flag |= 4;
         } else {
-            for (int b0 = 0; b0 < a.n_sampled; b0 += a.block_size) {
-                const int b1 = min(a.n_sampled, b0 + a.block_size);
-                BlockBest mine{-INFINITY, -1, 0, -1, -1, -1};
-                bool has_nan = false;
-                for (int p = b0 + lane; p < b1; p += 32) {
-                    const Cand cd = a.cand[(size_t)p * a.node_stride + n];
-                    if (cd.flags & 1u) has_nan = true;
-                    if (cd.k < 0) continue;
-                    const BlockBest x{cd.score, (long long)cd.left_count, cd.left_gq, p, cd.k, a.sampled[p]};
-                    if (block_better(x, mine)) mine = x;
-                }
-                merge_block(mine, has_nan);
-            }
+            // no usable candidate: the node stays a leaf with its Newton value
+            w.left_value = -(double)tg32 / ((double)th32 + a.lambda);
+            w.right_value = w.left_value;
         }
-        if (lane == 0) {
-            const FrontierNode fn = cur[n];
-            pb_winner w;
-            w.feature = best_f;
-            w.threshold = best_t;
-            w.score = best_s;
-            w.tree_node = fn.tree_node;
-            w.left_count = (best_f >= 0) ? best_c : 0;
-            w.total_count = fn.count;
-            w.left_gq = (best_f >= 0) ? best_lg : 0;
-            w.total_gq = fn.gq;
-            w.left_id = -1;
-            w.right_id = -1;
-            const float tg32 = __fmul_rn(__ll2float_rn(fn.gq), inv);
-            const float lg32 = __fmul_rn(__ll2float_rn(w.left_gq), inv);
-            const float th32 = (float)fn.count;
-            const float lh32 = (float)w.left_count;
-            w.left_grad = lg32;
-            w.total_grad = tg32;
-            int flag = 0;
-            if (best_f >= 0) {
-                w.left_value = -(double)lg32 / ((double)lh32 + a.lambda);
-                const double rg = (double)tg32 - (double)lg32;
-                const double rh = (double)th32 - (double)lh32;
-                w.right_value = -rg / (rh + a.lambda);
-                flag = 1;
-                if (keep_frontier && w.left_count >= 2ll * a.min_leaf) flag |= 2;
-                if (keep_frontier && (w.total_count - w.left_count) >= 2ll * a.min_leaf) flag |= 4;
-            } else {
-                // no usable candidate: the node stays a leaf with its Newton value
-                w.left_value = -(double)tg32 / ((double)th32 + a.lambda);
-                w.right_value = w.left_value;
-            }
-            win[n] = w;
-            s_flag[n] = flag;
-        }
+        win[n] = w;
+        c.sel_flag[n] = flag;
+        __threadfence();  // the winner and the flag are visible before the ticket is
+        const unsigned ticket = atomicAdd(&c.head->select_ticket, 1u);
+        s_last = (ticket == (unsigned)n_ctx - 1u) ? 1 : 0;
     }
     __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    if (threadIdx.x == 0) c.head->select_ticket = 0u;  // ready for the next launch
 
-    // ---- B. warp 0: exclusive prefix counts of splits and of active children ----
-    if (warp == 0) {
-        int carry_id = 0, carry_slot = 0;
-        for (int base = 0; base < n_ctx; base += 32) {
-            const int n = base + lane;
-            const int fl = (n < n_ctx) ? s_flag[n] : 0;
-            int v_id = fl & 1;
-            int v_slot = ((fl >> 1) & 1) + ((fl >> 2) & 1);
-            const int own_id = v_id, own_slot = v_slot;
-            for (int d = 1; d < 32; d <<= 1) {
-                const int t1 = __shfl_up_sync(0xFFFFFFFFu, v_id, d);
-                const int t2 = __shfl_up_sync(0xFFFFFFFFu, v_slot, d);
-                if (lane >= d) { v_id += t1; v_slot += t2; }
-            }
-            if (n < n_ctx) {
-                s_ids[n] = carry_id + v_id - own_id;
-                s_slots[n] = carry_slot + v_slot - own_slot;
-            }
-            carry_id += __shfl_sync(0xFFFFFFFFu, v_id, 31);
-            carry_slot += __shfl_sync(0xFFFFFFFFu, v_slot, 31);
+    // ---- B. (last CTA) exclusive prefix counts of splits and of active children, one warp ----
+    // (other CTAs wrote the flags and winners: they are read past the L1 of this SM)
+    const volatile int32_t* flags = c.sel_flag;
+    __shared__ int s_first_id, s_any_dir;
+    if (threadIdx.x == 0) s_any_dir = 0;
+    // per 32-node group the number of splits / active children, then their exclusive prefix
+    __shared__ int s_grp_id[kMaxCtx / 32 + 1], s_grp_slot[kMaxCtx / 32 + 1];
+    const int n_groups = (n_ctx + 31) / 32;
+    for (int g = warp; g < n_groups; g += n_warps) {
+        const int i = g * 32 + lane;
+        const int fl = (i < n_ctx) ? flags[i] : 0;
+        int v_id = fl & 1, v_slot = ((fl >> 1) & 1) + ((fl >> 2) & 1);
+        for (int d = 16; d > 0; d >>= 1) {
+            v_id += __shfl_xor_sync(0xFFFFFFFFu, v_id, d);
+            v_slot += __shfl_xor_sync(0xFFFFFFFFu, v_slot, d);
         }
-        if (lane == 0) {
-            const int next_id = c.head->n_tree_nodes + 2 * carry_id;
-            c.head->n_tree_nodes = next_id;
-            c.head->n_ctx[a.depth + 1] = carry_slot;
-            c.log_head->n_ctx[a.depth] = n_ctx;
-            if (a.depth + 1 <= kMaxDepth) c.log_head->n_ctx[a.depth + 1] = carry_slot;
-            c.log_head->n_tree_nodes = next_id;
-        }
+        if (lane == 0) { s_grp_id[g] = v_id; s_grp_slot[g] = v_slot; }
     }
     __syncthreads();
-    // (n_tree_nodes was advanced above; recover the value it had before this depth)
-    int total_splits = 0;
-    {
-        const int last = n_ctx - 1;
-        total_splits = s_ids[last] + (s_flag[last] & 1);
+    if (threadIdx.x == 0) {
+        int run_id = 0, run_slot = 0;
+        for (int g = 0; g < n_groups; ++g) {
+            const int t1 = s_grp_id[g], t2 = s_grp_slot[g];
+            s_grp_id[g] = run_id;
+            s_grp_slot[g] = run_slot;
+            run_id += t1;
+            run_slot += t2;
+        }
+        s_first_id = c.head->n_tree_nodes;
+        const int next_id = s_first_id + 2 * run_id;
+        c.head->n_tree_nodes = next_id;
+        c.head->n_ctx[a.depth + 1] = run_slot;
+        c.log_head->n_ctx[a.depth] = n_ctx;
+        if (a.depth + 1 <= kMaxDepth) c.log_head->n_ctx[a.depth + 1] = run_slot;
+        c.log_head->n_tree_nodes = next_id;
     }
-    const int first_id = c.head->n_tree_nodes - 2 * total_splits;
+    __syncthreads();
+    const int first_id = s_first_id;
 
-    // ---- C. one thread per node: child ids, next frontier, partition table ----
+    // ---- C. (last CTA) child ids, next frontier, partition table: a warp per 32-node group ----
     int any_dir = 0;
-    for (int n = threadIdx.x; n < n_ctx; n += blockDim.x) {
-        pb_winner& w = win[n];
-        const int fl = s_flag[n];
+    for (int g = warp; g < n_groups; g += n_warps) {
+        const int i = g * 32 + lane;
+        const int fl = (i < n_ctx) ? flags[i] : 0;
+        int v_id = fl & 1, v_slot = ((fl >> 1) & 1) + ((fl >> 2) & 1);
+        const int own_id = v_id, own_slot = v_slot;
+        for (int d = 1; d < 32; d <<= 1) {
+            const int t1 = __shfl_up_sync(0xFFFFFFFFu, v_id, d);
+            const int t2 = __shfl_up_sync(0xFFFFFFFFu, v_slot, d);
+            if (lane >= d) { v_id += t1; v_slot += t2; }
+        }
+        if (i >= n_ctx) continue;
+        const int ids_before = s_grp_id[g] + v_id - own_id;
+        int slot = s_grp_slot[g] + v_slot - own_slot;
+        pb_winner w;
+        {
+            const volatile pb_winner* src = win + i;
+            w.feature = src->feature; w.threshold = src->threshold; w.tree_node = src->tree_node;
+            w.left_count = src->left_count; w.total_count = src->total_count;
+            w.left_gq = src->left_gq; w.total_gq = src->total_gq;
+            w.left_value = src->left_value; w.right_value = src->right_value;
+        }
         PartEntry pe;
         pe.feature = w.feature;
         pe.threshold = w.threshold;
         pe.slot_left = pe.slot_right = kSlotNone;
         pe.leaf_left = pe.leaf_right = (uint16_t)w.tree_node;
         if (fl & 1) {
-            const int lid = first_id + 2 * s_ids[n];
-            w.left_id = lid;
-            w.right_id = lid + 1;
+            const int lid = first_id + 2 * ids_before;
+            win[i].left_id = lid;
+            win[i].right_id = lid + 1;
             pe.leaf_left = (uint16_t)lid;
             pe.leaf_right = (uint16_t)(lid + 1);
             c.node_value[lid] = w.left_value;
             c.node_value[lid + 1] = w.right_value;
-            int slot = s_slots[n];
             if (fl & 2) {
                 FrontierNode fn; fn.tree_node = lid; fn.count = (int32_t)w.left_count; fn.gq = w.left_gq;
                 nxt[slot] = fn;
@@ -362,7 +367,7 @@ __global__ void __launch_bounds__(512) select_kernel(SelectArgs a) {
         } else {
             c.node_value[w.tree_node] = w.left_value;
         }
-        c.part[n] = pe;
+        c.part[i] = pe;
     }
     if (any_dir) atomicOr(&s_any_dir, 1);
     __syncthreads();
@@ -542,18 +547,26 @@ static int need_workspace(const pb_train_state* st, const char* who) {
 // scorer: gsum | cnt | gain-weight table | era-summed gradient sums | era-summed counts.
 struct BlockPlan {
     int64_t fb;  // features per block
+    bool fused;  // the histogram is never stored (fused flush): no gsum / cnt arrays
     size_t off_gsum, off_cnt, off_gw, off_lg, off_lc;
 };
 
+// The era-summed tables of the fused flush are laid out per lane of the histogram kernel and so
+// cover the features of the last CTA in full: up to this many features more than the block has.
+constexpr int64_t kTotPad = 128;
+
 static bool plan_block(size_t avail, int stride, int64_t n_eras, int64_t max_bins, int64_t n_thr, int64_t n_feat,
-                       BlockPlan* p) {
-    const size_t cells = (size_t)stride * n_eras * max_bins;
+                       bool fused, BlockPlan* p) {
+    const size_t cells = fused ? 0 : (size_t)stride * n_eras * max_bins;
     const size_t per_feat = cells * 12 + score_scratch_bytes_per_feature(stride, (int)n_eras, (int)n_thr);
-    if (avail < per_feat + 5 * 256) return false;
-    int64_t fb = (int64_t)((avail - 5 * 256) / per_feat);
+    const size_t fixed = 5 * 256 + (fused ? (size_t)kTotPad * stride * n_thr * 12 : 0);
+    if (avail < per_feat + fixed) return false;
+    int64_t fb = (int64_t)((avail - fixed) / per_feat);
     if (fb > n_feat) fb = n_feat;
     if (fb < 1) return false;
     p->fb = fb;
+    p->fused = fused;
+    const size_t tot_feats = (size_t)fb + (fused ? kTotPad : 0);
     size_t o = 0;
     p->off_gsum = o;
     o += align_up((size_t)fb * cells * 8, 256);
@@ -562,9 +575,49 @@ static bool plan_block(size_t avail, int stride, int64_t n_eras, int64_t max_bin
     p->off_gw = o;
     o += align_up((size_t)fb * stride * n_eras * n_thr * 8, 256);
     p->off_lg = o;
-    o += align_up((size_t)fb * stride * n_thr * 8, 256);
+    o += align_up(tot_feats * stride * n_thr * 8, 256);
     p->off_lc = o;
     return true;
+}
+
+// The histogram launch of one depth, up to the feature list and the output arrays.
+static HistLaunch hist_launch_of(const pb_train_state* st, int64_t depth, const Ctl& c) {
+    const int stride = node_stride_of(depth);
+    HistLaunch h;
+    h.codes = st->codes;
+    h.pitch = st->pitch;
+    h.code_bits = (int)st->code_bits;
+    h.feat_rows = nullptr;
+    h.n_feat = 1;
+    h.gq = st->gq;
+    h.slot = st->slot;
+    h.era_offsets = st->era_offsets;
+    h.n_eras = (int)st->n_eras;
+    h.max_bins = (int)st->max_bins;
+    h.max_era_rows = (int)st->max_era_rows;
+    h.n_nodes_ptr = &c.head->n_ctx[depth];
+    h.n_nodes = stride;
+    h.node_stride = stride;
+    h.count_bits = (int)st->count_bits;
+    h.lo_bits = (int)st->lo_bits;
+    h.max_arity = hist_max_arity();
+    h.cnt = nullptr;
+    h.gsum = nullptr;
+    h.fuse = nullptr;
+    return h;
+}
+
+// The flush of the histogram kernel does the per-era gain step itself when a CTA holds a whole era
+// of few-bin cells and no directional term needs the stored histogram (PACKBOOST_FUSED_FLUSH=0
+// keeps the separate gain kernel, for comparisons).
+static bool use_fused_flush(const pb_train_state* st, int64_t depth) {
+    static const bool enabled = [] {
+        const char* e = getenv("PACKBOOST_FUSED_FLUSH");
+        return !(e && e[0] == '0' && e[1] == 0);
+    }();
+    if (!enabled || st->direction_weight != 0.0) return false;
+    Ctl c = ctl_view(st->ctl);
+    return hist_can_fuse(hist_launch_of(st, depth, c));
 }
 
 static int hist_score_blocks(const pb_train_state* st, int64_t depth, const int32_t* feat_rows, const int32_t* feat_pos,
@@ -575,26 +628,28 @@ static int hist_score_blocks(const pb_train_state* st, int64_t depth, const int3
     uint32_t* cnt = reinterpret_cast<uint32_t*>(scratch + plan.off_cnt);
     for (int64_t f0 = 0; f0 < n_feat; f0 += plan.fb) {
         const int nf = (int)((n_feat - f0 < plan.fb) ? (n_feat - f0) : plan.fb);
-        HistLaunch h;
-        h.codes = st->codes;
-        h.pitch = st->pitch;
-        h.code_bits = (int)st->code_bits;
+        HistLaunch h = hist_launch_of(st, depth, c);
         h.feat_rows = feat_rows + f0;
         h.n_feat = nf;
-        h.gq = st->gq;
-        h.slot = st->slot;
-        h.era_offsets = st->era_offsets;
-        h.n_eras = (int)st->n_eras;
-        h.max_bins = (int)st->max_bins;
-        h.max_era_rows = (int)st->max_era_rows;
-        h.n_nodes_ptr = &c.head->n_ctx[depth];
-        h.n_nodes = stride;
-        h.node_stride = stride;
-        h.count_bits = (int)st->count_bits;
-        h.lo_bits = (int)st->lo_bits;
-        h.max_arity = hist_max_arity();
         h.cnt = cnt;   // the histogram kernel overwrites (or zeroes, then adds to) every cell that is read later
         h.gsum = gsum;
+        HistFuse fz;
+        memset(&fz, 0, sizeof(fz));
+        if (plan.fused) {
+            fz.gw = reinterpret_cast<float2*>(scratch + plan.off_gw);
+            fz.lg_tot = reinterpret_cast<int64_t*>(scratch + plan.off_lg);
+            fz.lc_tot = reinterpret_cast<uint32_t*>(scratch + plan.off_lc);
+            fz.thr_ids = st->thr_ids;
+            fz.n_thr = (int)st->n_thresholds;
+            // ascending distinct bin ids below max_bins - 1: as many as there are means all of them
+            fz.full_sweep = (st->n_thresholds == st->max_bins - 1) ? 1 : 0;
+            fz.inv_scale_ptr = &c.head->inv_scale;
+            fz.lambda_l2 = (float)st->lambda_l2;
+            fz.era_alpha = (float)(st->era_alpha > 0.0 ? st->era_alpha : 0.0);
+            h.fuse = &fz;
+            h.cnt = nullptr;
+            h.gsum = nullptr;
+        }
         int rc = launch_hist(h, stream);
         if (rc) return rc;
         ScoreLaunch s;
@@ -621,6 +676,9 @@ static int hist_score_blocks(const pb_train_state* st, int64_t depth, const int3
         s.gw = reinterpret_cast<float2*>(scratch + plan.off_gw);
         s.lg_tot = reinterpret_cast<int64_t*>(scratch + plan.off_lg);
         s.lc_tot = reinterpret_cast<uint32_t*>(scratch + plan.off_lc);
+        s.fused = plan.fused ? 1 : 0;
+        s.tot_fpl = plan.fused ? fz.tot_fpl : 0;
+        s.tot_lanes = plan.fused ? fz.tot_lanes : 0;
         rc = launch_score(s, stream);
         if (rc) return rc;
     }
@@ -721,7 +779,7 @@ extern "C" int pb_depth_hist_score(const pb_train_state* st, int64_t depth, cons
     char* ws = static_cast<char*>(st->workspace);
     BlockPlan plan;
     PB_REQUIRE(plan_block((size_t)st->workspace_bytes - cand_bytes, stride, st->n_eras, st->max_bins, st->n_thresholds,
-                          n_feat, &plan),
+                          n_feat, use_fused_flush(st, depth), &plan),
                "workspace too small for one feature of histogram at depth %lld", (long long)depth);
     return hist_score_blocks(st, depth, feat_rows, feat_pos, n_feat, ws + cand_bytes, plan, reinterpret_cast<Cand*>(ws),
                              (cudaStream_t)stream_);
@@ -759,7 +817,7 @@ extern "C" int pb_depth_select_cand(const pb_train_state* st, int64_t depth, con
     a.min_leaf = (int)st->min_samples_leaf;
     a.lambda = st->lambda_l2;
     prof_begin(kProfSelect, (cudaStream_t)stream_);
-    select_kernel<<<1, 512, 0, (cudaStream_t)stream_>>>(a);
+    select_kernel<<<(unsigned)a.node_stride, kSelThreads, 0, (cudaStream_t)stream_>>>(a);
     prof_end(kProfSelect, (cudaStream_t)stream_);
     count_launch(1);
     PB_LAUNCH_CHECK("select_kernel");
@@ -913,7 +971,8 @@ extern "C" int pb_depth_hist_score_static(const pb_train_state* st, int64_t dept
     PB_REQUIRE(feat_rows && feat_pos, "null feature list");
     const int stride = node_stride_of(depth);
     BlockPlan plan;
-    PB_REQUIRE(plan_block(kStaticScratchBytes, stride, st->n_eras, st->max_bins, st->n_thresholds, n_feat, &plan),
+    PB_REQUIRE(plan_block(kStaticScratchBytes, stride, st->n_eras, st->max_bins, st->n_thresholds, n_feat,
+                          use_fused_flush(st, depth), &plan),
                "static scratch too small: one feature of histogram and scorer tables at depth %lld needs %llu bytes, "
                "the fixed array holds %llu; use pb_depth_hist_score with a workspace",
                (long long)depth,

@@ -32,7 +32,10 @@
 
 #include <stdlib.h>
 
+#include <type_traits>
+
 #include "common.cuh"
+#include "des_math.cuh"
 
 namespace pb {
 
@@ -65,6 +68,8 @@ struct HistKernelArgs {
     int lo_bits;     // LB
     uint32_t* cnt;
     int64_t* gsum;
+    int fuse;        // 1: the lane kernel's flush writes gains and era-summed totals instead of the histogram
+    HistFuse fz;
 };
 
 template <int BITS, int THREADS>
@@ -411,6 +416,135 @@ __global__ void __launch_bounds__(kLaneWarps * 32, 2) hist_lane_kernel(HistKerne
     // warp take different items and add up the columns of the R lanes that own the tuple
     const uint32_t cmask = (1u << CB) - 1u;
     const int col0 = lane - phase * TL;
+    if (a.fuse) {
+        // ---- fused flush: per-era gains instead of the histogram -----------------------------------
+        // The CTA holds the complete cells of its era (one tile per era), so everything the scorer
+        // needs from this era is computed here: the prefix over the bins of every (feature, node), the
+        // gain and validity weight of every threshold (one 8-byte entry each), and the era's
+        // contribution to the left counts / gradient sums summed over eras (integer atomics: exact and
+        // independent of their order).  The histogram itself is never written.
+        const HistFuse& z = a.fz;
+        __shared__ int s_thr[kLaneBinsMax];
+        if (threadIdx.x < kLaneBinsMax) s_thr[threadIdx.x] = (threadIdx.x < z.n_thr) ? z.thr_ids[threadIdx.x] : -1;
+        __syncthreads();
+        const float inv_scale = *z.inv_scale_ptr;
+        const int K = z.n_thr;
+        const int lane_global = blockIdx.y * TL + col0;   // == (feat0 + fl) / FPL for every fl
+        const int lanes_total = gridDim.y * TL;
+        auto fuse_emit = [&](auto nbt_c, int fl, int n, const uint32_t (&aw)[kLaneBinsMax],
+                             const uint32_t (&bw)[kLaneBinsMax]) {
+            constexpr int NBT = decltype(nbt_c)::value;  // compile-time bound of the bin count
+            uint32_t cb[NBT];
+            long long gb[NBT];
+            uint32_t tc = 0;
+            long long tgq = 0;
+#pragma unroll
+            for (int b = 0; b < NBT; ++b) {
+                cb[b] = aw[b] & cmask;
+                gb[b] = (long long)(int32_t)bw[b] * (1ll << LB) + (long long)(aw[b] >> CB);
+                if (b < nb) {
+                    tc += cb[b];
+                    tgq += gb[b];
+                }
+            }
+            const EraTotals et = era_totals(tc, tgq, inv_scale, z.lambda_l2, z.era_alpha);
+            float2* out = z.gw + (((size_t)(feat0 + fl) * a.n_eras + era) * a.node_stride + n) * K;
+            const size_t tot0 = (((size_t)n * K) * FPL + fl) * lanes_total + lane_global;  // threshold 0
+            const size_t tot_step = (size_t)FPL * lanes_total;
+            uint32_t c = 0;
+            long long g = 0;
+            if (NBT == 5 && z.full_sweep) {
+                float2 gk[4];
+#pragma unroll
+                for (int b = 0; b < 4; ++b) {
+                    c += cb[b];
+                    g += gb[b];
+                    gk[b] = gain_of(c, g, tc, et.tg, et.th, et.parent, inv_scale, z.lambda_l2, et.w_era);
+                    if (c) atomicAdd(z.lc_tot + tot0 + b * tot_step, c);
+                    if (g) atomicAdd(reinterpret_cast<unsigned long long*>(z.lg_tot + tot0 + b * tot_step), (unsigned long long)g);
+                }
+                reinterpret_cast<float4*>(out)[0] = make_float4(gk[0].x, gk[0].y, gk[1].x, gk[1].y);
+                reinterpret_cast<float4*>(out)[1] = make_float4(gk[2].x, gk[2].y, gk[3].x, gk[3].y);
+            } else {
+                int kk = 0;
+                int next = s_thr[0];
+#pragma unroll
+                for (int b = 0; b < NBT - 1; ++b) {
+                    if (b < nb - 1) {
+                        c += cb[b];
+                        g += gb[b];
+                        if (b == next) {
+                            out[kk] = gain_of(c, g, tc, et.tg, et.th, et.parent, inv_scale, z.lambda_l2, et.w_era);
+                            if (c) atomicAdd(z.lc_tot + tot0 + kk * tot_step, c);
+                            if (g) atomicAdd(reinterpret_cast<unsigned long long*>(z.lg_tot + tot0 + kk * tot_step), (unsigned long long)g);
+                            ++kk;
+                            next = (kk < K) ? s_thr[kk] : -1;
+                        }
+                    }
+                }
+            }
+        };
+        for (int item = warp * R + phase; item < n_nodes * T; item += kLaneWarps * R) {
+            const int n = item / T, t = item - n * T;
+            if (A * t >= n_mine) continue;
+            const uint32_t* tcells = cells + (size_t)t * n_cells * 64;
+            if (A == 2 && nb == 5) {
+                // every joint cell is read once and added to the row sum of one feature and the column
+                // sum of the other
+                const uint32_t* tc2 = tcells + (size_t)(n * 25) * 64 + col0;
+                uint32_t a0[kLaneBinsMax], b0[kLaneBinsMax], a1[kLaneBinsMax], b1[kLaneBinsMax];
+#pragma unroll
+                for (int b = 0; b < kLaneBinsMax; ++b) a0[b] = b0[b] = a1[b] = b1[b] = 0u;
+#pragma unroll
+                for (int c1 = 0; c1 < 5; ++c1)
+#pragma unroll
+                    for (int c0 = 0; c0 < 5; ++c0) {
+                        uint32_t aw = 0, bw = 0;
+#pragma unroll
+                        for (int ph = 0; ph < R; ++ph) {
+                            aw += tc2[(c1 * 5 + c0) * 64 + ph * TL];
+                            bw += tc2[(c1 * 5 + c0) * 64 + ph * TL + 32];
+                        }
+                        a0[c0] += aw;
+                        b0[c0] += bw;
+                        a1[c1] += aw;
+                        b1[c1] += bw;
+                    }
+                fuse_emit(std::integral_constant<int, 5>(), 2 * t, n, a0, b0);
+                if (2 * t + 1 < n_mine) fuse_emit(std::integral_constant<int, 5>(), 2 * t + 1, n, a1, b1);
+            } else {
+                int below = 1;  // bins^fi
+                for (int fi = 0; fi < A; ++fi, below *= nb) {
+                    const int fl = t * A + fi;
+                    if (fl >= n_mine) break;
+                    const int above = cpn / (below * nb);
+                    uint32_t aw[kLaneBinsMax], bw[kLaneBinsMax];
+#pragma unroll
+                    for (int b = 0; b < kLaneBinsMax; ++b) {
+                        aw[b] = 0u;
+                        bw[b] = 0u;
+                        if (b >= nb) continue;
+                        uint32_t a_sum = 0, b_sum = 0;
+                        for (int hi = 0; hi < above; ++hi)
+                            for (int lo = 0; lo < below; ++lo) {
+                                const uint32_t cell = (uint32_t)(n * cpn + (hi * nb + b) * below + lo) * 64u + col0;
+#pragma unroll
+                                for (int ph = 0; ph < R; ++ph) {
+                                    a_sum += tcells[cell + ph * TL];
+                                    b_sum += tcells[cell + ph * TL + 32];
+                                }
+                            }
+                        aw[b] = a_sum;
+                        bw[b] = b_sum;
+                    }
+                    if (nb == 5) fuse_emit(std::integral_constant<int, 5>(), fl, n, aw, bw);
+                    else fuse_emit(std::integral_constant<int, kLaneBinsMax>(), fl, n, aw, bw);
+                }
+            }
+        }
+        return;
+    }
+
     // decode the packed sums of the bins of one (feature, node) and write them out
     auto emit = [&](int fl, int n, const uint32_t (&aw)[kLaneBinsMax], const uint32_t (&bw)[kLaneBinsMax]) {
         const size_t o0 = (((size_t)(feat0 + fl) * a.n_eras + era) * a.node_stride + n) * nb;
@@ -587,6 +721,11 @@ int hist_max_arity() {
     return 2;
 }
 
+bool hist_can_fuse(const HistLaunch& h) {
+    return h.code_bits == 4 && h.max_era_rows <= kTileRowsMax &&
+           (int64_t)h.n_nodes * h.max_bins * kLaneCellBytes <= kLaneSmemMax && h.n_feat > 0 && h.n_nodes > 0;
+}
+
 int launch_hist(const HistLaunch& h, cudaStream_t stream) {
     if (h.n_feat <= 0 || h.n_nodes <= 0) return PB_OK;
     HistKernelArgs a;
@@ -606,6 +745,8 @@ int launch_hist(const HistLaunch& h, cudaStream_t stream) {
     a.gsum = h.gsum;
     a.count_bits = h.count_bits;
     a.lo_bits = h.lo_bits;
+    a.fuse = 0;
+    memset(&a.fz, 0, sizeof(a.fz));
 
     const int rpi = (h.code_bits == 4) ? 32 : 16;
     a.tile_rows = kTileRowsMax;
@@ -670,6 +811,17 @@ int launch_hist(const HistLaunch& h, cudaStream_t stream) {
         a.group = arity;
         a.copies = 1;
         const size_t smem = slot * tuples;  // cells; the launcher adds the per-warp staging
+        if (h.fuse && !a.use_atomics) {
+            a.fuse = 1;
+            h.fuse->tot_fpl = arity * tuples;
+            h.fuse->tot_lanes = ((h.n_feat + a.feats_per_cta - 1) / a.feats_per_cta) * (32 / phases);
+            a.fz = *h.fuse;
+            const size_t tot = (size_t)h.node_stride * a.fz.n_thr * a.fz.tot_fpl * a.fz.tot_lanes;
+            PB_CUDA_TRY(cudaMemsetAsync(a.fz.lc_tot, 0, tot * sizeof(uint32_t), stream));
+            PB_CUDA_TRY(cudaMemsetAsync(a.fz.lg_tot, 0, tot * sizeof(int64_t), stream));
+        } else if (h.fuse) {
+            return fail_arg("fused flush requested for a launch that cannot fuse (check hist_can_fuse first)");
+        }
         prof_begin(kProfHist, stream);
         int rc;
         if (arity == 2) rc = (tuples == 2) ? launch_lane<2, 2>(a, smem, phases, stream) : launch_lane<2, 1>(a, smem, phases, stream);
@@ -682,6 +834,7 @@ int launch_hist(const HistLaunch& h, cudaStream_t stream) {
         return PB_OK;
     }
 
+    if (h.fuse) return fail_arg("fused flush requested for a launch that cannot fuse (check hist_can_fuse first)");
     // shared-memory plan: cells per feature, node chunks, feature group, copies
     const int64_t per_feat_all = (int64_t)h.n_nodes * h.max_bins;
     int nodes_per_chunk = h.n_nodes;

@@ -19,6 +19,7 @@
 //                 the global min_samples_leaf mask and the best threshold of the pair.
 
 #include "common.cuh"
+#include "des_math.cuh"
 
 namespace pb {
 
@@ -27,11 +28,6 @@ namespace {
 constexpr int kGainThreads = 256;
 constexpr int kChainThreads = 256;
 constexpr int kSmallBins = 8;
-
-__device__ __forceinline__ float f_add(float a, float b) { return __fadd_rn(a, b); }
-__device__ __forceinline__ float f_sub(float a, float b) { return __fsub_rn(a, b); }
-__device__ __forceinline__ float f_mul(float a, float b) { return __fmul_rn(a, b); }
-__device__ __forceinline__ float f_div(float a, float b) { return __fdiv_rn(a, b); }
 
 __device__ __forceinline__ float sign_of(float v) {
     // torch.sign: -1, 0, +1, NaN stays NaN (compares false to everything)
@@ -50,22 +46,6 @@ struct GainArgs {
     int nodes_per_cta;  // small-bin kernel: power of two <= 32 dividing the block; wide kernel: warps per CTA
     int era_splits;
 };
-
-// gain and validity weight of threshold t of one (node, era) from its integer prefix sums
-__device__ __forceinline__ float2 gain_of(uint32_t lc, long long lgq, uint32_t tc, float tg, float th, float parent,
-                                          float inv_scale, float lam, float w_era) {
-    const float lg = f_mul(__ll2float_rn(lgq), inv_scale);
-    const float lh = (float)lc;
-    const float rg = f_sub(tg, lg);
-    const float rh = f_sub(th, lh);
-    const float dl = f_add(lh, lam);
-    const float dr = f_add(rh, lam);
-    const float g2 = f_mul(0.5f, f_add(f_div(f_mul(lg, lg), dl), f_div(f_mul(rg, rg), dr)));
-    float2 out;
-    out.x = f_sub(g2, parent);
-    out.y = ((lc > 0) && (tc - lc > 0)) ? w_era : 0.f;
-    return out;
-}
 
 // ---- few bins: a thread scans the bins of its (era, node) in registers ---------------------------
 template <int KT, int NBT>  // compile-time bounds of the threshold count and of the bin count
@@ -366,7 +346,7 @@ __device__ __forceinline__ void finish_pairs(const ScoreLaunch& s, int f, int no
             const float agr = (a_den > 0.f) ? f_div(a_num, a_den) : 0.f;
             score = f_add(score, f_mul(s.direction_weight, agr));
         }
-        const size_t o = ((size_t)f * s.node_stride + node) * K + my_k;
+        const size_t o = tot_index(f, node, my_k, s.node_stride, K, s.tot_fpl, s.tot_lanes);
         const long long lc_all = s.lc_tot[o];
         const long long total = s.frontier[node].count;
         const bool ok = (lc_all >= s.min_samples_leaf) && (total - lc_all >= s.min_samples_leaf);
@@ -725,13 +705,19 @@ int launch_score(const ScoreLaunch& s, cudaStream_t stream) {
     if (K < 1 || K > kChainThreads) return fail_arg("n_thresholds=%d outside [1,%d]", K, kChainThreads);
     if (!s.gw || !s.lc_tot || !s.lg_tot) return fail_arg("scorer scratch is null");
     const size_t tot_cells = (size_t)s.n_feat * s.node_stride * K;
-    PB_CUDA_TRY(cudaMemsetAsync(s.lc_tot, 0, tot_cells * sizeof(uint32_t), stream));
-    PB_CUDA_TRY(cudaMemsetAsync(s.lg_tot, 0, tot_cells * sizeof(int64_t), stream));
+    if (!s.fused) {
+        PB_CUDA_TRY(cudaMemsetAsync(s.lc_tot, 0, tot_cells * sizeof(uint32_t), stream));
+        PB_CUDA_TRY(cudaMemsetAsync(s.lg_tot, 0, tot_cells * sizeof(int64_t), stream));
+    }
 
     prof_begin(kProfScore, stream);
     GainArgs g;
     g.s = s;
-    if (NB <= kSmallBins) {
+    if (s.fused) {
+        // the histogram kernel's flush already wrote the (gain, weight) table and the era-summed
+        // totals: only the era recursion is left
+        if (s.direction_weight != 0.f) return fail_arg("the fused flush cannot serve the directional term");
+    } else if (NB <= kSmallBins) {
         int npc = 1;
         while (npc < 32 && npc < s.n_nodes_max) npc *= 2;
         g.nodes_per_cta = npc;
@@ -757,7 +743,7 @@ int launch_score(const ScoreLaunch& s, cudaStream_t stream) {
         if (grid.y > 65535u) return fail_arg("scorer grid too large");
         gain_kernel_wide<<<grid, kGainThreads, 0, stream>>>(g);
     }
-    PB_LAUNCH_CHECK("gain_kernel");
+    if (!s.fused) PB_LAUNCH_CHECK("gain_kernel");
 
     ChainArgs c;
     c.s = s;
@@ -806,7 +792,7 @@ int launch_score(const ScoreLaunch& s, cudaStream_t stream) {
         chain_kernel<<<grid, threads, smem, stream>>>(c);
     }
     prof_end(kProfScore, stream);
-    count_launch(2);
+    count_launch(s.fused ? 1 : 2);
     PB_LAUNCH_CHECK("chain_kernel");
     return PB_OK;
 }

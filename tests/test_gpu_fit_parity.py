@@ -274,9 +274,14 @@ def test_predict_generic_node_arrays_when_children_are_not_adjacent():
 
 
 def _check_scores(got, want, label):
-    """DES scores within 1e-5 relative.  A score is mean - lambda * std of per-era gains, so it can
-    cancel to far below the gains it is made of; such scores are held to 1e-5 of the largest score
-    of the fit instead, and their number is reported."""
+    """DES scores against the reference's: within 1e-5 relative, or within 1e-4 of the largest score
+    of the fit.  A per-era gain is the small difference of terms G^2 / (H + lambda) that are
+    thousands of times larger (a root era of 4 700 rows: terms of ~600, gains of ~0.05), and the
+    reference feeds it float32 sums taken row by row, whose rounding noise (~1e-7 of the terms)
+    therefore shows up at ~1e-4 of the gain.  The CUDA path takes the same sums exactly; that its
+    scores are the reference's arithmetic on exact sums is checked bit for bit in
+    ``test_fit_is_bit_identical_to_the_exact_sum_oracle``.  The number of scores that needed the
+    absolute term is printed."""
     got = np.asarray(got, np.float64)
     want = np.asarray(want, np.float64)
     finite = np.isfinite(want)
@@ -287,8 +292,37 @@ def _check_scores(got, want, label):
     rel_ok = np.abs(g - w) <= 1e-5 * np.abs(w)
     print(f"{label}: {w.size} scores, {int((~rel_ok).sum())} outside 1e-5 relative "
           f"(max abs diff there {np.abs(g - w)[~rel_ok].max() if (~rel_ok).any() else 0:.3g}, score scale {scale:.3g})")
-    np.testing.assert_allclose(g, w, rtol=1e-5, atol=1e-5 * scale)
+    np.testing.assert_allclose(g, w, rtol=1e-5, atol=1e-4 * scale)
     return int((~rel_ok).sum()), int(w.size)
+
+
+@pytest.mark.parametrize("name", list(cases.CASES) + ["config3_wide"])
+def test_fit_is_bit_identical_to_the_exact_sum_oracle(name):
+    """The oracle's ``exact_sums`` variant is the reference's algorithm with one change: gradient
+    sums are exact (the fixed-point gradients of the CUDA path) and rounded to float32 once,
+    instead of float32 sums in row order.  Everything downstream is the reference's float32 /
+    float64 arithmetic, operation by operation, so the CUDA path must agree with it in every bit:
+    tree structure, every split's DES score (float32), every leaf value (float64) and every
+    training prediction (float32)."""
+    X, y, era, cfg, rounds, Xh = {**cases.CASES, **cases.WIDE_CASES}[name]()
+    model = po.fit(X, y, era, po.OracleParams(exact_sums=True, **cfg), rounds, record_depths=True)
+    booster = _fit_gpu(X, y, era, cfg, rounds)
+    off_o, cols_o = flatten_oracle(model.trees)
+    off_g, cols_g = flatten_trees(booster.trees)
+    np.testing.assert_array_equal(off_g, off_o)
+    for k in ("feature", "threshold", "left", "right", "is_leaf"):
+        np.testing.assert_array_equal(cols_g[k], cols_o[k], err_msg=k)
+    np.testing.assert_array_equal(cols_g["value"].view(np.int64), cols_o["value"].astype(np.float64).view(np.int64))
+    rec = booster.split_records()
+    B = cfg["pack_size"]
+    want = model.depth_records
+    assert len(want) == rec["node"].shape[0]
+    np.testing.assert_array_equal(rec["node"], [r["node"] for r in want])
+    np.testing.assert_array_equal(rec["left_count"], [r["left_count"] for r in want])
+    np.testing.assert_array_equal(rec["score"].view(np.int32),
+                                  np.asarray([r["score"] for r in want], dtype=np.float32).view(np.int32))
+    np.testing.assert_array_equal(booster.train_predictions().view(np.int32), model.train_preds.view(np.int32))
+    np.testing.assert_array_equal(booster.predict(Xh).view(np.int32), model.predict(Xh).view(np.int32))
 
 
 @pytest.mark.parametrize("name", list(cases.CASES))
@@ -330,7 +364,46 @@ def test_wide_cases_match_reference(name):
         m = populated_leaves(np.array([0, off[t + 1] - off[t]]), {k: v[sl] for k, v in gcols.items()}, codes_train)
         for j in range(B):
             populated[off[t + j]: off[t + j + 1]] = m
-    n_abs = assert_values_close(cols["value"], gold["value"], gold["is_leaf"] & populated)
-    scale = np.abs(gold["pred_train_head"]).max() + 1e-12
+    leaves = gold["is_leaf"] & populated
+    n_abs = assert_values_close(cols["value"], gold["value"], leaves)
+    print(f"{name}: {int(leaves.sum())} leaf values, {n_abs} outside 1e-5 relative (within 1e-5 of the largest leaf value)")
+    # A prediction is tree_weight * (sum of one leaf value per tree): its tolerance is the leaf
+    # tolerance carried through that sum, 1e-5 of tree_weight * sum over trees of the largest |leaf|.
+    # (The reference adds up to 500 000 float32 gradients one after the other; the rounding noise of
+    # that sum alone is ~2e-5 of its value, so 1e-5 of each prediction is not attainable against it.)
+    per_tree = np.array([np.abs(gold["value"][off[t]: off[t + 1]][leaves[off[t]: off[t + 1]]]).max()
+                         for t in range(len(off) - 1)])
+    scale = float(gold["tree_weight"]) * float(per_tree.sum())
     np.testing.assert_allclose(booster.predict(X[:2048]), gold["pred_train_head"], rtol=1e-5, atol=1e-5 * scale)
     np.testing.assert_allclose(booster.train_predictions()[:2048], gold["pred_train_head"], rtol=1e-5, atol=1e-5 * scale)
+    # First-round leaf values against float64 arithmetic: with zero predictions the gradients are
+    # exactly -y, so the gradient sum of every node can be recomputed without summation noise.
+    # The CUDA path sums exactly in fixed point and rounds a node's total and its left child's sum
+    # to float32 once each; the right child's sum is their difference (packboost/booster.py:2103-2108),
+    # so a child's value may be off by the float32 rounding of those two numbers and no more.
+    t0 = {k: gold[k][off[0]: off[1]] for k in ("feature", "threshold", "left", "right", "is_leaf")}
+    from gpu_util import leaf_index
+    n0 = int(off[1] - off[0])
+    where = leaf_index(t0, codes_train)
+    lam = float(cfg.get("lambda_l2", 1e-6))
+    sums = np.bincount(where, weights=-y.astype(np.float64), minlength=n0)
+    cnts = np.bincount(where, minlength=n0).astype(np.float64)
+    parent = np.full(n0, -1)
+    for i in range(n0 - 1, -1, -1):            # children carry larger ids than their parent
+        if not t0["is_leaf"][i]:
+            l, r = int(t0["left"][i]), int(t0["right"][i])
+            sums[i] = sums[l] + sums[r]
+            cnts[i] = cnts[l] + cnts[r]
+            parent[l] = parent[r] = i
+    hit = (cnts > 0) & t0["is_leaf"] & (parent >= 0)
+    idx = np.flatnonzero(hit)
+    sib = np.where(t0["left"][parent[idx]] == idx, t0["right"][parent[idx]], t0["left"][parent[idx]])
+    exact = -sums[idx] / (cnts[idx] + lam)
+    eps = 2.0 ** -23
+    bound = eps * (np.abs(sums[parent[idx]]) + np.abs(sums[sib]) + np.abs(sums[idx])) / (cnts[idx] + lam) + 1e-7 * np.abs(exact)
+    # (plus the fixed-point quantum of a gradient, 2^-24 of the largest one, as a random walk over the rows)
+    bound += 2.0 ** -24 * float(np.abs(y).max()) * (np.sqrt(cnts[parent[idx]]) + np.sqrt(cnts[sib]) + np.sqrt(cnts[idx])) / (cnts[idx] + lam)
+    got0 = cols["value"][off[0]: off[1]][idx]
+    worst = np.max(np.abs(got0 - exact) / bound)
+    print(f"{name}: first-round leaves vs float64: worst error / float32 rounding bound = {worst:.3f}")
+    assert worst <= 1.0
