@@ -522,7 +522,15 @@ def find_splits(
                 a_num = a_num + w_full * agree
                 a_den = a_den + w_full
             lc_all = lc_all + lc
-        std = torch.sqrt(torch.clamp_min(m2 / torch.clamp_min(wsum, 1e-12), 0.0))
+        var = torch.clamp_min(m2 / torch.clamp_min(wsum, 1e-12), 0.0)
+        if fx is not None:
+            # torch's vectorised CPU square root is not correctly rounded (torch 2.11, AVX-512 build:
+            # one unit in the last place off for ~0.3 % of inputs); the exact variant takes the IEEE
+            # square root, as the CUDA path does
+            with np.errstate(invalid="ignore"):
+                std = torch.from_numpy(np.sqrt(var.numpy()))
+        else:
+            std = torch.sqrt(var)
         score = mean - lam_dro * std
         if use_dir:
             agr = torch.zeros_like(a_num)
@@ -550,6 +558,8 @@ def find_splits(
                 "features": fblock.clone(), "counts": cnt, "grad_hist": gh,
                 "score": s_nbk.clone(), "left_count": lc_all.permute(1, 0, 2).clone(),
                 "sel": sel.clone(), "K": K,
+                "mean": mean.permute(1, 0, 2).clone(), "m2": m2.permute(1, 0, 2).clone(),
+                "wsum": wsum.permute(1, 0, 2).clone(),
             })
         if not torch.any(has):
             continue
@@ -623,6 +633,7 @@ class OracleModel:
     depth_records: list[dict]
     round_seconds: list[float]
     wide: bool = False
+    trace: dict = field(default_factory=dict)
 
     def predict(self, X: np.ndarray) -> np.ndarray:
         """``PackBoost.predict`` on the CPU route (``booster.py:658-712``)."""
@@ -673,9 +684,11 @@ def fit(
     num_rounds: int,
     *,
     record_depths: bool = False,
+    trace_at: tuple[int, int] | None = None,
 ) -> OracleModel:
     """Squared-loss boosting rounds (``booster.py:375-656`` without eval sets
-    and metric logging)."""
+    and metric logging).  ``trace_at=(round, depth)`` keeps the intermediate tensors of that one
+    frontier call (see ``find_splits``) in ``model.trace`` for kernel-level parity tests."""
     from time import perf_counter
 
     Xn = np.asarray(X)
@@ -710,6 +723,7 @@ def fit(
     lr32 = float(p.learning_rate)
     gq_bits = fixed_point_bits(int(np.bincount(era_codes.astype(np.int64)).max())) if N else 30
     trees: list[dict[str, np.ndarray]] = []
+    kept_trace: dict = {}
     depth_records: list[dict] = []
     round_seconds: list[float] = []
 
@@ -741,8 +755,13 @@ def fit(
                 if not active:
                     break
                 subset = sample_features(rng, F, p.layer_feature_fraction)
+                tr = {} if trace_at == (rnd, depth) else None
                 splits = find_splits([a[1] for a in active], [a[2] for a in active],
-                                     grad, hess, codes, subset, E, p, fx=fx)
+                                     grad, hess, codes, subset, E, p, trace=tr, fx=fx)
+                if tr is not None:
+                    tr["subset"] = subset.clone()
+                    tr["node_ids"] = [a[0] for a in active]
+                    kept_trace.update(tr)
                 nxt: list[tuple[int, torch.Tensor, torch.Tensor]] = []
                 for (nid, rows, eras_r), dec in zip(active, splits):
                     if dec is None:
@@ -788,7 +807,7 @@ def fit(
 
     return OracleModel(params=p, trees=trees, bin_edges=edges, tree_weight=lr32,
                        train_preds=preds.numpy().copy(), depth_records=depth_records,
-                       round_seconds=round_seconds, wide=wide)
+                       round_seconds=round_seconds, wide=wide, trace=kept_trace)
 
 
 def near_tie_gaps(X, y, era, p: OracleParams, num_rounds: int) -> np.ndarray:

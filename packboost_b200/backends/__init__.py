@@ -71,6 +71,7 @@ _PROTOS: dict[str, tuple[Any, list[Any]]] = {
     "pb_launch_count": (i64, []),
     "pb_bin_pack_f32": (C.c_int, [vp, i64, i64, i64, vp, i64, i64, vp, vp, i64, i64, vp]),
     "pb_pack_codes_u8": (C.c_int, [vp, i64, i64, i64, vp, vp, i64, i64, vp]),
+    "pb_copy_columns_h2d": (C.c_int, [vp, vp, i64, i64, i64, i64, vp]),
     "pb_pack_rows": (C.c_int, [vp, i64, i64, i64, vp, i64, i64, vp, i64, i64, vp]),
     "pb_train_state_bytes": (i64, []),
     "pb_ctl_bytes": (i64, []),

@@ -43,7 +43,7 @@ import torch
 from . import backends as B
 from .config import PackBoostConfig
 from .forest import validate_forest
-from .sharding import choose_replicated, dealt_part, feature_map, local_part
+from .sharding import agree_all, block_size, choose_replicated, dealt_part, feature_map, local_part, owned_range
 from .data import (BinningResult, PackedMatrix, PackedRows, code_bits_for, detect_prebinned, pack_feature_major,
                    pack_row_major, quantile_edges_device)
 
@@ -312,7 +312,7 @@ class _DeviceTrainer:
             if self.replicated and self.world > 1:
                 rows, pos = dealt_part(s, self.rank, self.world)
             else:
-                rows, pos = local_part(s, self.rank, self.world)
+                rows, pos = local_part(s, self.rank, self.world, self.F)
             n_local.append(int(pos.shape[0]))
             fh[d, 1, : pos.shape[0]] = torch.from_numpy(rows)
             fh[d, 2, : pos.shape[0]] = torch.from_numpy(pos)
@@ -483,6 +483,7 @@ class PackBoost:
         self._fit_ctx: dict | None = None
         self._eval_states: list = []
         self._last_n_ctx: list[int] = []
+        self._round_depths: list[int] = []   # depths with live nodes (= feature draws consumed) per round
         self._split_log: list[np.ndarray] = []
         self._pending_log = None
         self._predrawn = None
@@ -580,6 +581,14 @@ class PackBoost:
             is_binned = detect_prebinned(X_np, cfg.max_bins)
         if bool(cfg.prebinned) and not is_binned:
             raise ValueError("prebinned=True requires X to contain integer bins within [0, max_bins).")
+        rank, world = 0, 1
+        if torch.distributed.is_available() and torch.distributed.is_initialized():
+            rank, world = torch.distributed.get_rank(), torch.distributed.get_world_size()
+        # With several GPUs every rank histograms and scores only a share of the sampled features,
+        # and brings to its device only the strip of columns it owns (a contiguous block of
+        # ceil(F / world) features).
+        c0, c1 = owned_range(F, rank, world)
+        blk = block_size(F, world)
         if is_binned:
             edges = None
             self._binner = BinningResult(bins=None, bin_edges=None, prebinned=True)
@@ -589,38 +598,50 @@ class PackBoost:
                 X_src = X_np if X_np.dtype in (np.uint8, np.int8) else X_np.astype(np.uint8)
                 X_src = X_src.view(np.uint8)
         else:
-            if on_device:
-                X_src = X_np.to(torch.float32)
-                edges = quantile_edges_device(X_src, cfg.max_bins)
+            X_src = X_np.to(torch.float32) if on_device else X_np.astype(np.float32, copy=False)
+            if world > 1:
+                # each rank sorts its own columns; the edge tables are exchanged
+                own = np.zeros((cfg.max_bins - 1, blk), dtype=np.float32)
+                if c1 > c0:
+                    own[:, : c1 - c0] = quantile_edges_device(X_src[:, c0:c1], cfg.max_bins)
+                parts = torch.empty((world, cfg.max_bins - 1, blk), dtype=torch.float32, device=self._device)
+                torch.distributed.all_gather_into_tensor(parts, torch.from_numpy(own).to(self._device))
+                edges = np.ascontiguousarray(parts.permute(1, 0, 2).reshape(cfg.max_bins - 1, world * blk)[:, :F].cpu().numpy())
             else:
-                X_src = X_np.astype(np.float32, copy=False)
                 edges = quantile_edges_device(X_src, cfg.max_bins)
             self._binner = BinningResult(bins=None, bin_edges=edges, prebinned=False)
 
-        rank, world = 0, 1
-        if torch.distributed.is_available() and torch.distributed.is_initialized():
-            rank, world = torch.distributed.get_rank(), torch.distributed.get_world_size()
-        # With several GPUs every rank histograms and scores only the features it owns
-        # (feature % world == rank).  When the whole packed matrix fits comfortably in one GPU's
-        # memory it is kept on every rank anyway: each rank can then route rows itself and the
-        # per-depth go-left bitmask exchange disappears (one all-reduce per depth instead of two).
-        # PACKBOOST_SHARD_CODES=1 forces the memory-sharded layout.
-        # The choice is agreed by all ranks (their GPUs may have different amounts of free memory,
-        # and the two layouts issue different collectives).
+        # When the whole packed matrix fits comfortably in one GPU's memory it is kept on every rank
+        # anyway (each rank packs its strip, an all-gather over NVLink completes the copies): each
+        # rank can then route rows itself and the per-depth go-left bitmask exchange disappears (one
+        # exchange per depth instead of two).  PACKBOOST_SHARD_CODES=1 forces the memory-sharded
+        # layout.  The choice is agreed by all ranks (their GPUs may have different amounts of free
+        # memory, and the two layouts issue different collectives).
         replicate = False
+        bits = code_bits_for(cfg.max_bins)
         if world > 1:
-            bits = code_bits_for(cfg.max_bins)
             free, _tot = torch.cuda.mem_get_info(self._device)
             replicate = choose_replicated(N * F * bits // 8, free, world,
                                           os.getenv("PACKBOOST_SHARD_CODES") == "1", self._device)
         if world > 1 and not replicate:
             feat_local = feature_map(F, rank, world)
+            matrix = pack_feature_major(X_src, edges, cfg.max_bins, row_order=order, feature_map=feat_local,
+                                        n_features_local=c1 - c0, validate_codes=validate_on_device,
+                                        columns=(c0, c1), defer_validation=True)
+        elif world > 1:
+            feat_local = feature_map(F, 0, 1)
+            matrix = PackedMatrix(N, blk * world, bits, self._device)   # feature rows past F stay empty
+            pack_feature_major(X_src, edges, cfg.max_bins, row_order=order, validate_codes=validate_on_device,
+                               columns=(c0, c1), out=matrix, defer_validation=True)
+            slabs = matrix.codes.view(world, -1)
+            torch.distributed.all_gather_into_tensor(matrix.codes.view(-1), slabs[rank].clone())
+            matrix.n_features_local = F
         else:
             feat_local = feature_map(F, 0, 1)
-        n_local = int((feat_local >= 0).sum())
-        matrix = pack_feature_major(X_src, edges, cfg.max_bins, row_order=order,
-                                    feature_map=feat_local if (world > 1 and not replicate) else None,
-                                    n_features_local=n_local, validate_codes=validate_on_device)
+            matrix = pack_feature_major(X_src, edges, cfg.max_bins, row_order=order, validate_codes=validate_on_device,
+                                        defer_validation=True)
+        if validate_on_device and not agree_all(matrix.max_code < min(cfg.max_bins, 128), self._device):
+            raise ValueError("prebinned=True requires X to contain integer bins within [0, max_bins).")
         y_sorted = y_np if order is None else y_np[order]
         self._trainer = _DeviceTrainer(cfg, matrix, y_sorted, era_offsets, F, feat_local, rank, world,
                                        replicated=replicate)
@@ -628,6 +649,7 @@ class PackBoost:
         self._fit_ctx = {"era_sorted": era_sorted, "y_sorted": y_sorted, "F": F}
 
         self._depth_logs = []
+        self._round_depths = []
         self._split_log = []
         self._round_metrics = []
         self._trees = []
@@ -719,6 +741,7 @@ class PackBoost:
         n_ctx = [int(v) for v in head["n_ctx"][: D + 1]]
         self._last_n_ctx = n_ctx
         used = next((d for d in range(D) if n_ctx[d] == 0), D)
+        self._round_depths.append(used)
         if used < D:
             self._rng.set_state(state0)
             for _ in range(used):

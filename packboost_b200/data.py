@@ -133,6 +133,7 @@ class PackedMatrix:
         self.code_bits = int(code_bits)
         self.pitch = (self.rows_padded * code_bits // 8 + 127) // 128 * 128
         self.n_features_local = int(n_features_local)
+        self.max_code = 0   # largest pre-binned code seen while packing (when validation was asked for)
         self.codes = torch.zeros((max(self.n_features_local, 1), self.pitch), dtype=torch.uint8, device=device)
 
     def unpack(self) -> torch.Tensor:
@@ -145,6 +146,19 @@ class PackedMatrix:
         return full[: self.n_features_local, : self.n_rows].contiguous()
 
 
+_STAGE: dict = {}
+
+
+def _staging(nbytes: int) -> list[tuple[torch.Tensor, torch.cuda.Event]]:
+    """Two reusable page-locked buffers (and the events that guard their reuse) for bringing
+    pageable host arrays to the device chunk by chunk."""
+    have = _STAGE.get("bufs")
+    if have is None or have[0][0].numel() < nbytes:
+        have = [(torch.empty(nbytes, dtype=torch.uint8).pin_memory(), torch.cuda.Event()) for _ in range(2)]
+        _STAGE["bufs"] = have
+    return have
+
+
 def pack_feature_major(
     X: np.ndarray | torch.Tensor,
     edges: np.ndarray | None,
@@ -154,55 +168,105 @@ def pack_feature_major(
     feature_map: np.ndarray | None = None,
     n_features_local: int | None = None,
     validate_codes: bool = False,
+    columns: tuple[int, int] | None = None,
+    out: "PackedMatrix | None" = None,
+    defer_validation: bool = False,
 ) -> PackedMatrix:
-    """Bin (when ``edges`` is given) and pack host data into a device ``PackedMatrix``.
+    """Bin (when ``edges`` is given) and pack host or device data into a device ``PackedMatrix``.
 
     ``row_order`` lists source rows in destination order (era-sorted rows);
     ``feature_map[j]`` is the destination feature row of column ``j`` or -1.
+    ``columns=(c0, c1)`` restricts the work to that strip of columns: only those bytes travel to
+    the device (one strided copy per chunk from page-locked memory) and ``feature_map`` /
+    ``edges`` still refer to the full width.  ``out`` packs into an existing matrix.
     ``validate_codes`` checks on the device that pre-binned input stays below ``max_bins``
-    (negative int8 values show up as codes >= 128) and raises ``ValueError`` otherwise.
+    (negative int8 values show up as codes >= 128) and raises ``ValueError`` otherwise; with
+    ``defer_validation`` the largest code seen is only recorded in ``PackedMatrix.max_code`` (several
+    ranks must agree before any of them raises).
+
+    Host input reaches the device asynchronously: a page-locked tensor is read in place, a pageable
+    array goes through two reusable page-locked staging buffers so that the host copy of chunk
+    ``i + 1`` overlaps the transfer and the packing of chunk ``i``.
     """
     dev = _device()
     lib = B.lib()
     n_rows, n_feat = X.shape
     bits = code_bits_for(max_bins)
+    c0, c1 = (0, n_feat) if columns is None else (int(columns[0]), int(columns[1]))
+    width = c1 - c0
     n_local = n_feat if n_features_local is None else n_features_local
-    pm = PackedMatrix(n_rows, n_local, bits, dev)
-    fmap_t = None
-    if feature_map is not None:
-        fmap_t = torch.from_numpy(np.ascontiguousarray(feature_map, dtype=np.int32)).to(dev)
+    pm = out if out is not None else PackedMatrix(n_rows, n_local, bits, dev)
+    if width <= 0 or n_rows == 0:
+        torch.cuda.current_stream().synchronize()
+        return pm
+    fmap = np.arange(n_feat, dtype=np.int32) if feature_map is None else np.ascontiguousarray(feature_map, dtype=np.int32)
+    fmap_t = torch.from_numpy(np.ascontiguousarray(fmap[c0:c1])).to(dev)
     is_f32 = edges is not None
-    edges_t = torch.from_numpy(np.ascontiguousarray(edges, dtype=np.float32)).to(dev) if is_f32 else None
+    edges_t = (torch.from_numpy(np.ascontiguousarray(np.asarray(edges, dtype=np.float32)[:, c0:c1])).to(dev)
+               if is_f32 else None)
     stream = torch.cuda.current_stream().cuda_stream
-    src_dtype = np.float32 if is_f32 else np.uint8
     is_tensor = isinstance(X, torch.Tensor)
-    order_t = None
-    if is_tensor and row_order is not None:
-        order_t = torch.from_numpy(np.ascontiguousarray(row_order, dtype=np.int64)).to(X.device)
+    on_device = is_tensor and X.is_cuda
+    pinned = is_tensor and (not X.is_cuda) and X.is_pinned() and X.is_contiguous()
     want = torch.float32 if is_f32 else torch.uint8
+    item = 4 if is_f32 else 1
+    np_want = np.float32 if is_f32 else np.uint8
+    order_t = None
+    if row_order is not None and is_tensor:
+        order_t = torch.from_numpy(np.ascontiguousarray(row_order, dtype=np.int64)).to(X.device)
     top = torch.zeros((), dtype=torch.uint8, device=dev)
-    for a, b in _row_chunks(n_rows, n_feat * (4 if is_f32 else 1)):
-        if is_tensor:
-            # device tensors are sliced in place; pinned host tensors are copied asynchronously
+    chunks = list(_row_chunks(n_rows, width * item))
+    stage = None
+    for i, (a, b) in enumerate(chunks):
+        n = b - a
+        if on_device:
             rows = X[a:b] if order_t is None else X.index_select(0, order_t[a:b])
+            rows = rows[:, c0:c1]
             if rows.dtype == torch.int8 and not is_f32:
                 rows = rows.view(torch.uint8)
-            chunk = rows.to(device=dev, dtype=want, non_blocking=True).contiguous()
+            chunk = rows.to(dtype=want).contiguous()
+        elif pinned and order_t is None and X.dtype in ((torch.float32,) if is_f32 else (torch.uint8, torch.int8)):
+            # page-locked source of the right type: the strip is read where it lies
+            chunk = torch.empty((n, width), dtype=want, device=dev)
+            B.check(lib.pb_copy_columns_h2d(chunk.data_ptr(), X.data_ptr() + a * n_feat * item, n, n_feat * item,
+                                            c0 * item, width * item, stream))
         else:
-            rows = X[a:b] if row_order is None else X[row_order[a:b]]
-            chunk = torch.from_numpy(np.ascontiguousarray(rows, dtype=src_dtype)).to(dev, non_blocking=False)
+            # pageable (or gathered / converted) source: through a page-locked staging buffer
+            if stage is None:
+                stage = _staging((chunks[0][1] - chunks[0][0]) * width * item)
+            buf, ev = stage[i % 2]
+            ev.synchronize()                       # the transfer that last used this buffer is done
+            dst = buf[: n * width * item].view(want).view(n, width)
+            if is_tensor:
+                rows = X[a:b] if order_t is None else X.index_select(0, order_t[a:b])
+                rows = rows[:, c0:c1]
+                if rows.dtype == torch.int8 and not is_f32:
+                    rows = rows.view(torch.uint8)
+                dst.copy_(rows)
+            else:
+                rows = X[a:b] if row_order is None else X[row_order[a:b]]
+                rows = rows[:, c0:c1]
+                if rows.dtype == np.int8 and not is_f32:
+                    rows = rows.view(np.uint8)
+                if rows.dtype == np_want and rows.flags.writeable:
+                    dst.copy_(torch.from_numpy(rows))   # multi-threaded strided host copy
+                else:
+                    np.copyto(dst.numpy(), rows, casting="unsafe")
+            chunk = dst.to(dev, non_blocking=True)
+            ev.record()
         if validate_codes and not is_f32:
             top = torch.maximum(top, chunk.max())
         if is_f32:
-            B.check(lib.pb_bin_pack_f32(chunk.data_ptr(), b - a, n_feat, a, edges_t.data_ptr(), edges_t.shape[0],
-                                        max_bins, B._ptr(fmap_t), pm.codes.data_ptr(), pm.pitch, bits, stream))
+            B.check(lib.pb_bin_pack_f32(chunk.data_ptr(), n, width, a, edges_t.data_ptr(), edges_t.shape[0],
+                                        max_bins, fmap_t.data_ptr(), pm.codes.data_ptr(), pm.pitch, bits, stream))
         else:
-            B.check(lib.pb_pack_codes_u8(chunk.data_ptr(), b - a, n_feat, a, B._ptr(fmap_t), pm.codes.data_ptr(),
+            B.check(lib.pb_pack_codes_u8(chunk.data_ptr(), n, width, a, fmap_t.data_ptr(), pm.codes.data_ptr(),
                                          pm.pitch, bits, stream))
         # no synchronisation per chunk: the copy, the pack kernel and the release of `chunk` are
         # ordered on the current stream
     torch.cuda.current_stream().synchronize()
-    if validate_codes and int(top.item()) >= min(max_bins, 128):
+    pm.max_code = max(pm.max_code, int(top.item())) if validate_codes else pm.max_code
+    if validate_codes and not defer_validation and pm.max_code >= min(max_bins, 128):
         raise ValueError("prebinned=True requires X to contain integer bins within [0, max_bins).")
     return pm
 

@@ -1,8 +1,11 @@
 """Feature sharding across the GPUs of one node (one process per GPU).
 
-Feature ``f`` lives on rank ``f % world`` at local row ``f // world``.  Every
-rank keeps the row state (targets, predictions, gradients, row -> node map)
-replicated and runs the same host control flow with the same seed, so the
+Rank ``r`` of ``world`` owns the contiguous block of features
+``[r * block, min(F, (r + 1) * block))`` with ``block = ceil(F / world)``; feature ``f`` sits
+at local row ``f - r * block``.  (Contiguous blocks, not a modulo deal, so that a rank's columns
+are one strip of every row of the caller's row-major matrix and can be brought to the device
+with a single strided copy.)  Every rank keeps the row state (targets, predictions, gradients,
+row -> node map) replicated and runs the same host control flow with the same seed, so the
 per-depth feature subsets agree without communication.
 """
 
@@ -11,22 +14,39 @@ from __future__ import annotations
 import numpy as np
 
 
+def block_size(n_features: int, world: int) -> int:
+    return (int(n_features) + max(world, 1) - 1) // max(world, 1)
+
+
+def owned_range(n_features: int, rank: int, world: int) -> tuple[int, int]:
+    """Half-open range of the global feature ids rank ``rank`` holds."""
+    if world <= 1:
+        return 0, int(n_features)
+    blk = block_size(n_features, world)
+    return min(n_features, rank * blk), min(n_features, (rank + 1) * blk)
+
+
 def feature_map(n_features: int, rank: int, world: int) -> np.ndarray:
     """``int32 [F]``: local feature row of each global feature, -1 when another rank holds it."""
     f = np.arange(n_features, dtype=np.int64)
     if world <= 1:
         return f.astype(np.int32)
-    return np.where(f % world == rank, f // world, -1).astype(np.int32)
+    c0, c1 = owned_range(n_features, rank, world)
+    return np.where((f >= c0) & (f < c1), f - c0, -1).astype(np.int32)
 
 
-def local_part(subset: np.ndarray, rank: int, world: int) -> tuple[np.ndarray, np.ndarray]:
+def local_part(subset: np.ndarray, rank: int, world: int, n_features: int | None = None) -> tuple[np.ndarray, np.ndarray]:
     """For a sampled feature list: ``(local feature rows, positions in the sampled order)`` of the
-    features this rank holds, both int32, positions ascending."""
+    features this rank holds, both int32, positions ascending.  ``n_features`` (the width of the
+    data set) is needed when ``world > 1``."""
     subset = np.asarray(subset)
     if world <= 1:
         return subset.astype(np.int32), np.arange(subset.shape[0], dtype=np.int32)
-    pos = np.nonzero(subset % world == rank)[0].astype(np.int32)
-    return (subset[pos] // world).astype(np.int32), pos
+    if n_features is None:
+        raise ValueError("n_features is required to locate a rank's block of features")
+    c0, c1 = owned_range(n_features, rank, world)
+    pos = np.nonzero((subset >= c0) & (subset < c1))[0].astype(np.int32)
+    return (subset[pos] - c0).astype(np.int32), pos
 
 
 def dealt_part(subset: np.ndarray, rank: int, world: int) -> tuple[np.ndarray, np.ndarray]:

@@ -90,3 +90,58 @@ def rows_avoiding_empty_leaves(off, cols, populated, codes):
         tree = {k: v[sl] for k, v in cols.items()}
         ok &= populated[off[i] + leaf_index(tree, codes)]
     return ok
+
+
+def gpu_candidates_at(X, y, era, cfg, round_idx, depth):
+    """Run ``round_idx`` whole rounds through the booster, then the phases of the next round up to
+    the histogram + score pass of ``depth``, and return that pass's candidate table as a structured
+    array ``[sampled position][frontier node]`` (score, k, left_count, flags, left_gq), the sampled
+    feature list and the number of frontier nodes."""
+    import os
+    os.environ["PACKBOOST_RUN_AHEAD"] = "0"
+    try:
+        booster = PackBoost(PackBoostConfig(device="cuda", **cfg))
+        booster._start(X, y, era)
+        for r in range(round_idx):
+            booster._boost_one_round(r, round_idx + 1)
+        booster._drain()
+        booster._predrawn = None
+    finally:
+        del os.environ["PACKBOOST_RUN_AHEAD"]
+    tr = booster._trainer
+    # the generator was advanced past the next round's draws by the look-ahead: rewind to the state
+    # the rounds so far leave behind by replaying them on a fresh generator
+    F, D, k = tr.F, tr.D, tr.n_sampled()
+    rng = torch.Generator(device="cpu")
+    rng.manual_seed(int(cfg["random_state"]))
+    for n_ctx in booster._round_depths:
+        for _ in range(n_ctx):
+            torch.randperm(F, generator=rng)
+    subsets = [torch.randperm(F, generator=rng)[:k].numpy().astype(np.int32) for _ in range(D)]
+    lib, st = tr.lib, C.byref(tr.st)
+    stream = torch.cuda.current_stream().cuda_stream
+    fh = torch.zeros((D, 3, max(k, 1)), dtype=torch.int32)
+    for d in range(D):
+        fh[d, 0, :k] = torch.from_numpy(subsets[d])
+        fh[d, 1, :k] = torch.from_numpy(subsets[d])
+        fh[d, 2, :k] = torch.arange(k, dtype=torch.int32)
+    tr.feat_dev.copy_(fh)
+    B.check(lib.pb_round_begin(st, 1 if round_idx > 0 else 0, stream))
+    for d in range(depth + 1):
+        B.check(lib.pb_depth_hist_score(st, d, tr.feat_dev[d, 1].data_ptr(), tr.feat_dev[d, 2].data_ptr(), k, k, stream))
+        if d < depth:
+            B.check(lib.pb_depth_select(st, d, tr.feat_dev[d, 0].data_ptr(), k, stream))
+            B.check(lib.pb_depth_partition(st, d, stream))
+    ptr, nbytes = C.c_void_p(), C.c_int64()
+    B.check(lib.pb_candidates_buffer(st, depth, k, C.byref(ptr), C.byref(nbytes)))
+    off = ptr.value - tr.workspace.data_ptr()
+    torch.cuda.synchronize()
+    raw = tr.workspace[off: off + nbytes.value].cpu().numpy()
+    cand_dt = np.dtype([("score", "<f4"), ("k", "<i4"), ("left_count", "<u4"), ("flags", "<u4"), ("left_gq", "<i8")])
+    table = raw.view(cand_dt).reshape(k, 1 << depth)
+    head = tr.ctl.cpu().numpy()
+    n_ctx = int(np.frombuffer(head[:256].tobytes(), dtype=np.int32, offset=24, count=PB_N_CTX)[depth])
+    return table, subsets[depth], n_ctx
+
+
+PB_N_CTX = 14  # entries of the per-depth frontier counts in the control block head

@@ -200,3 +200,53 @@ def test_device_quantile_edges_equal_host_quantile_edges():
         want = quantile_edges(X, nb)
         assert np.array_equal(quantile_edges_device(X, nb), want)
         assert np.array_equal(quantile_edges_device(torch.from_numpy(X).cuda(), nb), want)
+
+
+def _oracle_candidates(trace, K):
+    """Best threshold of every (sampled position, frontier node) from the oracle's per-candidate
+    scores: highest score, then largest left count, then largest threshold index
+    (packboost/booster.py:1912-1919 restricted to one feature)."""
+    out = {}
+    pos = 0
+    for blk in trace["blocks"]:
+        score = blk["score"].numpy()          # [node, feature in block, K], -inf where min_samples_leaf fails
+        lc = blk["left_count"].numpy()
+        for j in range(score.shape[1]):
+            for n in range(score.shape[0]):
+                s, c = score[n, j], lc[n, j]
+                best = None
+                for k in range(K):
+                    if np.isnan(s[k]):
+                        continue
+                    if best is None or s[k] > s[best] or (s[k] == s[best] and c[k] >= c[best]):
+                        best = k
+                out[(pos + j, n)] = (np.float32(s[best]), best, int(c[best]))
+        pos += score.shape[1]
+    return out
+
+
+@pytest.mark.parametrize("case,round_idx,depth", [("prebinned5", 0, 0), ("prebinned5", 1, 3), ("prebinned5", 3, 4),
+                                                  ("config1", 0, 2), ("config1", 4, 4), ("ragged_eras", 2, 3),
+                                                  ("kcuts_even", 1, 2), ("interleaved", 2, 3)])
+def test_scorer_candidates_match_oracle_bit_for_bit(case, round_idx, depth):
+    """Kernel-level check of the histogram + DES scorer pass: the candidate table it writes (best
+    threshold of every sampled feature at every frontier node: float32 score, threshold index,
+    left count) against the oracle's per-candidate scores in its exact-sum variant, for frontiers
+    of one to sixteen nodes in the first and in later rounds."""
+    import cases
+    from gpu_util import gpu_candidates_at
+    X, y, era, cfg, rounds, _ = cases.CASES[case]()
+    table, subset, n_ctx = gpu_candidates_at(X, y, era, cfg, round_idx, depth)
+    model = po.fit(X, y, era, po.OracleParams(exact_sums=True, **cfg), round_idx + 1, trace_at=(round_idx, depth))
+    tr = model.trace
+    assert tr, "the oracle did not reach this frontier"
+    np.testing.assert_array_equal(tr["subset"].numpy(), subset)
+    K = tr["blocks"][0]["K"]
+    want = _oracle_candidates(tr, K)
+    assert n_ctx == len(tr["context_nodes"])
+    bad = []
+    for (p, n), (s, k, c) in want.items():
+        g = table[p, n]
+        if (np.float32(g["score"]).view(np.int32) != s.view(np.int32)) or int(g["k"]) != k or int(g["left_count"]) != c:
+            bad.append((p, n, float(g["score"]), int(g["k"]), int(g["left_count"]), float(s), k, c))
+    assert not bad, f"{len(bad)} of {len(want)} candidates differ, first: {bad[:5]}"

@@ -73,16 +73,22 @@ def test_feature_map_and_local_part_partition_the_features():
     for r in range(world):
         m = sharding.feature_map(F, r, world)
         own = np.nonzero(m >= 0)[0]
-        assert np.array_equal(m[own], own // world)
+        c0, c1 = sharding.owned_range(F, r, world)
+        assert np.array_equal(own, np.arange(c0, c1))          # one contiguous strip of columns
+        assert np.array_equal(m[own], own - c0)
+        assert c1 - c0 <= sharding.block_size(F, world)
         seen[own] += 1
     assert np.all(seen == 1)
     subset = np.random.default_rng(0).permutation(F)[:11].astype(np.int32)
     pos_all = []
     for r in range(world):
-        rows, pos = sharding.local_part(subset, r, world)
-        assert np.array_equal(rows, subset[pos] // world) and np.all(subset[pos] % world == r)
+        rows, pos = sharding.local_part(subset, r, world, F)
+        c0, c1 = sharding.owned_range(F, r, world)
+        assert np.array_equal(rows, subset[pos] - c0) and np.all((subset[pos] >= c0) & (subset[pos] < c1))
         pos_all.append(pos)
     assert np.array_equal(np.sort(np.concatenate(pos_all)), np.arange(11))
+    # more ranks than features: the surplus ranks hold nothing
+    assert [sharding.owned_range(3, r, 8) for r in range(8)] == [(0, 1), (1, 2), (2, 3)] + [(3, 3)] * 5
 
 
 def test_edges_from_sorted_columns_equal_numpy_quantile():
@@ -143,7 +149,7 @@ def _worker(rank, world, port, out):
     full = rng.integers(1, 1 << 30, size=(subset.shape[0], nodes, 6)).astype(np.int32)   # 24-byte records
     # each rank fills the records of the features it holds; the others stay zero
     table = np.zeros_like(full)
-    _, pos = sharding.local_part(subset, rank, world)
+    _, pos = sharding.local_part(subset, rank, world, F)
     table[pos] = full[pos]
     t = torch.from_numpy(table)
     dist.all_reduce(t, op=dist.ReduceOp.SUM)
@@ -152,7 +158,8 @@ def _worker(rank, world, port, out):
     node_of = rng.integers(0, nodes, size=n_rows)
     win_feat = subset[rng.integers(0, subset.shape[0], size=nodes)]
     go_left = rng.integers(0, 2, size=n_rows).astype(bool)
-    mine = (win_feat[node_of] % world == rank) & go_left
+    c0, c1 = sharding.owned_range(F, rank, world)
+    mine = (win_feat[node_of] >= c0) & (win_feat[node_of] < c1) & go_left
     bits = np.packbits(mine, bitorder="little")
     bits = np.pad(bits, (0, (-len(bits)) % 4)).view(np.int32).copy()
     tb = torch.from_numpy(bits)
