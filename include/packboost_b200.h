@@ -94,15 +94,6 @@ int pb_pack_codes_u8(const uint8_t* x, int64_t n_chunk, int64_t n_features, int6
                      const int32_t* feature_map, uint8_t* codes, int64_t pitch,
                      int64_t code_bits, void* stream);
 
-/* Host -> device copy of a strip of columns of a row-major host matrix: `n_rows` rows of
- * `width_bytes` bytes starting `col_offset_bytes` into each source row of `src_pitch_bytes`, packed
- * densely at `dst` (one strided DMA; asynchronous when the source is page-locked).  With the
- * features sharded over several devices each device brings over only the columns it owns instead
- * of the whole matrix (the reference is single-device and has no counterpart; its upload is the
- * `.to(device)` of packboost/booster.py:419-429). */
-int pb_copy_columns_h2d(void* dst, const void* src_host, int64_t n_rows, int64_t src_pitch_bytes,
-                        int64_t col_offset_bytes, int64_t width_bytes, void* stream);
-
 /* Row-major packing for the predictor: `out[row][pitch_row]`, 4-bit (two features per byte,
  * even feature in the low nibble) or 8-bit.  Float input is binned with `edges` first
  * (`edges == NULL`: input is uint8 bin ids). */
@@ -153,7 +144,10 @@ typedef struct pb_train_state {
     int64_t gq_bits;             /* |gq| <= 2^gq_bits */
     int64_t count_bits;          /* CB: rows of a histogram tile < 2^CB */
     int64_t lo_bits;             /* LB = 32 - 2*CB: low gradient bits kept beside the count */
-    int64_t reserved[3];
+    int64_t cut_mass;            /* 1: k_cuts with cut_selection="mass": the n_thresholds thresholds of a feature are
+                                    taken per depth at the quantiles of its bin masses over the frontier rows
+                                    (packboost/backends/cpu/frontier_cpu.cpp:59-109); thr_ids is then unused */
+    int64_t reserved[2];
 } pb_train_state;
 
 /* sizeof(pb_train_state), so that a binding can verify its mirror of the struct. */

@@ -63,6 +63,12 @@ class OracleParams:
     # after the sums is unchanged, so the CUDA path must reproduce this variant bit for bit; the
     # difference between the two variants is the reference's own summation noise.
     exact_sums: bool = False
+    # The reference's torch frontier raises for ``k_cuts > 0`` with ``cut_selection="mass"``
+    # (``booster.py:1940``); its compiled C++ split finder implements the policy
+    # (``backends/cpu/frontier_cpu.cpp:59-109``, thresholds per feature from the bin masses of all
+    # frontier rows).  With this switch the oracle takes the thresholds the C++ code would take and
+    # scores them with the torch frontier's arithmetic, instead of raising.
+    native_mass_cuts: bool = False
     # ``max_bins`` above 128 is refused by the reference (int8 storage,
     # ``packboost/booster.py:394-395``, ``packboost/data.py:47-48``).  The
     # widened oracle stores codes as int16 instead and is otherwise identical.
@@ -280,6 +286,54 @@ def mass_cuts(counts: torch.Tensor, k: int) -> torch.Tensor:
     return table
 
 
+def even_cuts_native(num_bins: int, k: int) -> list[int]:
+    """Evenly spaced thresholds as the reference's C++ split finder takes them
+    (``backends/cpu/frontier_cpu.cpp:35-57``): ``round(i * (T - 1) / (k - 1))``, half away from zero."""
+    import math
+    max_thr = max(1, num_bins - 1)
+    kk = max(1, min(k, max_thr))
+    if kk == 1:
+        return [0]
+    step = float(max_thr - 1) / float(kk - 1)
+    out = []
+    for i in range(kk):
+        v = i * step
+        idx = int(math.floor(v + 0.5)) if v >= 0 else -int(math.floor(-v + 0.5))
+        out.append(max(0, min(idx, max_thr - 1)))
+    out = sorted(set(out))
+    while len(out) < kk:
+        out.append(out[-1])
+    return out
+
+
+def mass_cuts_native(mass: np.ndarray, num_bins: int, k: int) -> list[int]:
+    """Thresholds at the count-mass quantiles of one feature as the reference's C++ split finder
+    takes them (``backends/cpu/frontier_cpu.cpp:59-109``); ``mass[b]`` is the number of frontier
+    rows (all nodes, all eras) with code ``b``."""
+    max_thr = max(1, num_bins - 1)
+    kk = max(1, min(k, max_thr))
+    total = int(np.sum(mass))
+    if total <= 0:
+        return even_cuts_native(num_bins, kk)
+    cdf = np.cumsum(np.asarray(mass, dtype=np.int64))
+    upper = float(total) * (1.0 - 1e-12)
+    out = []
+    for i in range(kk):
+        alpha = 0.0 if kk == 1 else float(i) / float(kk - 1)
+        target = upper * alpha
+        idx = len(cdf) - 1
+        for j in range(len(cdf)):                 # lower_bound: first entry not below the target
+            if not (float(cdf[j]) < target):
+                idx = j
+                break
+        out.append(max(0, min(idx - 1, max_thr - 1)))
+    out = sorted(set(out))
+    if len(out) < kk:
+        out = sorted(set(out) | set(even_cuts_native(num_bins, kk)))
+    out = out[:kk]
+    return [max(0, min(v, max_thr - 1)) for v in out]
+
+
 # --------------------------------------------------------------------------
 # frontier: histograms -> DES scores -> winners
 # --------------------------------------------------------------------------
@@ -460,7 +514,12 @@ def find_splits(
         k_user = int(p.k_cuts)
         use_k = 0 < k_user < full_T
         per_feat_thr = None
-        if use_k and p.cut_selection == "mass":
+        if use_k and p.cut_selection == "mass" and p.native_mass_cuts:
+            masses = cnt.sum(dim=(1, 2)).numpy()                   # [B, bins] over nodes and eras
+            rows_thr = [mass_cuts_native(masses[b], nb, k_user) for b in range(masses.shape[0])]
+            per_feat_thr = torch.tensor(rows_thr, dtype=torch.int64)
+            thr_ids = per_feat_thr[0]
+        elif use_k and p.cut_selection == "mass":
             # The reference computes this table but then fails while mapping the
             # in-block winner back to a threshold (booster.py:1940 raises
             # "Index tensor must have the same number of dimensions as input
@@ -473,6 +532,7 @@ def find_splits(
         K = int(thr_ids.shape[-1])
         Bb = Lc.shape[0]
         if per_feat_thr is not None:
+            K = int(per_feat_thr.shape[1])
             pick = per_feat_thr.unsqueeze(1).expand(Bb, Nn, K)
         else:
             pick = thr_ids.view(1, 1, K).expand(Bb, Nn, K)

@@ -58,7 +58,7 @@ class TrainState(C.Structure):
         ("preds", vp), ("gq", vp), ("slot", vp), ("leaf", vp), ("ctl", vp), ("workspace", vp),
         ("workspace_bytes", i64),
         ("max_era_rows", i64), ("hist_rows_per_tile", i64), ("gq_bits", i64), ("count_bits", i64),
-        ("lo_bits", i64), ("reserved", i64 * 3),
+        ("lo_bits", i64), ("cut_mass", i64), ("reserved", i64 * 2),
     ]
 
 
@@ -71,7 +71,6 @@ _PROTOS: dict[str, tuple[Any, list[Any]]] = {
     "pb_launch_count": (i64, []),
     "pb_bin_pack_f32": (C.c_int, [vp, i64, i64, i64, vp, i64, i64, vp, vp, i64, i64, vp]),
     "pb_pack_codes_u8": (C.c_int, [vp, i64, i64, i64, vp, vp, i64, i64, vp]),
-    "pb_copy_columns_h2d": (C.c_int, [vp, vp, i64, i64, i64, i64, vp]),
     "pb_pack_rows": (C.c_int, [vp, i64, i64, i64, vp, i64, i64, vp, i64, i64, vp]),
     "pb_train_state_bytes": (i64, []),
     "pb_ctl_bytes": (i64, []),

@@ -45,7 +45,7 @@ from .config import PackBoostConfig
 from .forest import validate_forest
 from .sharding import agree_all, block_size, choose_replicated, dealt_part, feature_map, local_part, owned_range
 from .data import (BinningResult, PackedMatrix, PackedRows, code_bits_for, detect_prebinned, pack_feature_major,
-                   pack_row_major, quantile_edges_device)
+                   pack_feature_major_distributed, pack_row_major, quantile_edges_device)
 
 # ------------------------------ tree containers ------------------------------
 
@@ -193,11 +193,15 @@ class _DeviceTrainer:
         self.E = int(era_offsets.shape[0] - 1)
         nb = int(cfg.max_bins)
         k_user = int(cfg.k_cuts)
+        self.cut_mass = False
         if 0 < k_user < nb - 1:
-            if cfg.cut_selection == "mass":
-                raise RuntimeError(
-                    "k_cuts with cut_selection='mass' is not supported: the reference torch frontier raises on it")
+            # "mass": per depth and feature, thresholds at the quantiles of the bin masses of the frontier
+            # rows (the policy of the reference's compiled split finder; its torch frontier raises on
+            # it); the evenly spaced ids below are what the device falls back to for an empty frontier
+            self.cut_mass = cfg.cut_selection == "mass"
             thr = even_cut_ids(nb, k_user)
+            if self.cut_mass and thr.shape[0] != k_user:
+                thr = np.arange(k_user, dtype=np.int32)
         else:
             thr = np.arange(nb - 1, dtype=np.int32)
         self.thr_ids = torch.from_numpy(thr).to(self.dev)
@@ -225,6 +229,7 @@ class _DeviceTrainer:
         st.min_samples_leaf = int(cfg.min_samples_leaf)
         st.n_thresholds = int(thr.shape[0])
         st.feature_block_size = int(cfg.feature_block_size)
+        st.cut_mass = 1 if self.cut_mass else 0
         st.lambda_l2 = float(cfg.lambda_l2)
         st.lambda_dro = float(cfg.lambda_dro)
         st.direction_weight = float(cfg.direction_weight)
@@ -623,19 +628,13 @@ class PackBoost:
             free, _tot = torch.cuda.mem_get_info(self._device)
             replicate = choose_replicated(N * F * bits // 8, free, world,
                                           os.getenv("PACKBOOST_SHARD_CODES") == "1", self._device)
-        if world > 1 and not replicate:
-            feat_local = feature_map(F, rank, world)
-            matrix = pack_feature_major(X_src, edges, cfg.max_bins, row_order=order, feature_map=feat_local,
-                                        n_features_local=c1 - c0, validate_codes=validate_on_device,
-                                        columns=(c0, c1), defer_validation=True)
-        elif world > 1:
-            feat_local = feature_map(F, 0, 1)
-            matrix = PackedMatrix(N, blk * world, bits, self._device)   # feature rows past F stay empty
-            pack_feature_major(X_src, edges, cfg.max_bins, row_order=order, validate_codes=validate_on_device,
-                               columns=(c0, c1), out=matrix, defer_validation=True)
-            slabs = matrix.codes.view(world, -1)
-            torch.distributed.all_gather_into_tensor(matrix.codes.view(-1), slabs[rank].clone())
-            matrix.n_features_local = F
+        if world > 1:
+            # every rank brings over and packs 1 / world of the rows; the packed pieces are exchanged
+            # between the GPUs (all-gather for the replicated layout, all-to-all for the sharded one)
+            feat_local = feature_map(F, 0, 1) if replicate else feature_map(F, rank, world)
+            matrix = pack_feature_major_distributed(X_src, edges, cfg.max_bins, row_order=order, rank=rank, world=world,
+                                                    n_features=F, keep=None if replicate else (c0, c1),
+                                                    validate_codes=validate_on_device)
         else:
             feat_local = feature_map(F, 0, 1)
             matrix = pack_feature_major(X_src, edges, cfg.max_bins, row_order=order, validate_codes=validate_on_device,

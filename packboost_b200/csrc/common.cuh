@@ -57,7 +57,7 @@ struct Cand {
     float score;
     int32_t k;            // index into thr_ids, -1: empty entry
     uint32_t left_count;
-    uint32_t flags;       // bit 0: a globally valid threshold of this feature scored NaN
+    uint32_t flags;       // bit 0: a globally valid threshold of this feature scored NaN; bits 8-15: bin id of threshold k
     int64_t left_gq;
 };
 static_assert(sizeof(Cand) == 24, "Cand layout");
@@ -190,7 +190,8 @@ struct ScoreLaunch {
     int n_eras;
     int max_bins;
     int n_thr;
-    const int32_t* thr_ids;
+    const int32_t* thr_ids;      // [n_thr] ascending bin ids, or [n_feat][n_thr] with thr_per_feature
+    int thr_per_feature;         // 1: every feature of the block has its own threshold list (mass cuts)
     float lambda_l2, lambda_dro, direction_weight, era_alpha;
     int min_samples_leaf;
     Cand* cand;                  // [n_sampled][node_stride]
@@ -202,6 +203,10 @@ struct ScoreLaunch {
     int tot_fpl, tot_lanes;      // layout of lc_tot / lg_tot (tot_index(); 0, 0: the classic layout above)
 };
 int launch_score(const ScoreLaunch& s, cudaStream_t stream);
+// Per-feature threshold lists at the count-mass quantiles of the frontier rows (mass K-cuts), from a
+// stored histogram: thr_out[f][n_thr].
+int launch_mass_thresholds(const uint32_t* cnt, int n_feat, const int32_t* n_nodes_ptr, int n_nodes_max, int node_stride,
+                           int n_eras, int max_bins, int n_thr, int32_t* thr_out, cudaStream_t stream);
 size_t score_scratch_bytes_per_feature(int node_stride, int n_eras, int n_thr);
 
 }  // namespace pb

@@ -169,7 +169,6 @@ __global__ void __launch_bounds__(kSelThreads) select_kernel(SelectArgs a) {
     Ctl& c = a.c;
     __shared__ BlockBest s_best[kSelChunk];
     __shared__ int s_nan[kSelChunk];
-    __shared__ int s_thr[256];
     __shared__ int s_last;
     const int n_ctx = c.head->n_ctx[a.depth];
     const int n = blockIdx.x;
@@ -180,7 +179,6 @@ __global__ void __launch_bounds__(kSelThreads) select_kernel(SelectArgs a) {
     const float inv = c.head->inv_scale;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
     const bool keep_frontier = (a.depth + 1) < a.max_depth;
-    for (int i = threadIdx.x; i < a.n_thr && i < 256; i += blockDim.x) s_thr[i] = a.thr_ids[i];
 
     // ---- A. this node: in-block winners by the warps, cross-block merge by thread 0 ----
     float best_s = -INFINITY;
@@ -197,7 +195,8 @@ __global__ void __launch_bounds__(kSelThreads) select_kernel(SelectArgs a) {
                 const Cand cd = a.cand[(size_t)p * a.node_stride + n];
                 if (cd.flags & 1u) has_nan = true;
                 if (cd.k < 0) continue;
-                const BlockBest x{cd.score, (long long)cd.left_count, cd.left_gq, p, cd.k, a.sampled[p]};
+                // (the k field of a block winner carries the candidate's threshold bin id from here on)
+                const BlockBest x{cd.score, (long long)cd.left_count, cd.left_gq, p, (int)((cd.flags >> 8) & 0xFFu), a.sampled[p]};
                 if (block_better(x, mine)) mine = x;
             }
             has_nan = __any_sync(0xFFFFFFFFu, has_nan);
@@ -223,7 +222,7 @@ __global__ void __launch_bounds__(kSelThreads) select_kernel(SelectArgs a) {
                 const BlockBest& m = s_best[j];
                 if (s_nan[j] || m.p < 0) continue;
                 const int feat = m.f;
-                const int thr = s_thr[m.k];
+                const int thr = m.k;
                 const bool upd = (m.s > best_s) ||
                                  (m.s == best_s && ((m.c > best_c) ||
                                                     (m.c == best_c && ((feat > best_f) || (feat == best_f && thr > best_t)))));
@@ -548,7 +547,7 @@ static int need_workspace(const pb_train_state* st, const char* who) {
 struct BlockPlan {
     int64_t fb;  // features per block
     bool fused;  // the histogram is never stored (fused flush): no gsum / cnt arrays
-    size_t off_gsum, off_cnt, off_gw, off_lg, off_lc;
+    size_t off_gsum, off_cnt, off_gw, off_lg, off_lc, off_thr;
 };
 
 // The era-summed tables of the fused flush are laid out per lane of the histogram kernel and so
@@ -558,8 +557,8 @@ constexpr int64_t kTotPad = 128;
 static bool plan_block(size_t avail, int stride, int64_t n_eras, int64_t max_bins, int64_t n_thr, int64_t n_feat,
                        bool fused, BlockPlan* p) {
     const size_t cells = fused ? 0 : (size_t)stride * n_eras * max_bins;
-    const size_t per_feat = cells * 12 + score_scratch_bytes_per_feature(stride, (int)n_eras, (int)n_thr);
-    const size_t fixed = 5 * 256 + (fused ? (size_t)kTotPad * stride * n_thr * 12 : 0);
+    const size_t per_feat = cells * 12 + score_scratch_bytes_per_feature(stride, (int)n_eras, (int)n_thr) + (size_t)n_thr * 4;
+    const size_t fixed = 6 * 256 + (fused ? (size_t)kTotPad * stride * n_thr * 12 : 0);
     if (avail < per_feat + fixed) return false;
     int64_t fb = (int64_t)((avail - fixed) / per_feat);
     if (fb > n_feat) fb = n_feat;
@@ -577,6 +576,8 @@ static bool plan_block(size_t avail, int stride, int64_t n_eras, int64_t max_bin
     p->off_lg = o;
     o += align_up(tot_feats * stride * n_thr * 8, 256);
     p->off_lc = o;
+    o += align_up(tot_feats * stride * n_thr * 4, 256);
+    p->off_thr = o;  // per-feature threshold lists (mass cuts): fb * n_thr * 4 bytes
     return true;
 }
 
@@ -615,7 +616,7 @@ static bool use_fused_flush(const pb_train_state* st, int64_t depth) {
         const char* e = getenv("PACKBOOST_FUSED_FLUSH");
         return !(e && e[0] == '0' && e[1] == 0);
     }();
-    if (!enabled || st->direction_weight != 0.0) return false;
+    if (!enabled || st->direction_weight != 0.0 || st->cut_mass) return false;  // (mass cuts need the stored histogram)
     Ctl c = ctl_view(st->ctl);
     return hist_can_fuse(hist_launch_of(st, depth, c));
 }
@@ -652,6 +653,14 @@ static int hist_score_blocks(const pb_train_state* st, int64_t depth, const int3
         }
         int rc = launch_hist(h, stream);
         if (rc) return rc;
+        const int32_t* thr_ids = st->thr_ids;
+        if (st->cut_mass) {
+            int32_t* thr_tab = reinterpret_cast<int32_t*>(scratch + plan.off_thr);
+            rc = launch_mass_thresholds(cnt, nf, &c.head->n_ctx[depth], stride, stride, (int)st->n_eras, (int)st->max_bins,
+                                        (int)st->n_thresholds, thr_tab, stream);
+            if (rc) return rc;
+            thr_ids = thr_tab;
+        }
         ScoreLaunch s;
         s.cnt = cnt;
         s.gsum = gsum;
@@ -666,7 +675,8 @@ static int hist_score_blocks(const pb_train_state* st, int64_t depth, const int3
         s.n_eras = (int)st->n_eras;
         s.max_bins = (int)st->max_bins;
         s.n_thr = (int)st->n_thresholds;
-        s.thr_ids = st->thr_ids;
+        s.thr_ids = thr_ids;
+        s.thr_per_feature = st->cut_mass ? 1 : 0;
         s.lambda_l2 = (float)st->lambda_l2;
         s.lambda_dro = (float)st->lambda_dro;
         s.direction_weight = (float)st->direction_weight;

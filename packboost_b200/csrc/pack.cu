@@ -182,18 +182,6 @@ extern "C" int pb_pack_codes_u8(const uint8_t* x, int64_t n_chunk, int64_t n_fea
     return pack_fm(a, (int)code_bits, (cudaStream_t)stream);
 }
 
-extern "C" int pb_copy_columns_h2d(void* dst, const void* src_host, int64_t n_rows, int64_t src_pitch_bytes,
-                                   int64_t col_offset_bytes, int64_t width_bytes, void* stream) {
-    PB_REQUIRE(dst && src_host, "null buffer");
-    PB_REQUIRE(n_rows >= 0 && width_bytes >= 1 && col_offset_bytes >= 0 && col_offset_bytes + width_bytes <= src_pitch_bytes,
-               "column strip outside the source rows");
-    if (n_rows == 0) return PB_OK;
-    PB_CUDA_TRY(cudaMemcpy2DAsync(dst, (size_t)width_bytes, static_cast<const char*>(src_host) + col_offset_bytes,
-                                  (size_t)src_pitch_bytes, (size_t)width_bytes, (size_t)n_rows, cudaMemcpyHostToDevice,
-                                  (cudaStream_t)stream));
-    return PB_OK;
-}
-
 extern "C" int pb_pack_rows(const void* x, int64_t x_is_f32, int64_t n_rows, int64_t n_features, const float* edges,
                             int64_t n_edges, int64_t max_bins, uint8_t* out, int64_t pitch_row, int64_t code_bits,
                             void* stream) {

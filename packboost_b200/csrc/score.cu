@@ -76,7 +76,9 @@ __global__ void __launch_bounds__(kGainThreads, (KT <= 4 && NBT <= 5) ? 3 : 2) g
     const int e_end = min(E, e_begin + e_per);
     int thr[KT];
 #pragma unroll
-    for (int k = 0; k < KT; ++k) thr[k] = (k < K) ? s.thr_ids[k] : 0;
+    const int32_t* thr_list = s.thr_ids + (s.thr_per_feature ? (size_t)f * K : 0);
+#pragma unroll
+    for (int k = 0; k < KT; ++k) thr[k] = (k < K) ? thr_list[k] : 0;
     uint32_t lc_sum[KT];
     long long lg_sum[KT];
 #pragma unroll
@@ -199,7 +201,8 @@ __global__ void __launch_bounds__(kGainThreads) gain_kernel_wide(GainArgs a) {
     const int E = s.n_eras, NB = s.max_bins, K = s.n_thr;
     for (int i = threadIdx.x; i < 256; i += kGainThreads) s_kof[i] = -1;
     __syncthreads();
-    for (int k = threadIdx.x; k < K; k += kGainThreads) s_kof[s.thr_ids[k]] = k;
+    const int32_t* thr_list = s.thr_ids + (s.thr_per_feature ? (size_t)f * K : 0);
+    for (int k = threadIdx.x; k < K; k += kGainThreads) s_kof[thr_list[k]] = k;
     __syncthreads();
     if (node >= n_nodes) return;
     const float inv_scale = *s.inv_scale_ptr;
@@ -379,7 +382,9 @@ __device__ __forceinline__ void finish_pairs(const ScoreLaunch& s, int f, int no
         out.score = bs;
         out.k = bk;
         out.left_count = (bk >= 0) ? (uint32_t)bc : 0u;
-        out.flags = flags;
+        // the bin id of the chosen threshold travels with the candidate (the lists may differ per feature)
+        const int thr_bin = (bk >= 0) ? s.thr_ids[(s.thr_per_feature ? (size_t)f * K : 0) + bk] : 0;
+        out.flags = flags | ((uint32_t)thr_bin << 8);
         out.left_gq = (bk >= 0) ? res_lg[i * K + bk] : 0ll;
         s.cand[(size_t)s.feat_pos[f] * s.node_stride + node0 + i] = out;
     }
@@ -478,7 +483,7 @@ __global__ void __launch_bounds__(kChainThreads) chain_kernel(ChainArgs a) {
             const float pa = (gpar > 0) ? -1.f : ((gpar < 0) ? 1.f : 0.f);  // sign(-G/(H+lambda)), H+lambda > 0
             const float inv_scale = *s.inv_scale_ptr;
             const int NB = s.max_bins;
-            const int t = s.thr_ids[my_k];
+            const int t = s.thr_ids[(s.thr_per_feature ? (size_t)f * K : 0) + my_k];
             for (int e = 0; e < E; ++e) {
                 const float2 v = gw[(size_t)e * e_stride];
                 const float w = v.y;
@@ -694,6 +699,96 @@ __global__ void __launch_bounds__(2 * kUnitSlotsMax) chain_unit_kernel(ChainArgs
 }
 
 }  // namespace
+
+// ---- mass K-cuts -----------------------------------------------------------------------------------
+// Thresholds of one feature at the quantiles of its bin masses over all frontier rows (every node,
+// every era), as the reference's compiled split finder takes them
+// (packboost/backends/cpu/frontier_cpu.cpp:59-109; its evenly spaced fallback :35-57): the target
+// masses are i / (k - 1) of total * (1 - 1e-12) in float64, a threshold is one below the first bin
+// whose cumulative mass reaches the target, duplicates are dropped, evenly spaced ids fill up, and
+// the k smallest ids are kept.
+namespace {
+
+__global__ void __launch_bounds__(256) mass_thr_kernel(const uint32_t* __restrict__ cnt, const int32_t* n_nodes_ptr,
+                                                       int n_nodes_max, int node_stride, int E, int nb, int K,
+                                                       int32_t* __restrict__ thr_out) {
+    __shared__ unsigned int s_m[256];
+    __shared__ int s_set[256];
+    const int f = blockIdx.x;
+    const int n_nodes = min(*n_nodes_ptr, n_nodes_max);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
+    for (int i = threadIdx.x; i < 256; i += blockDim.x) { s_m[i] = 0u; s_set[i] = 0; }
+    __syncthreads();
+    // a warp takes (era, node) pairs in turn; lane l sums bins l, l + 32, ...
+    unsigned int acc[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] = 0u;
+    for (int pair = warp; pair < E * n_nodes; pair += n_warps) {
+        const int e = pair / n_nodes, n = pair - e * n_nodes;
+        const uint32_t* row = cnt + (((size_t)f * E + e) * node_stride + n) * nb;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const int b = j * 32 + lane;
+            if (b < nb) acc[j] += row[b];
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        const int b = j * 32 + lane;
+        if (b < nb && acc[j]) atomicAdd(&s_m[b], acc[j]);
+    }
+    __syncthreads();
+    if (threadIdx.x != 0) return;
+    const int max_thr = max(1, nb - 1);
+    const int kk = max(1, min(K, max_thr));
+    auto even_into_set = [&]() {  // evenly spaced ids, round half away from zero
+        if (kk == 1) { s_set[0] = 1; return; }
+        const double step = (double)(max_thr - 1) / (double)(kk - 1);
+        for (int i = 0; i < kk; ++i) {
+            long long idx = llround(round((double)i * step));
+            idx = max(0ll, min(idx, (long long)max_thr - 1));
+            s_set[(int)idx] = 1;
+        }
+    };
+    long long total = 0;
+    for (int b = 0; b < nb; ++b) total += s_m[b];
+    int have = 0;
+    if (total <= 0) {
+        even_into_set();
+    } else {
+        const double upper = (double)total * (1.0 - 1e-12);
+        for (int i = 0; i < kk; ++i) {
+            const double alpha = (kk == 1) ? 0.0 : (double)i / (double)(kk - 1);
+            const double target = upper * alpha;
+            long long run = 0;
+            int idx = nb - 1;
+            for (int b = 0; b < nb; ++b) {  // first bin whose cumulative mass is not below the target
+                run += s_m[b];
+                if (!((double)run < target)) { idx = b; break; }
+            }
+            const int thr = max(0, min(idx - 1, max_thr - 1));
+            if (!s_set[thr]) { s_set[thr] = 1; ++have; }
+        }
+        if (have < kk) even_into_set();
+    }
+    int w = 0, last = 0;
+    for (int b = 0; b < max_thr && w < kk; ++b)
+        if (s_set[b]) { thr_out[(size_t)f * K + w] = b; last = b; ++w; }
+    for (; w < K; ++w) thr_out[(size_t)f * K + w] = last;  // (not reached: kk distinct ids always exist)
+}
+
+}  // namespace
+
+int launch_mass_thresholds(const uint32_t* cnt, int n_feat, const int32_t* n_nodes_ptr, int n_nodes_max, int node_stride,
+                           int n_eras, int max_bins, int n_thr, int32_t* thr_out, cudaStream_t stream) {
+    if (n_feat <= 0) return PB_OK;
+    if (max_bins > 256 || n_thr < 1 || n_thr > 255) return fail_arg("mass thresholds: bin or threshold count out of range");
+    mass_thr_kernel<<<(unsigned)n_feat, 256, 0, stream>>>(cnt, n_nodes_ptr, n_nodes_max, node_stride, n_eras, max_bins,
+                                                           n_thr, thr_out);
+    count_launch(1);
+    PB_LAUNCH_CHECK("mass_thr_kernel");
+    return PB_OK;
+}
 
 size_t score_scratch_bytes_per_feature(int node_stride, int n_eras, int n_thr) {
     return (size_t)node_stride * n_eras * n_thr * sizeof(float2) + (size_t)node_stride * n_thr * 12;

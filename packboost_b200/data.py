@@ -127,11 +127,16 @@ def _row_chunks(n_rows: int, row_bytes: int) -> Iterable[tuple[int, int]]:
 class PackedMatrix:
     """Feature-major packed bin codes on the device (layout of ``pb_train_state.codes``)."""
 
-    def __init__(self, n_rows: int, n_features_local: int, code_bits: int, device: torch.device):
+    def __init__(self, n_rows: int, n_features_local: int, code_bits: int, device: torch.device,
+                 pitch: int | None = None):
         self.n_rows = int(n_rows)
         self.rows_padded = (self.n_rows + 255) // 256 * 256
         self.code_bits = int(code_bits)
         self.pitch = (self.rows_padded * code_bits // 8 + 127) // 128 * 128
+        if pitch is not None:
+            if pitch % 128 or pitch < self.pitch:
+                raise ValueError("pitch must be a multiple of 128 that covers the padded rows")
+            self.pitch = int(pitch)
         self.n_features_local = int(n_features_local)
         self.max_code = 0   # largest pre-binned code seen while packing (when validation was asked for)
         self.codes = torch.zeros((max(self.n_features_local, 1), self.pitch), dtype=torch.uint8, device=device)
@@ -147,6 +152,25 @@ class PackedMatrix:
 
 
 _STAGE: dict = {}
+
+
+def _parallel_copy(dst: np.ndarray, src: np.ndarray) -> None:
+    """``dst[...] = src`` for 2-D arrays with the rows dealt over a few threads (numpy releases the
+    GIL while it copies): one thread moves ~10 GB/s, the host link takes five times that."""
+    import os
+    from concurrent.futures import ThreadPoolExecutor
+    n = src.shape[0]
+    workers = max(1, min(8, (os.cpu_count() or 2) // 2, n // 4096))
+    if workers == 1:
+        np.copyto(dst, src, casting="unsafe")
+        return
+    pool = _STAGE.get("pool")
+    if pool is None:
+        pool = _STAGE["pool"] = ThreadPoolExecutor(max_workers=8)
+    step = (n + workers - 1) // workers
+    futs = [pool.submit(np.copyto, dst[a:a + step], src[a:a + step], "unsafe") for a in range(0, n, step)]
+    for f in futs:
+        f.result()
 
 
 def _staging(nbytes: int) -> list[tuple[torch.Tensor, torch.cuda.Event]]:
@@ -168,7 +192,7 @@ def pack_feature_major(
     feature_map: np.ndarray | None = None,
     n_features_local: int | None = None,
     validate_codes: bool = False,
-    columns: tuple[int, int] | None = None,
+    rows: tuple[int, int] | None = None,
     out: "PackedMatrix | None" = None,
     defer_validation: bool = False,
 ) -> PackedMatrix:
@@ -176,10 +200,9 @@ def pack_feature_major(
 
     ``row_order`` lists source rows in destination order (era-sorted rows);
     ``feature_map[j]`` is the destination feature row of column ``j`` or -1.
-    ``columns=(c0, c1)`` restricts the work to that strip of columns: only those bytes travel to
-    the device (one strided copy per chunk from page-locked memory) and ``feature_map`` /
-    ``edges`` still refer to the full width.  ``out`` packs into an existing matrix.
-    ``validate_codes`` checks on the device that pre-binned input stays below ``max_bins``
+    ``rows=(r0, r1)`` packs only that range of destination rows, into rows ``0 .. r1 - r0`` of
+    ``out`` (one rank's share when several GPUs split the upload).  ``out`` packs into an existing
+    matrix.  ``validate_codes`` checks on the device that pre-binned input stays below ``max_bins``
     (negative int8 values show up as codes >= 128) and raises ``ValueError`` otherwise; with
     ``defer_validation`` the largest code seen is only recorded in ``PackedMatrix.max_code`` (several
     ranks must agree before any of them raises).
@@ -192,75 +215,62 @@ def pack_feature_major(
     lib = B.lib()
     n_rows, n_feat = X.shape
     bits = code_bits_for(max_bins)
-    c0, c1 = (0, n_feat) if columns is None else (int(columns[0]), int(columns[1]))
-    width = c1 - c0
+    r0, r1 = (0, n_rows) if rows is None else (int(rows[0]), int(rows[1]))
     n_local = n_feat if n_features_local is None else n_features_local
-    pm = out if out is not None else PackedMatrix(n_rows, n_local, bits, dev)
-    if width <= 0 or n_rows == 0:
-        torch.cuda.current_stream().synchronize()
+    pm = out if out is not None else PackedMatrix(r1 - r0, n_local, bits, dev)
+    if r1 <= r0:
         return pm
-    fmap = np.arange(n_feat, dtype=np.int32) if feature_map is None else np.ascontiguousarray(feature_map, dtype=np.int32)
-    fmap_t = torch.from_numpy(np.ascontiguousarray(fmap[c0:c1])).to(dev)
+    fmap_t = None
+    if feature_map is not None:
+        fmap_t = torch.from_numpy(np.ascontiguousarray(feature_map, dtype=np.int32)).to(dev)
     is_f32 = edges is not None
-    edges_t = (torch.from_numpy(np.ascontiguousarray(np.asarray(edges, dtype=np.float32)[:, c0:c1])).to(dev)
-               if is_f32 else None)
+    edges_t = torch.from_numpy(np.ascontiguousarray(edges, dtype=np.float32)).to(dev) if is_f32 else None
     stream = torch.cuda.current_stream().cuda_stream
     is_tensor = isinstance(X, torch.Tensor)
-    on_device = is_tensor and X.is_cuda
-    pinned = is_tensor and (not X.is_cuda) and X.is_pinned() and X.is_contiguous()
     want = torch.float32 if is_f32 else torch.uint8
     item = 4 if is_f32 else 1
     np_want = np.float32 if is_f32 else np.uint8
+    # a tensor that torch can hand to the copy engine as it is: on the device, or page-locked
+    direct = is_tensor and (X.is_cuda or X.is_pinned())
     order_t = None
     if row_order is not None and is_tensor:
         order_t = torch.from_numpy(np.ascontiguousarray(row_order, dtype=np.int64)).to(X.device)
     top = torch.zeros((), dtype=torch.uint8, device=dev)
-    chunks = list(_row_chunks(n_rows, width * item))
+    chunks = [(r0 + a, r0 + b) for a, b in _row_chunks(r1 - r0, n_feat * item)]
     stage = None
     for i, (a, b) in enumerate(chunks):
         n = b - a
-        if on_device:
-            rows = X[a:b] if order_t is None else X.index_select(0, order_t[a:b])
-            rows = rows[:, c0:c1]
-            if rows.dtype == torch.int8 and not is_f32:
-                rows = rows.view(torch.uint8)
-            chunk = rows.to(dtype=want).contiguous()
-        elif pinned and order_t is None and X.dtype in ((torch.float32,) if is_f32 else (torch.uint8, torch.int8)):
-            # page-locked source of the right type: the strip is read where it lies
-            chunk = torch.empty((n, width), dtype=want, device=dev)
-            B.check(lib.pb_copy_columns_h2d(chunk.data_ptr(), X.data_ptr() + a * n_feat * item, n, n_feat * item,
-                                            c0 * item, width * item, stream))
+        if direct:
+            src = X[a:b] if order_t is None else X.index_select(0, order_t[a:b])
+            if src.dtype == torch.int8 and not is_f32:
+                src = src.view(torch.uint8)
+            chunk = src.to(device=dev, dtype=want, non_blocking=True).contiguous()
         else:
-            # pageable (or gathered / converted) source: through a page-locked staging buffer
+            # pageable source: through a page-locked staging buffer
             if stage is None:
-                stage = _staging((chunks[0][1] - chunks[0][0]) * width * item)
+                stage = _staging((chunks[0][1] - chunks[0][0]) * n_feat * item)
             buf, ev = stage[i % 2]
             ev.synchronize()                       # the transfer that last used this buffer is done
-            dst = buf[: n * width * item].view(want).view(n, width)
+            dst = buf[: n * n_feat * item].view(want).view(n, n_feat)
             if is_tensor:
-                rows = X[a:b] if order_t is None else X.index_select(0, order_t[a:b])
-                rows = rows[:, c0:c1]
-                if rows.dtype == torch.int8 and not is_f32:
-                    rows = rows.view(torch.uint8)
-                dst.copy_(rows)
+                src = X[a:b] if order_t is None else X.index_select(0, order_t[a:b])
+                if src.dtype == torch.int8 and not is_f32:
+                    src = src.view(torch.uint8)
+                dst.copy_(src)
             else:
-                rows = X[a:b] if row_order is None else X[row_order[a:b]]
-                rows = rows[:, c0:c1]
-                if rows.dtype == np.int8 and not is_f32:
-                    rows = rows.view(np.uint8)
-                if rows.dtype == np_want and rows.flags.writeable:
-                    dst.copy_(torch.from_numpy(rows))   # multi-threaded strided host copy
-                else:
-                    np.copyto(dst.numpy(), rows, casting="unsafe")
+                src = X[a:b] if row_order is None else X[row_order[a:b]]
+                if src.dtype == np.int8 and not is_f32:
+                    src = src.view(np.uint8)
+                _parallel_copy(dst.numpy(), src)
             chunk = dst.to(dev, non_blocking=True)
             ev.record()
         if validate_codes and not is_f32:
             top = torch.maximum(top, chunk.max())
         if is_f32:
-            B.check(lib.pb_bin_pack_f32(chunk.data_ptr(), n, width, a, edges_t.data_ptr(), edges_t.shape[0],
-                                        max_bins, fmap_t.data_ptr(), pm.codes.data_ptr(), pm.pitch, bits, stream))
+            B.check(lib.pb_bin_pack_f32(chunk.data_ptr(), n, n_feat, a - r0, edges_t.data_ptr(), edges_t.shape[0],
+                                        max_bins, B._ptr(fmap_t), pm.codes.data_ptr(), pm.pitch, bits, stream))
         else:
-            B.check(lib.pb_pack_codes_u8(chunk.data_ptr(), n, width, a, fmap_t.data_ptr(), pm.codes.data_ptr(),
+            B.check(lib.pb_pack_codes_u8(chunk.data_ptr(), n, n_feat, a - r0, B._ptr(fmap_t), pm.codes.data_ptr(),
                                          pm.pitch, bits, stream))
         # no synchronisation per chunk: the copy, the pack kernel and the release of `chunk` are
         # ordered on the current stream
@@ -269,6 +279,54 @@ def pack_feature_major(
     if validate_codes and not defer_validation and pm.max_code >= min(max_bins, 128):
         raise ValueError("prebinned=True requires X to contain integer bins within [0, max_bins).")
     return pm
+
+
+def rows_per_rank(n_rows: int, world: int) -> int:
+    """Rows each rank packs when the upload is split by rows: equal shares rounded up to 256 rows
+    (128 bytes of 4-bit codes), so that every rank's bytes of a feature row are a whole, aligned
+    segment of it."""
+    per = (n_rows + world - 1) // max(world, 1)
+    return (per + 255) // 256 * 256
+
+
+def pack_feature_major_distributed(X, edges, max_bins, *, row_order, rank: int, world: int, n_features: int,
+                                   keep: tuple[int, int] | None, validate_codes: bool = False) -> PackedMatrix:
+    """Pack the matrix with ``world`` GPUs sharing the host -> device transfer.
+
+    Rank ``r`` brings over and packs only rows ``[r * R, (r + 1) * R)`` (``R = rows_per_rank``): a
+    contiguous piece of the caller's row-major matrix, 1 / world of the bytes, at the full speed of
+    its own host link.  The packed pieces are then exchanged between the GPUs (NVLink): with
+    ``keep=None`` every rank ends up with the whole feature-major matrix (all-gather), with
+    ``keep=(c0, c1)`` with all rows of its own features ``c0 .. c1`` only (all-to-all; every rank
+    owns a block of ``ceil(F / world)`` features).  The result is laid out exactly like the matrix a
+    single GPU would pack, with ``pitch = world * R * code_bits / 8``."""
+    import torch.distributed as dist
+    dev = _device()
+    n_rows = X.shape[0]
+    bits = code_bits_for(max_bins)
+    per = rows_per_rank(n_rows, world)
+    seg = per * bits // 8                                   # bytes of one feature row per rank (multiple of 128)
+    blk = (n_features + world - 1) // world
+    f_pad = blk * world
+    slab = PackedMatrix(per, f_pad, bits, dev)
+    assert slab.pitch == seg
+    r0, r1 = min(n_rows, rank * per), min(n_rows, (rank + 1) * per)
+    pack_feature_major(X, edges, max_bins, row_order=row_order, validate_codes=validate_codes, rows=(r0, r1), out=slab,
+                       defer_validation=True)
+    if keep is None:
+        full = PackedMatrix(n_rows, f_pad, bits, dev, pitch=world * seg)
+        parts = torch.empty((world, f_pad, seg), dtype=torch.uint8, device=dev)
+        dist.all_gather_into_tensor(parts, slab.codes)
+        full.codes.view(f_pad, world, seg).copy_(parts.permute(1, 0, 2))
+        full.n_features_local = n_features
+    else:
+        full = PackedMatrix(n_rows, blk, bits, dev, pitch=world * seg)
+        parts = torch.empty((world, blk, seg), dtype=torch.uint8, device=dev)
+        dist.all_to_all_single(parts, slab.codes.view(world, blk, seg))
+        full.codes.view(blk, world, seg).copy_(parts.permute(1, 0, 2))
+        full.n_features_local = keep[1] - keep[0]
+    full.max_code = slab.max_code
+    return full
 
 
 class PackedRows:

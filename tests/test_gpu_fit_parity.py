@@ -407,3 +407,37 @@ def test_wide_cases_match_reference(name):
     worst = np.max(np.abs(got0 - exact) / bound)
     print(f"{name}: first-round leaves vs float64: worst error / float32 rounding bound = {worst:.3f}")
     assert worst <= 1.0
+
+
+@pytest.mark.parametrize("name,k", [("config1", 4), ("prebinned5", 2), ("ragged_eras", 7), ("interleaved", 5)])
+def test_mass_k_cuts_match_the_compiled_reference_and_the_oracle(name, k):
+    """``k_cuts`` with ``cut_selection="mass"`` (the reference's default policy, and the one its
+    published GPU run uses).  The reference's torch frontier raises on it; its compiled C++ split
+    finder implements it.  The thresholds of every (depth, feature) follow the C++ definition, the
+    scoring the torch frontier as always: the trees must equal those of the compiled reference
+    (``oracle/_ref``, when it was built) in structure, and the oracle's restatement of the policy in
+    its exact-sum variant in every bit."""
+    from oracle import native_ref
+    X, y, era, cfg, rounds, Xh = cases.CASES[name]()
+    cfg = dict(cfg)
+    cfg.update(k_cuts=k, cut_selection="mass", direction_weight=0.0)
+    booster = _fit_gpu(X, y, era, cfg, rounds)
+    off_g, cols_g = flatten_trees(booster.trees)
+    model = po.fit(X, y, era, po.OracleParams(exact_sums=True, native_mass_cuts=True, **cfg), rounds, record_depths=True)
+    off_o, cols_o = flatten_oracle(model.trees)
+    np.testing.assert_array_equal(off_g, off_o)
+    for key in ("feature", "threshold", "left", "right", "is_leaf"):
+        np.testing.assert_array_equal(cols_g[key], cols_o[key], err_msg=key)
+    np.testing.assert_array_equal(cols_g["value"].view(np.int64), cols_o["value"].astype(np.float64).view(np.int64))
+    rec = booster.split_records()
+    np.testing.assert_array_equal(rec["score"].view(np.int32),
+                                  np.asarray([r["score"] for r in model.depth_records], dtype=np.float32).view(np.int32))
+    np.testing.assert_array_equal(booster.train_predictions().view(np.int32), model.train_preds.view(np.int32))
+    if native_ref.available():
+        ref = native_ref.fit(X, y, era, po.OracleParams(**cfg), rounds)
+        off_r, cols_r = flatten_oracle(ref.trees)
+        np.testing.assert_array_equal(off_g, off_r)
+        for key in ("feature", "threshold", "left", "right", "is_leaf"):
+            np.testing.assert_array_equal(cols_g[key], cols_r[key], err_msg=f"compiled reference: {key}")
+        scale = np.abs(ref.train_preds).max()
+        np.testing.assert_allclose(booster.train_predictions(), ref.train_preds, rtol=1e-5, atol=1e-5 * scale)
