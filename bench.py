@@ -26,7 +26,6 @@ digests at every N and in every layout mean the same model bit for bit.
 from __future__ import annotations
 
 import argparse
-import ctypes as C
 import json
 import os
 import subprocess
@@ -333,18 +332,15 @@ def main():
         # a replayed round graph holds the number counted while it was captured
         out["launches"] = (int(lib.pb_launch_count()) - launches0
                            + (trainer.graph_replays - replays0) * trainer.graph_launches)
-        trainer.use_graph = False
-        lib.pb_profile_enable(1)
-        ms5 = (C.c_double * 5)()
-        n5 = (C.c_int64 * 5)()
+        trainer.enable_profile()    # eager launches, every kernel family bracketed by CUDA events
         logs0 = len(booster._depth_logs)
         barrier()
         for r in range(args.warmup + args.steps, total):
             booster._boost_one_round(r, total)
         booster._drain()
         barrier()
-        lib.pb_profile_enable(0)
-        B.check(lib.pb_profile_collect(ms5, n5))
+        ms5, n5 = trainer.profile_totals()
+        trainer.disable_profile()
         F_s = trainer.n_sampled()
         f_loc = F_s / world
         K = CFG["max_bins"] - 1

@@ -65,13 +65,20 @@ int pb_device_count(void);
 
 /* Instrumentation (the reference times its phases with perf_counter buckets,
  * packboost/booster.py:220-270, and a cudaEvent pair around its kernel,
- * packboost/backends/cuda/frontier_cuda.cu:670-710).  While enabled, every launch of a kernel
- * family is bracketed by two events on its stream.  After synchronising, pb_profile_collect
- * returns per family (0 histogram, 1 scorer, 2 select, 3 partition, 4 round begin/end) the
- * summed milliseconds and the number of bracketed launches, and clears the record.
- * pb_launch_count is the number of kernels this library launched since it was loaded. */
-int pb_profile_enable(int on);
-int pb_profile_collect(double* ms_by_kind /* [5] */, int64_t* launches_by_kind /* [5] */);
+ * packboost/backends/cuda/frontier_cuda.cu:670-710).  A profile object belongs to one training
+ * state (`pb_train_state.profile`, NULL = no timing): while it is set, every launch of a kernel
+ * family made through that state is bracketed by two events on its stream (not inside a stream
+ * capture).  After synchronising, pb_profile_collect returns per family (0 histogram, 1 scorer,
+ * 2 select, 3 partition, 4 round begin/end) the summed milliseconds and the number of bracketed
+ * launches; pb_profile_collect_launches returns the launches one by one in issue order (family and
+ * milliseconds, at most `cap`; `*n_out` is how many there were).  Both clear the record.  States
+ * with different profile objects may run concurrently.  pb_launch_count is the number of kernels
+ * this library launched since it was loaded.  With PACKBOOST_NVTX=1 in the environment every phase
+ * entry point opens an NVTX range ("pb.hist_score d=3", ...) for tools that attach to the process. */
+void* pb_profile_create(void);
+void pb_profile_destroy(void* profile);
+int pb_profile_collect(void* profile, double* ms_by_kind /* [5] */, int64_t* launches_by_kind /* [5] */);
+int pb_profile_collect_launches(void* profile, int32_t* kinds, float* ms, int64_t cap, int64_t* n_out);
 int64_t pb_launch_count(void);
 
 /* ---- binning and packing (packboost/data.py:45-58, 96-111) ---------------------------- */
@@ -147,8 +154,22 @@ typedef struct pb_train_state {
     int64_t cut_mass;            /* 1: k_cuts with cut_selection="mass": the n_thresholds thresholds of a feature are
                                     taken per depth at the quantiles of its bin masses over the frontier rows
                                     (packboost/backends/cpu/frontier_cpu.cpp:59-109); thr_ids is then unused */
-    int64_t reserved[2];
+    void* profile;               /* pb_profile_create() object, or NULL: see "Instrumentation" */
+    int64_t reserved[1];
 } pb_train_state;
+
+/* Index checks for debugging (the reference checks its inputs on the host,
+ * packboost/booster.py:349-367, and guards indices in its kernels,
+ * packboost/backends/cuda/frontier_cuda.cu:279-303, 451).  A library built with -DPB_DEBUG_BOUNDS
+ * (`python -m packboost_b200.build --debug-bounds`) makes the training kernels check the frontier
+ * slot and the bin codes of every row they accumulate and the feature id of every split they apply;
+ * a violation is recorded in a sticky word of the control block and the offending index is skipped
+ * - nothing traps.  pb_debug_flags copies that word to the host (it synchronises the device):
+ * bit 0 slot out of range, bit 1 bin code >= max_bins, bit 2 feature id out of range.  In a regular
+ * build the checks are compiled out and the word stays 0; pb_debug_bounds_enabled says which build
+ * this is. */
+int pb_debug_bounds_enabled(void);
+int pb_debug_flags(const pb_train_state* st, uint32_t* flags_out);
 
 /* sizeof(pb_train_state), so that a binding can verify its mirror of the struct. */
 int64_t pb_train_state_bytes(void);

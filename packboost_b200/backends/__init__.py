@@ -33,7 +33,9 @@ __all__ = [
     "check",
 ]
 
-_LIB_PATH = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "libpackboost_b200.so")
+# PACKBOOST_DEBUG_LIB=1 loads the build with index checks compiled in (python -m packboost_b200.build --debug-bounds)
+_LIB_PATH = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))),
+                         "libpackboost_b200_dbg.so" if os.getenv("PACKBOOST_DEBUG_LIB") == "1" else "libpackboost_b200.so")
 _LIB: C.CDLL | None = None
 _LOAD_ERROR: str | None = None
 
@@ -58,7 +60,7 @@ class TrainState(C.Structure):
         ("preds", vp), ("gq", vp), ("slot", vp), ("leaf", vp), ("ctl", vp), ("workspace", vp),
         ("workspace_bytes", i64),
         ("max_era_rows", i64), ("hist_rows_per_tile", i64), ("gq_bits", i64), ("count_bits", i64),
-        ("lo_bits", i64), ("cut_mass", i64), ("reserved", i64 * 2),
+        ("lo_bits", i64), ("cut_mass", i64), ("profile", vp), ("reserved", i64 * 1),
     ]
 
 
@@ -66,9 +68,13 @@ _PROTOS: dict[str, tuple[Any, list[Any]]] = {
     "pb_last_error": (C.c_char_p, []),
     "pb_abi_version": (C.c_int, []),
     "pb_device_count": (C.c_int, []),
-    "pb_profile_enable": (C.c_int, [C.c_int]),
-    "pb_profile_collect": (C.c_int, [vp, vp]),
+    "pb_profile_create": (vp, []),
+    "pb_profile_destroy": (None, [vp]),
+    "pb_profile_collect": (C.c_int, [vp, vp, vp]),
+    "pb_profile_collect_launches": (C.c_int, [vp, vp, vp, i64, vp]),
     "pb_launch_count": (i64, []),
+    "pb_debug_bounds_enabled": (C.c_int, []),
+    "pb_debug_flags": (C.c_int, [C.POINTER(TrainState), vp]),
     "pb_bin_pack_f32": (C.c_int, [vp, i64, i64, i64, vp, i64, i64, vp, vp, i64, i64, vp]),
     "pb_pack_codes_u8": (C.c_int, [vp, i64, i64, i64, vp, vp, i64, i64, vp]),
     "pb_pack_rows": (C.c_int, [vp, i64, i64, i64, vp, i64, i64, vp, i64, i64, vp]),

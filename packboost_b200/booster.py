@@ -289,6 +289,70 @@ class _DeviceTrainer:
         self.graph_launches = 0
         self.graph_replays = 0
         self.pending_delta = False
+        self.prof = None
+        self._prof_ms, self._prof_n = [0.0] * 5, [0] * 5
+
+    # -- per-phase timing (the reference fills hist_ms / score_ms / partition_ms of its depth logs
+    #    with perf_counter buckets, packboost/booster.py:220-270) --------------------------------
+    def enable_profile(self) -> None:
+        """Bracket every kernel family launch of this trainer with CUDA events.  Events cannot time
+        kernels inside a graph replay, so rounds are launched eagerly while this is on."""
+        if self.prof is None:
+            self.prof = self.lib.pb_profile_create()
+            self.st.profile = self.prof
+            self.use_graph = False
+            self.release_graph()
+
+    def disable_profile(self) -> None:
+        if self.prof is not None:
+            torch.cuda.current_stream().synchronize()
+            self.st.profile = None
+            self.lib.pb_profile_destroy(self.prof)
+            self.prof = None
+
+    def __del__(self):
+        try:
+            self.disable_profile()
+        except Exception:
+            pass
+
+    def profile_totals(self) -> tuple[list[float], list[int]]:
+        """Summed milliseconds and launch counts per kernel family since the last collection
+        (0 histogram, 1 scorer, 2 select, 3 partition, 4 round begin); synchronise first."""
+        ms5, n5 = (C.c_double * 5)(), (C.c_int64 * 5)()
+        B.check(self.lib.pb_profile_collect(self.prof, ms5, n5))
+        tot_ms = [a + b for a, b in zip(self._prof_ms, ms5)]
+        tot_n = [a + b for a, b in zip(self._prof_n, n5)]
+        self._prof_ms, self._prof_n = [0.0] * 5, [0] * 5
+        return tot_ms, tot_n
+
+    def profile_by_depth(self) -> list[dict[str, float]]:
+        """Milliseconds per depth of the rounds since the last collection: the launches come back in
+        issue order, a histogram launch after a select launch opens the next depth."""
+        cap = 4096
+        kinds, ms, n = (C.c_int32 * cap)(), (C.c_float * cap)(), C.c_int64()
+        B.check(self.lib.pb_profile_collect_launches(self.prof, kinds, ms, cap, C.byref(n)))
+        out: list[dict[str, float]] = []
+        cur = None
+        seen_select = True
+        names = {0: "hist_ms", 1: "score_ms", 2: "select_ms", 3: "partition_ms"}
+        for i in range(min(int(n.value), cap)):
+            k = int(kinds[i])
+            self._prof_ms[k] += float(ms[i])   # (kept for profile_totals)
+            self._prof_n[k] += 1
+            if k == 4:
+                seen_select = True
+                continue
+            if k == 0 and seen_select:
+                cur = {"hist_ms": 0.0, "score_ms": 0.0, "select_ms": 0.0, "partition_ms": 0.0}
+                out.append(cur)
+                seen_select = False
+            if cur is None:
+                continue
+            cur[names[k]] += float(ms[i])
+            if k == 2:
+                seen_select = True
+        return out
 
     def n_sampled(self) -> int:
         frac = float(self.cfg.layer_feature_fraction)
@@ -679,6 +743,8 @@ class PackBoost:
         # Without per-round consumers the host runs one round ahead of the device: round r is
         # enqueued before the log of round r - 1 is read, so the device never waits for the host.
         run_ahead = not want_metrics and os.getenv("PACKBOOST_RUN_AHEAD") != "0"
+        if want_metrics and os.getenv("PACKBOOST_PHASE_TIMERS", "1") != "0":
+            trainer.enable_profile()   # fills hist_ms / score_ms / partition_ms of the depth logs
 
         state0, subsets = self._predrawn if self._predrawn is not None else draw()
         self._predrawn = None
@@ -747,8 +813,9 @@ class PackBoost:
                 torch.randperm(self._fit_ctx["F"], generator=self._rng)
             self._predrawn = None
         k = self._trainer.n_sampled()
+        phase_ms = self._trainer.profile_by_depth() if self._trainer.prof is not None else []
         for d in range(used):
-            self._depth_logs.append(self._depth_log(d, n_ctx[d], k))
+            self._depth_logs.append(self._depth_log(d, n_ctx[d], k, phase_ms[d] if d < len(phase_ms) else None))
             w = winners[(1 << d) - 1: (1 << d) - 1 + n_ctx[d]]
             self._split_log.append(w[w["feature"] >= 0].copy())
         self._flush_pending_tree()
@@ -811,13 +878,19 @@ class PackBoost:
                 "left_count": rec["left_count"].astype(np.int64),
                 "right_count": (rec["total_count"] - rec["left_count"]).astype(np.int64)}
 
-    def _depth_log(self, depth: int, n_nodes: int, k: int) -> dict[str, object]:
+    def _depth_log(self, depth: int, n_nodes: int, k: int, ms: dict | None = None) -> dict[str, object]:
+        """Depth record with the reference's field names (``packboost/booster.py:220-270, 565-579``).
+        The millisecond fields are device times of the depth's kernels (CUDA events) when per-round
+        metrics were asked for, else 0: timing needs eager launches, which the fast path avoids.
+        ``scan_ms`` stays 0 (the prefix scan is part of the scorer kernels)."""
         blk = int(self.config.feature_block_size)
         blk = k if (blk <= 0 or blk > k) else blk
+        ms = ms or {}
         return {
             "nodes_processed": n_nodes, "nodes_skipped": 0, "rows_total": 0,
             "feature_blocks": (k + blk - 1) // blk, "bincount_calls": 0,
-            "hist_ms": 0.0, "scan_ms": 0.0, "score_ms": 0.0, "partition_ms": 0.0,
+            "hist_ms": ms.get("hist_ms", 0.0), "scan_ms": 0.0,
+            "score_ms": ms.get("score_ms", 0.0) + ms.get("select_ms", 0.0), "partition_ms": ms.get("partition_ms", 0.0),
             "nodes_subtract_ok": 0, "nodes_rebuild": n_nodes, "nodes_subtract_fallback": 0,
             "nodes_collapsed": n_nodes * (int(self.config.pack_size) - 1), "feature_block_size": blk,
             "depth": depth, "feature_subset_size": k, "pack_size": int(self.config.pack_size),

@@ -41,9 +41,16 @@ def _stale(target: str, deps: list[str]) -> bool:
     return any(os.path.getmtime(d) > t for d in deps)
 
 
-def build(force: bool = False, verbose: bool = False) -> str:
+DEBUG_LIB_PATH = os.path.join(HERE, "libpackboost_b200_dbg.so")
+
+
+def build(force: bool = False, verbose: bool = False, debug_bounds: bool = False) -> str:
+    """``debug_bounds``: build the variant with the kernels' index checks compiled in
+    (``-DPB_DEBUG_BOUNDS``, see ``pb_debug_flags`` in the header) as ``libpackboost_b200_dbg.so``
+    beside the regular library (``PACKBOOST_DEBUG_LIB=1`` makes ``packboost_b200.backends`` load it)."""
     nvcc = _nvcc()
-    objdir = os.path.join(HERE, "build")
+    objdir = os.path.join(HERE, "build_dbg" if debug_bounds else "build")
+    lib_path = DEBUG_LIB_PATH if debug_bounds else LIB_PATH
     os.makedirs(objdir, exist_ok=True)
     headers = [os.path.join(CSRC, "common.cuh"), os.path.join(CSRC, "des_math.cuh"),
                os.path.join(HERE, "..", "include", "packboost_b200.h")]
@@ -54,15 +61,15 @@ def build(force: bool = False, verbose: bool = False) -> str:
         o = os.path.join(objdir, src.replace(".cu", ".o"))
         objs.append(o)
         if force or _stale(o, [s] + headers):
-            cmd = [nvcc, "-c", s, "-o", o] + ARCH + COMMON + EXTRA.get(src, [])
+            cmd = [nvcc, "-c", s, "-o", o] + ARCH + COMMON + EXTRA.get(src, []) + (["-DPB_DEBUG_BOUNDS"] if debug_bounds else [])
             res = subprocess.run(cmd, capture_output=True, text=True)
             log_lines.append("$ " + " ".join(cmd))
             log_lines.append(res.stderr)
             if res.returncode != 0:
                 sys.stderr.write(res.stdout + res.stderr)
                 raise RuntimeError(f"nvcc failed on {src}")
-    if force or _stale(LIB_PATH, objs):
-        cmd = [nvcc, "-shared", "-o", LIB_PATH] + objs + ARCH
+    if force or _stale(lib_path, objs):
+        cmd = [nvcc, "-shared", "-o", lib_path] + objs + ARCH
         res = subprocess.run(cmd, capture_output=True, text=True)
         if res.returncode != 0:
             sys.stderr.write(res.stdout + res.stderr)
@@ -72,8 +79,8 @@ def build(force: bool = False, verbose: bool = False) -> str:
             fh.write("\n".join(log_lines))
         if verbose:
             print("\n".join(log_lines))
-    return LIB_PATH
+    return lib_path
 
 
 if __name__ == "__main__":
-    print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))
+    print(build(force="--force" in sys.argv, verbose="-v" in sys.argv, debug_bounds="--debug-bounds" in sys.argv))

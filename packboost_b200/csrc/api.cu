@@ -1,9 +1,13 @@
 // Error reporting and device probes of the C ABI.
 
 #include <stdarg.h>
+#include <stdlib.h>
+
+#include <nvtx3/nvToolsExt.h>
 
 #include <atomic>
 #include <mutex>
+#include <new>
 #include <utility>
 #include <vector>
 
@@ -33,25 +37,31 @@ int fail_cuda(cudaError_t e, const char* what) {
     return PB_ERR_CUDA;
 }
 
-// Timing hooks: when enabled, a pair of events brackets each launch of a kernel family on the
-// launching stream; pb_profile_collect (after the caller synchronised) sums the elapsed times.
-static bool g_prof_on = false;
-static std::vector<cudaEvent_t> g_ev_pool;
-static std::vector<std::pair<int, std::pair<cudaEvent_t, cudaEvent_t>>> g_ev_used;
-static cudaEvent_t g_open[kProfKinds];
-static std::atomic<long long> g_launches{0};
-static std::mutex g_prof_mu;
-
-static cudaEvent_t take_event() {
-    if (!g_ev_pool.empty()) {
-        cudaEvent_t e = g_ev_pool.back();
-        g_ev_pool.pop_back();
+// Timing hooks.  A profile object (pb_profile_create) hangs off a training state; while it is
+// there, a pair of events brackets each launch of a kernel family on the launching stream and
+// pb_profile_collect* (after the caller synchronised) reads the elapsed times.  Every state has
+// its own object, so concurrent trainers do not see each other's launches.
+struct Profile {
+    std::mutex mu;
+    std::vector<cudaEvent_t> pool;
+    std::vector<std::pair<int, std::pair<cudaEvent_t, cudaEvent_t>>> used;
+    cudaEvent_t open[kProfKinds] = {};
+    ~Profile() {
+        for (auto e : pool) cudaEventDestroy(e);
+        for (auto& u : used) { cudaEventDestroy(u.second.first); cudaEventDestroy(u.second.second); }
+    }
+    cudaEvent_t take() {
+        if (!pool.empty()) {
+            cudaEvent_t e = pool.back();
+            pool.pop_back();
+            return e;
+        }
+        cudaEvent_t e = nullptr;
+        cudaEventCreate(&e);
         return e;
     }
-    cudaEvent_t e = nullptr;
-    cudaEventCreate(&e);
-    return e;
-}
+};
+static std::atomic<long long> g_launches{0};
 
 // (no timing inside a stream capture: the events would become graph dependencies)
 static bool capturing(cudaStream_t stream) {
@@ -59,47 +69,90 @@ static bool capturing(cudaStream_t stream) {
     return cudaStreamIsCapturing(stream, &cs) == cudaSuccess && cs != cudaStreamCaptureStatusNone;
 }
 
-void prof_begin(int kind, cudaStream_t stream) {
-    if (!g_prof_on || capturing(stream)) return;
-    std::lock_guard<std::mutex> lk(g_prof_mu);
-    cudaEvent_t e = take_event();
+void prof_begin(void* prof, int kind, cudaStream_t stream) {
+    if (!prof || capturing(stream)) return;
+    Profile* p = static_cast<Profile*>(prof);
+    std::lock_guard<std::mutex> lk(p->mu);
+    cudaEvent_t e = p->take();
     cudaEventRecord(e, stream);
-    g_open[kind] = e;
+    p->open[kind] = e;
 }
 
-void prof_end(int kind, cudaStream_t stream) {
-    if (!g_prof_on || capturing(stream)) return;
-    std::lock_guard<std::mutex> lk(g_prof_mu);
-    cudaEvent_t e = take_event();
+void prof_end(void* prof, int kind, cudaStream_t stream) {
+    if (!prof || capturing(stream)) return;
+    Profile* p = static_cast<Profile*>(prof);
+    std::lock_guard<std::mutex> lk(p->mu);
+    if (!p->open[kind]) return;
+    cudaEvent_t e = p->take();
     cudaEventRecord(e, stream);
-    g_ev_used.push_back({kind, {g_open[kind], e}});
+    p->used.push_back({kind, {p->open[kind], e}});
+    p->open[kind] = nullptr;
+}
+
+// NVTX ranges around the phases of a round (PACKBOOST_NVTX=1): visible on the timeline of a tool
+// that attaches to the process, free otherwise.
+static bool nvtx_on() {
+    static const bool on = [] {
+        const char* e = getenv("PACKBOOST_NVTX");
+        return e && e[0] == '1';
+    }();
+    return on;
+}
+void nvtx_push(const char* fmt, long long a) {
+    if (!nvtx_on()) return;
+    char buf[64];
+    snprintf(buf, sizeof(buf), fmt, a);
+    nvtxRangePushA(buf);
+}
+void nvtx_pop() {
+    if (nvtx_on()) nvtxRangePop();
 }
 
 void count_launch(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
 
 }  // namespace pb
 
-extern "C" int pb_profile_enable(int on) {
-    std::lock_guard<std::mutex> lk(pb::g_prof_mu);
-    pb::g_prof_on = (on != 0);
-    return PB_OK;
-}
+extern "C" void* pb_profile_create(void) { return new (std::nothrow) pb::Profile(); }
 
-extern "C" int pb_profile_collect(double* ms_by_kind, int64_t* launches_by_kind) {
-    PB_REQUIRE(ms_by_kind && launches_by_kind, "null argument");
-    std::lock_guard<std::mutex> lk(pb::g_prof_mu);
-    for (int k = 0; k < pb::kProfKinds; ++k) { ms_by_kind[k] = 0.0; launches_by_kind[k] = 0; }
-    for (auto& u : pb::g_ev_used) {
+extern "C" void pb_profile_destroy(void* prof) { delete static_cast<pb::Profile*>(prof); }
+
+static int collect(void* prof, double* ms_by_kind, int64_t* launches_by_kind, int32_t* kinds, float* ms_each, int64_t cap,
+                   int64_t* n_out) {
+    PB_REQUIRE(prof != nullptr, "profile is null");
+    pb::Profile* p = static_cast<pb::Profile*>(prof);
+    std::lock_guard<std::mutex> lk(p->mu);
+    if (ms_by_kind)
+        for (int k = 0; k < pb::kProfKinds; ++k) { ms_by_kind[k] = 0.0; launches_by_kind[k] = 0; }
+    int64_t n = 0;
+    for (auto& u : p->used) {
         float ms = 0.f;
         cudaError_t e = cudaEventElapsedTime(&ms, u.second.first, u.second.second);
         if (e != cudaSuccess) return pb::fail_cuda(e, "cudaEventElapsedTime (synchronise the stream first)");
-        ms_by_kind[u.first] += ms;
-        launches_by_kind[u.first] += 1;
-        pb::g_ev_pool.push_back(u.second.first);
-        pb::g_ev_pool.push_back(u.second.second);
+        if (ms_by_kind) {
+            ms_by_kind[u.first] += ms;
+            launches_by_kind[u.first] += 1;
+        }
+        if (kinds && n < cap) {
+            kinds[n] = u.first;
+            ms_each[n] = ms;
+        }
+        ++n;
+        p->pool.push_back(u.second.first);
+        p->pool.push_back(u.second.second);
     }
-    pb::g_ev_used.clear();
+    p->used.clear();
+    if (n_out) *n_out = n;
     return PB_OK;
+}
+
+extern "C" int pb_profile_collect(void* prof, double* ms_by_kind, int64_t* launches_by_kind) {
+    PB_REQUIRE(ms_by_kind && launches_by_kind, "null argument");
+    return collect(prof, ms_by_kind, launches_by_kind, nullptr, nullptr, 0, nullptr);
+}
+
+extern "C" int pb_profile_collect_launches(void* prof, int32_t* kinds, float* ms, int64_t cap, int64_t* n_out) {
+    PB_REQUIRE(kinds && ms && n_out && cap >= 0, "null argument");
+    return collect(prof, nullptr, nullptr, kinds, ms, cap, n_out);
 }
 
 extern "C" int64_t pb_launch_count(void) { return (int64_t)pb::g_launches.load(); }

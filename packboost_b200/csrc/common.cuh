@@ -31,9 +31,17 @@ int fail_cuda(cudaError_t e, const char* what);
 // ---- optional in-stream timing of the kernel families and a launch counter -----------------
 
 enum ProfKind { kProfHist = 0, kProfScore = 1, kProfSelect = 2, kProfPartition = 3, kProfRound = 4, kProfKinds = 5 };
-void prof_begin(int kind, cudaStream_t stream);
-void prof_end(int kind, cudaStream_t stream);
+void prof_begin(void* prof, int kind, cudaStream_t stream);  // prof: pb_train_state.profile, may be null
+void prof_end(void* prof, int kind, cudaStream_t stream);
 void count_launch(int n);
+void nvtx_push(const char* fmt, long long a);  // PACKBOOST_NVTX=1: NVTX range around a phase
+void nvtx_pop();
+struct NvtxRange {  // range for the lifetime of the object
+    NvtxRange(const char* fmt, long long a) { nvtx_push(fmt, a); }
+    ~NvtxRange() { nvtx_pop(); }
+    NvtxRange(const NvtxRange&) = delete;
+    NvtxRange& operator=(const NvtxRange&) = delete;
+};
 
 #define PB_REQUIRE(cond, ...)                               \
     do {                                                    \
@@ -85,7 +93,14 @@ struct CtlHead {
     int32_t n_ctx[kMaxDepth + 2];
     int32_t any_dir[kMaxDepth + 2];
     uint32_t select_ticket;  // CTAs of the running select launch that have written their node (reset by the last)
+    uint32_t debug_flags;    // PB_DEBUG_BOUNDS builds: sticky bits of index violations seen by the kernels
 };
+
+// Bits of CtlHead::debug_flags (builds with -DPB_DEBUG_BOUNDS check the indices they are handed and
+// record a violation here instead of using the index; other builds never set them).
+constexpr uint32_t kDbgSlot = 1u;     // a row's frontier slot is neither "none" nor below the frontier's capacity
+constexpr uint32_t kDbgCode = 2u;     // a bin code is >= max_bins
+constexpr uint32_t kDbgFeature = 4u;  // a winner's feature id is outside the data set or not held by this device
 
 // Addresses of the sub-tables inside the caller's control block.
 struct Ctl {
@@ -156,6 +171,8 @@ struct HistLaunch {
     // into the per-threshold (gain, weight) rows and adds the left counts / gradient sums into the
     // era-summed tables, i.e. it does the work of the scorer's gain kernel.
     struct HistFuse* fuse;
+    void* prof;                  // pb_train_state.profile
+    uint32_t* debug_flags;       // &CtlHead::debug_flags, or nullptr
 };
 struct HistFuse {
     float2* gw;                  // [n_feat][n_eras][node_stride][n_thr]
@@ -199,6 +216,7 @@ struct ScoreLaunch {
     float2* gw;                  // [n_feat][n_eras][node_stride][n_thr] (gain, validity weight)
     uint32_t* lc_tot;            // [n_feat][node_stride][n_thr] left counts summed over eras
     int64_t* lg_tot;             // [n_feat][node_stride][n_thr] left gradient sums summed over eras
+    void* prof;                  // pb_train_state.profile
     int fused;                   // 1: gw and the totals were written by the histogram kernel's fused flush
     int tot_fpl, tot_lanes;      // layout of lc_tot / lg_tot (tot_index(); 0, 0: the classic layout above)
 };

@@ -395,6 +395,7 @@ struct PartArgs {
     int64_t n;
     uint32_t* bits;        // goleft_bits output
     const uint32_t* bits_in;  // apply_bits input
+    int n_features_total, n_features_local;
 };
 
 // mode 0: fused (decide + apply); mode 1: write go-left bits for locally held features;
@@ -436,6 +437,13 @@ __global__ void __launch_bounds__(kRowThreads) partition_kernel(PartArgs a) {
                 new_slot = kSlotNone;  // a slot past the frontier, or a node that does not split
                 if ((int)sl < n_ctx) {
                     const PartEntry pe = tab[sl];
+#ifdef PB_DEBUG_BOUNDS
+                    if (pe.feature >= a.n_features_total ||
+                        (MODE != 2 && pe.feature >= 0 && a.feat_local[pe.feature] >= a.n_features_local)) {
+                        atomicOr(&a.c.head->debug_flags, kDbgFeature);
+                        continue;
+                    }
+#endif
                     if (pe.feature >= 0) {
                         bool left = false;
                         if (MODE == 2) {
@@ -605,6 +613,8 @@ static HistLaunch hist_launch_of(const pb_train_state* st, int64_t depth, const 
     h.cnt = nullptr;
     h.gsum = nullptr;
     h.fuse = nullptr;
+    h.prof = st->profile;
+    h.debug_flags = &c.head->debug_flags;
     return h;
 }
 
@@ -686,6 +696,7 @@ static int hist_score_blocks(const pb_train_state* st, int64_t depth, const int3
         s.gw = reinterpret_cast<float2*>(scratch + plan.off_gw);
         s.lg_tot = reinterpret_cast<int64_t*>(scratch + plan.off_lg);
         s.lc_tot = reinterpret_cast<uint32_t*>(scratch + plan.off_lc);
+        s.prof = st->profile;
         s.fused = plan.fused ? 1 : 0;
         s.tot_fpl = plan.fused ? fz.tot_fpl : 0;
         s.tot_lanes = plan.fused ? fz.tot_lanes : 0;
@@ -735,19 +746,20 @@ extern "C" int pb_train_prepare(pb_train_state* st, const int32_t* era_offsets_h
 }
 
 extern "C" int pb_round_begin(const pb_train_state* st, int64_t apply_previous, void* stream_) {
+    NvtxRange nvtx("pb.round_begin apply=%lld", (long long)apply_previous);
     int rc = check_state(st);
     if (rc) return rc;
     cudaStream_t stream = (cudaStream_t)stream_;
     Ctl c = ctl_view(st->ctl);
     const int g = row_grid(st->n_rows);
-    prof_begin(kProfRound, stream);
+    prof_begin(st->profile, kProfRound, stream);
     round_reset_kernel<<<1, 32, 0, stream>>>(c);
     preds_absmax_kernel<<<g, kRowThreads, 0, stream>>>(st->preds, st->y, st->leaf, c.delta, st->n_rows,
                                                         apply_previous ? 1 : 0, c.head);
     quantise_kernel<<<g, kRowThreads, 0, stream>>>(st->preds, st->y, st->gq, st->slot, st->leaf, st->n_rows,
                                                     rows_padded(st->n_rows), c.head, (int)st->gq_bits);
     root_kernel<<<1, 32, 0, stream>>>(c, st->n_rows, (int)st->min_samples_leaf, st->lambda_l2, (int)st->gq_bits);
-    prof_end(kProfRound, stream);
+    prof_end(st->profile, kProfRound, stream);
     count_launch(4);
     PB_LAUNCH_CHECK("round_begin");
     return PB_OK;
@@ -775,6 +787,7 @@ extern "C" int pb_depth_clear_candidates(const pb_train_state* st, int64_t depth
 
 extern "C" int pb_depth_hist_score(const pb_train_state* st, int64_t depth, const int32_t* feat_rows,
                                    const int32_t* feat_pos, int64_t n_feat, int64_t n_sampled, void* stream_) {
+    NvtxRange nvtx("pb.hist_score d=%lld", (long long)depth);
     int rc = check_state(st);
     if (rc) return rc;
     rc = need_workspace(st, "pb_depth_hist_score");
@@ -806,6 +819,7 @@ extern "C" int pb_depth_select(const pb_train_state* st, int64_t depth, const in
 
 extern "C" int pb_depth_select_cand(const pb_train_state* st, int64_t depth, const int32_t* sampled_features,
                                     int64_t n_sampled, const void* cand, void* stream_) {
+    NvtxRange nvtx("pb.select d=%lld", (long long)depth);
     int rc = check_state(st);
     if (rc) return rc;
     PB_REQUIRE(depth >= 0 && depth < st->max_depth, "depth out of range");
@@ -826,9 +840,9 @@ extern "C" int pb_depth_select_cand(const pb_train_state* st, int64_t depth, con
     a.n_thr = (int)st->n_thresholds;
     a.min_leaf = (int)st->min_samples_leaf;
     a.lambda = st->lambda_l2;
-    prof_begin(kProfSelect, (cudaStream_t)stream_);
+    prof_begin(st->profile, kProfSelect, (cudaStream_t)stream_);
     select_kernel<<<(unsigned)a.node_stride, kSelThreads, 0, (cudaStream_t)stream_>>>(a);
-    prof_end(kProfSelect, (cudaStream_t)stream_);
+    prof_end(st->profile, kProfSelect, (cudaStream_t)stream_);
     count_launch(1);
     PB_LAUNCH_CHECK("select_kernel");
     return PB_OK;
@@ -837,6 +851,7 @@ extern "C" int pb_depth_select_cand(const pb_train_state* st, int64_t depth, con
 template <int MODE>
 static int launch_partition(const pb_train_state* st, int64_t depth, uint32_t* bits, const uint32_t* bits_in,
                             void* stream_) {
+    NvtxRange nvtx("pb.partition d=%lld", (long long)depth);
     int rc = check_state(st);
     if (rc) return rc;
     PB_REQUIRE(depth >= 0 && depth < st->max_depth, "depth out of range");
@@ -851,15 +866,17 @@ static int launch_partition(const pb_train_state* st, int64_t depth, uint32_t* b
     a.n = st->n_rows;
     a.bits = bits;
     a.bits_in = bits_in;
+    a.n_features_total = (int)st->n_features_total;
+    a.n_features_local = (int)st->n_features_local;
     const size_t smem = sizeof(PartEntry) * (size_t)(1 << depth);
     const int g = row_grid((st->n_rows + 7) / 8);  // a thread takes eight rows
     cudaStream_t stream = (cudaStream_t)stream_;
-    prof_begin(kProfPartition, stream);
+    prof_begin(st->profile, kProfPartition, stream);
     if (st->code_bits == 4)
         partition_kernel<4, MODE><<<g, kRowThreads, smem, stream>>>(a);
     else
         partition_kernel<8, MODE><<<g, kRowThreads, smem, stream>>>(a);
-    prof_end(kProfPartition, stream);
+    prof_end(st->profile, kProfPartition, stream);
     count_launch(1);
     PB_LAUNCH_CHECK("partition_kernel");
     return PB_OK;
@@ -880,6 +897,7 @@ extern "C" int pb_depth_apply_bits(const pb_train_state* st, int64_t depth, cons
 }
 
 extern "C" int pb_round_end(const pb_train_state* st, void* stream) {
+    NvtxRange nvtx("pb.round_end (pack of %lld)", st ? (long long)st->pack_size : 0ll);
     int rc = check_state(st);
     if (rc) return rc;
     delta_kernel<<<8, 256, 0, (cudaStream_t)stream>>>(ctl_view(st->ctl), (int)st->pack_size, (float)st->learning_rate);
@@ -896,6 +914,21 @@ extern "C" int pb_apply_leaf_delta(const pb_train_state* st, void* stream) {
                                                                                       st->n_rows);
     count_launch(1);
     PB_LAUNCH_CHECK("apply_delta_kernel");
+    return PB_OK;
+}
+
+extern "C" int pb_debug_bounds_enabled(void) {
+#ifdef PB_DEBUG_BOUNDS
+    return 1;
+#else
+    return 0;
+#endif
+}
+
+extern "C" int pb_debug_flags(const pb_train_state* st, uint32_t* flags_out) {
+    PB_REQUIRE(st && st->ctl && flags_out, "null argument");
+    Ctl c = ctl_view(st->ctl);
+    PB_CUDA_TRY(cudaMemcpy(flags_out, &c.head->debug_flags, sizeof(uint32_t), cudaMemcpyDeviceToHost));
     return PB_OK;
 }
 
@@ -933,6 +966,9 @@ extern "C" int pb_hist_build(const pb_train_state* st, const int32_t* feat_rows,
     h.max_arity = hist_max_arity();
     h.cnt = cnt;
     h.gsum = gsum;
+    h.fuse = nullptr;
+    h.prof = st->profile;
+    h.debug_flags = &ctl_view(st->ctl).head->debug_flags;
     return launch_hist(h, (cudaStream_t)stream);
 }
 
@@ -972,6 +1008,7 @@ extern "C" int64_t pb_static_scratch_bytes(void) { return (int64_t)kStaticScratc
 extern "C" int pb_depth_hist_score_static(const pb_train_state* st, int64_t depth, const int32_t* feat_rows,
                                           const int32_t* feat_pos, int64_t n_feat, int64_t n_sampled,
                                           void* cand_out, void* stream_) {
+    NvtxRange nvtx("pb.hist_score_static d=%lld", (long long)depth);
     int rc = check_state(st);
     if (rc) return rc;
     PB_REQUIRE(depth >= 0 && depth < st->max_depth, "depth out of range");

@@ -70,6 +70,7 @@ struct HistKernelArgs {
     int64_t* gsum;
     int fuse;        // 1: the lane kernel's flush writes gains and era-summed totals instead of the histogram
     HistFuse fz;
+    uint32_t* debug_flags;
 };
 
 template <int BITS, int THREADS>
@@ -173,6 +174,12 @@ __global__ void __launch_bounds__(THREADS) hist_kernel(HistKernelArgs a) {
                         code = (w[j >> 2] >> ((j & 3) * 8)) & 0xFF;
                     }
                     const uint32_t base = (cb2[j >> 1] >> ((j & 1) * 16)) & 0xFFFFu;
+#ifdef PB_DEBUG_BOUNDS
+                    if (base != 0xFFFFu && code >= nb) {
+                        if (a.debug_flags) atomicOr(a.debug_flags, kDbgCode);
+                        continue;
+                    }
+#endif
                     if (base != 0xFFFFu) {
                         uint32_t* cell = fc + (size_t)(base + code) * copies;
                         atomicAdd(cell, (((uint32_t)g[j] & lo_mask) << CB) + 1u);
@@ -348,6 +355,10 @@ __global__ void __launch_bounds__(kLaneWarps * 32, 2) hist_lane_kernel(HistKerne
         for (int h = 0; h < 2; ++h) {
             const int r = c * kLaneRows + 2 * lane + h;
             const bool ok = (r >= r0) & (r < r1) & (raw_s[h] < n_nodes);
+#ifdef PB_DEBUG_BOUNDS
+            if ((r >= r0) & (r < r1) & (raw_s[h] != (int)kSlotNone) & (raw_s[h] >= a.n_nodes) && a.debug_flags)
+                atomicOr(a.debug_flags, kDbgSlot);
+#endif
             any_ok |= ok;
             // a row that is not accumulated adds zero to the cells of node 0: the row steps below
             // carry no branch, so the rows of a batch and the tuples of a lane interleave freely.
@@ -385,6 +396,17 @@ __global__ void __launch_bounds__(kLaneWarps * 32, 2) hist_lane_kernel(HistKerne
                         for (int t = 0; t < T; ++t) {
                             // joint code of the tuple, pre-scaled by the cell pitch (256 bytes)
                             const uint32_t w0 = w[t * A][j >> 3];
+#ifdef PB_DEBUG_BOUNDS
+                            if (rec[q].y | rec[q].z | (raw[q].x & 1u)) {  // an accumulated row: its codes must be bins
+                                bool bad = ((w0 >> bit) & 0xFu) >= (uint32_t)nb;
+#pragma unroll
+                                for (int i = 1; i < A; ++i) bad |= ((w[t * A + i][j >> 3] >> bit) & 0xFu) >= (uint32_t)nb;
+                                if (bad && A * t < n_mine) {
+                                    if (a.debug_flags) atomicOr(a.debug_flags, kDbgCode);
+                                    continue;
+                                }
+                            }
+#endif
                             uint32_t off = (bit >= 8) ? ((w0 >> (bit - 8)) & 0xF00u) : ((w0 << (8 - bit)) & 0xF00u);
                             uint32_t mul = nb_scaled;
 #pragma unroll
@@ -747,6 +769,7 @@ int launch_hist(const HistLaunch& h, cudaStream_t stream) {
     a.lo_bits = h.lo_bits;
     a.fuse = 0;
     memset(&a.fz, 0, sizeof(a.fz));
+    a.debug_flags = h.debug_flags;
 
     const int rpi = (h.code_bits == 4) ? 32 : 16;
     a.tile_rows = kTileRowsMax;
@@ -822,12 +845,12 @@ int launch_hist(const HistLaunch& h, cudaStream_t stream) {
         } else if (h.fuse) {
             return fail_arg("fused flush requested for a launch that cannot fuse (check hist_can_fuse first)");
         }
-        prof_begin(kProfHist, stream);
+        prof_begin(h.prof, kProfHist, stream);
         int rc;
         if (arity == 2) rc = (tuples == 2) ? launch_lane<2, 2>(a, smem, phases, stream) : launch_lane<2, 1>(a, smem, phases, stream);
         else rc = (tuples == 4) ? launch_lane<1, 4>(a, smem, phases, stream)
                   : (tuples == 2) ? launch_lane<1, 2>(a, smem, phases, stream) : launch_lane<1, 1>(a, smem, phases, stream);
-        prof_end(kProfHist, stream);
+        prof_end(h.prof, kProfHist, stream);
         if (rc) return rc;
         count_launch(1);
         PB_LAUNCH_CHECK("hist_lane_kernel");
@@ -868,7 +891,7 @@ int launch_hist(const HistLaunch& h, cudaStream_t stream) {
     const size_t smem = (size_t)group * per_feat * copies * 2 * sizeof(uint32_t);
     dim3 grid((unsigned)n_tiles, (unsigned)((h.n_feat + feats_per_cta - 1) / feats_per_cta), (unsigned)chunks);
     if (grid.y > 65535u || grid.z > 65535u) return fail_arg("histogram grid too large");
-    prof_begin(kProfHist, stream);
+    prof_begin(h.prof, kProfHist, stream);
     if (h.code_bits == 4) {
         if (smem > 48 * 1024)
             PB_CUDA_TRY(cudaFuncSetAttribute(hist_kernel<4, 256>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
@@ -878,7 +901,7 @@ int launch_hist(const HistLaunch& h, cudaStream_t stream) {
             PB_CUDA_TRY(cudaFuncSetAttribute(hist_kernel<8, 512>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         hist_kernel<8, 512><<<grid, threads, smem, stream>>>(a);
     }
-    prof_end(kProfHist, stream);
+    prof_end(h.prof, kProfHist, stream);
     count_launch(1);
     PB_LAUNCH_CHECK("hist_kernel");
     return PB_OK;

@@ -805,7 +805,7 @@ int launch_score(const ScoreLaunch& s, cudaStream_t stream) {
         PB_CUDA_TRY(cudaMemsetAsync(s.lg_tot, 0, tot_cells * sizeof(int64_t), stream));
     }
 
-    prof_begin(kProfScore, stream);
+    prof_begin(s.prof, kProfScore, stream);
     GainArgs g;
     g.s = s;
     if (s.fused) {
@@ -886,7 +886,7 @@ int launch_score(const ScoreLaunch& s, cudaStream_t stream) {
         const int threads = ((npc * K + 31) / 32) * 32;
         chain_kernel<<<grid, threads, smem, stream>>>(c);
     }
-    prof_end(kProfScore, stream);
+    prof_end(s.prof, kProfScore, stream);
     count_launch(s.fused ? 1 : 2);
     PB_LAUNCH_CHECK("chain_kernel");
     return PB_OK;
