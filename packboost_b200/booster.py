@@ -813,7 +813,7 @@ class PackBoost:
                 torch.randperm(self._fit_ctx["F"], generator=self._rng)
             self._predrawn = None
         k = self._trainer.n_sampled()
-        phase_ms = self._trainer.profile_by_depth() if self._trainer.prof is not None else []
+        phase_ms = self._trainer.profile_by_depth() if getattr(self._trainer, "prof", None) is not None else []
         for d in range(used):
             self._depth_logs.append(self._depth_log(d, n_ctx[d], k, phase_ms[d] if d < len(phase_ms) else None))
             w = winners[(1 << d) - 1: (1 << d) - 1 + n_ctx[d]]
