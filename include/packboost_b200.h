@@ -71,7 +71,8 @@ int pb_device_count(void);
  * capture).  After synchronising, pb_profile_collect returns per family (0 histogram, 1 scorer,
  * 2 select, 3 partition, 4 round begin/end) the summed milliseconds and the number of bracketed
  * launches; pb_profile_collect_launches returns the launches one by one in issue order (family and
- * milliseconds, at most `cap`; `*n_out` is how many there were).  Both clear the record.  States
+ * milliseconds, at most `cap`; `*n_out` is how many there were).  Both take the launches that have
+ * finished, in issue order up to the first unfinished one, and remove them from the record.  States
  * with different profile objects may run concurrently.  pb_launch_count is the number of kernels
  * this library launched since it was loaded.  With PACKBOOST_NVTX=1 in the environment every phase
  * entry point opens an NVTX range ("pb.hist_score d=3", ...) for tools that attach to the process. */
@@ -263,6 +264,28 @@ int pb_depth_partition(const pb_train_state* st, int64_t depth, void* stream);
  * of `bits` every device applies them. */
 int pb_depth_goleft_bits(const pb_train_state* st, int64_t depth, uint32_t* bits, void* stream);
 int pb_depth_apply_bits(const pb_train_state* st, int64_t depth, const uint32_t* bits, void* stream);
+
+/* ---- cross-device exchange (several devices, features sharded) ----------------------------------
+ * The reference is single-device and has nothing to cite here.  With the sampled features of a
+ * depth split over several devices, each device fills the candidate entries of its own features
+ * (pb_depth_clear_candidates first) and the tables are merged by a SUM all-reduce over their
+ * int32 words (entries are disjoint); in the memory-sharded layout the go-left bits are merged the
+ * same way (disjoint bits: SUM is OR).  These entry points do that on NCCL, on the caller's stream,
+ * for hosts that have no collective library of their own (a framework that already holds a
+ * communicator can all-reduce the buffers itself).  NCCL is looked up at run time; without it they
+ * return PB_ERR_ARG and say so.  Usage: one rank calls pb_comm_unique_id and hands the
+ * PB_COMM_ID_BYTES bytes to the others by whatever means the host has, every rank calls
+ * pb_comm_init with its device current, then per depth pb_comm_allreduce_candidates between
+ * pb_depth_hist_score and pb_depth_select (and pb_comm_allreduce_mask between pb_depth_goleft_bits
+ * and pb_depth_apply_bits).  A failure of an earlier collective (for instance a peer that left) is
+ * reported by the next call as an error code.  pb_comm_destroy after the last collective has
+ * finished. */
+#define PB_COMM_ID_BYTES 128
+int pb_comm_unique_id(void* id_out /* PB_COMM_ID_BYTES */);
+int pb_comm_init(void** comm_out, const void* unique_id, int64_t n_ranks, int64_t rank);
+int pb_comm_allreduce_candidates(void* comm, const pb_train_state* st, int64_t depth, int64_t n_sampled, void* stream);
+int pb_comm_allreduce_mask(void* comm, uint32_t* bits, int64_t n_words, void* stream);
+int pb_comm_destroy(void* comm);
 
 /* End of a round: finish the leaf-delta table (pack aggregation, packboost/booster.py:
  * 582-598: every one of the B identical trees adds its float32 leaf value, scaled by the

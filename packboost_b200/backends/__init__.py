@@ -93,6 +93,11 @@ _PROTOS: dict[str, tuple[Any, list[Any]]] = {
     "pb_depth_partition": (C.c_int, [C.POINTER(TrainState), i64, vp]),
     "pb_depth_goleft_bits": (C.c_int, [C.POINTER(TrainState), i64, vp, vp]),
     "pb_depth_apply_bits": (C.c_int, [C.POINTER(TrainState), i64, vp, vp]),
+    "pb_comm_unique_id": (C.c_int, [vp]),
+    "pb_comm_init": (C.c_int, [C.POINTER(vp), vp, i64, i64]),
+    "pb_comm_allreduce_candidates": (C.c_int, [vp, C.POINTER(TrainState), i64, i64, vp]),
+    "pb_comm_allreduce_mask": (C.c_int, [vp, vp, i64, vp]),
+    "pb_comm_destroy": (C.c_int, [vp]),
     "pb_round_end": (C.c_int, [C.POINTER(TrainState), vp]),
     "pb_apply_leaf_delta": (C.c_int, [C.POINTER(TrainState), vp]),
     "pb_era_correlation": (C.c_int, [vp, vp, vp, i64, vp, vp]),

@@ -290,7 +290,22 @@ class _DeviceTrainer:
         self.graph_replays = 0
         self.pending_delta = False
         self.prof = None
+        # PACKBOOST_COMM=native: the per-depth exchanges go through the library's own NCCL entry
+        # points (pb_comm_*) instead of torch.distributed; the communicator id is handed round once
+        self.comm = None
+        if world > 1 and os.getenv("PACKBOOST_COMM") == "native":
+            ident = torch.zeros(128, dtype=torch.uint8, device=self.dev)
+            if rank == 0:
+                raw = (C.c_ubyte * 128)()
+                B.check(self.lib.pb_comm_unique_id(raw))
+                ident.copy_(torch.tensor(list(raw), dtype=torch.uint8))
+            torch.distributed.broadcast(ident, src=0)
+            raw = (C.c_ubyte * 128)(*ident.cpu().tolist())
+            comm = C.c_void_p()
+            B.check(self.lib.pb_comm_init(C.byref(comm), raw, world, rank))
+            self.comm = comm
         self._prof_ms, self._prof_n = [0.0] * 5, [0] * 5
+        self._prof_queue: list[tuple[int, float]] = []
 
     # -- per-phase timing (the reference fills hist_ms / score_ms / partition_ms of its depth logs
     #    with perf_counter buckets, packboost/booster.py:220-270) --------------------------------
@@ -311,6 +326,9 @@ class _DeviceTrainer:
             self.prof = None
 
     def __del__(self):
+        import sys
+        if sys.is_finalizing():   # (the CUDA context may be gone already; the process is ending anyway)
+            return
         try:
             self.disable_profile()
         except Exception:
@@ -327,29 +345,37 @@ class _DeviceTrainer:
         return tot_ms, tot_n
 
     def profile_by_depth(self) -> list[dict[str, float]]:
-        """Milliseconds per depth of the rounds since the last collection: the launches come back in
-        issue order, a histogram launch after a select launch opens the next depth."""
+        """Milliseconds per depth of the oldest round whose launches have not been handed out yet.
+        The library returns finished launches in issue order; a round opens with its round-begin
+        bracket, and within it a histogram launch after a select launch opens the next depth.  The
+        host may be enqueuing a round ahead: launches of later rounds stay queued here."""
         cap = 4096
         kinds, ms, n = (C.c_int32 * cap)(), (C.c_float * cap)(), C.c_int64()
         B.check(self.lib.pb_profile_collect_launches(self.prof, kinds, ms, cap, C.byref(n)))
-        out: list[dict[str, float]] = []
-        cur = None
-        seen_select = True
-        names = {0: "hist_ms", 1: "score_ms", 2: "select_ms", 3: "partition_ms"}
         for i in range(min(int(n.value), cap)):
             k = int(kinds[i])
             self._prof_ms[k] += float(ms[i])   # (kept for profile_totals)
             self._prof_n[k] += 1
-            if k == 4:
-                seen_select = True
-                continue
+            self._prof_queue.append((k, float(ms[i])))
+        q = self._prof_queue
+        while q and q[0][0] != 4:              # leftovers of a round that was handed out already
+            q.pop(0)
+        if not q:
+            return []
+        end = next((i for i in range(1, len(q)) if q[i][0] == 4), len(q))
+        mine, self._prof_queue = q[1:end], q[end:]
+        out: list[dict[str, float]] = []
+        cur = None
+        seen_select = True
+        names = {0: "hist_ms", 1: "score_ms", 2: "select_ms", 3: "partition_ms"}
+        for k, t in mine:
             if k == 0 and seen_select:
                 cur = {"hist_ms": 0.0, "score_ms": 0.0, "select_ms": 0.0, "partition_ms": 0.0}
                 out.append(cur)
                 seen_select = False
             if cur is None:
                 continue
-            cur[names[k]] += float(ms[i])
+            cur[names[k]] += t
             if k == 2:
                 seen_select = True
         return out
@@ -413,6 +439,12 @@ class _DeviceTrainer:
         self.graph, self.graph_signature = graph, signature
         self.graph_launches = int(self.lib.pb_launch_count()) - before  # kernels per replay
 
+    def close_comm(self) -> None:
+        if self.comm is not None:
+            torch.cuda.current_stream().synchronize()
+            B.check(self.lib.pb_comm_destroy(self.comm))
+            self.comm = None
+
     def release_graph(self) -> None:
         """Drop the captured round graph (it is captured again if more rounds are enqueued)."""
         if self.graph is not None:
@@ -446,13 +478,20 @@ class _DeviceTrainer:
             B.check(lib.pb_depth_select(st, d, sampled, k, stream))
             if self.world > 1 and not self.replicated:
                 B.check(lib.pb_depth_goleft_bits(st, d, self.bits.data_ptr(), stream))
-                torch.distributed.all_reduce(self.bits, op=torch.distributed.ReduceOp.SUM)
+                if self.comm is not None:
+                    B.check(lib.pb_comm_allreduce_mask(self.comm, self.bits.data_ptr(), self.bits.numel(), stream))
+                else:
+                    torch.distributed.all_reduce(self.bits, op=torch.distributed.ReduceOp.SUM)
                 B.check(lib.pb_depth_apply_bits(st, d, self.bits.data_ptr(), stream))
             else:
                 B.check(lib.pb_depth_partition(st, d, stream))
         B.check(lib.pb_round_end(st, stream))
 
     def _allreduce_candidates(self, depth: int, k: int) -> None:
+        if self.comm is not None:
+            B.check(self.lib.pb_comm_allreduce_candidates(self.comm, C.byref(self.st), depth, k,
+                                                          torch.cuda.current_stream().cuda_stream))
+            return
         ptr, nbytes = C.c_void_p(), C.c_int64()
         B.check(self.lib.pb_candidates_buffer(C.byref(self.st), depth, k, C.byref(ptr), C.byref(nbytes)))
         off = ptr.value - self.workspace.data_ptr()
@@ -836,6 +875,7 @@ class PackBoost:
         self._trainer.release_graph()
         self._trainer.flush_predictions()
         torch.cuda.current_stream().synchronize()
+        self._trainer.close_comm()
 
     def train_predictions(self) -> np.ndarray:
         """Predictions of the training rows as maintained during ``fit`` (original row order)."""

@@ -17,7 +17,7 @@ CSRC = os.path.join(HERE, "csrc")
 LIB_NAME = "libpackboost_b200.so"
 LIB_PATH = os.path.join(HERE, LIB_NAME)
 
-SOURCES = ["api.cu", "hist.cu", "score.cu", "frontier.cu", "pack.cu", "predict.cu", "metrics.cu"]
+SOURCES = ["api.cu", "hist.cu", "score.cu", "frontier.cu", "pack.cu", "predict.cu", "metrics.cu", "comm.cu"]
 # The scorer, and the histogram kernel whose flush computes the per-era gains, must round every
 # product and sum separately (no fused multiply-add) to keep the float32 operation order of the
 # algorithm they implement.
@@ -69,7 +69,7 @@ def build(force: bool = False, verbose: bool = False, debug_bounds: bool = False
                 sys.stderr.write(res.stdout + res.stderr)
                 raise RuntimeError(f"nvcc failed on {src}")
     if force or _stale(lib_path, objs):
-        cmd = [nvcc, "-shared", "-o", lib_path] + objs + ARCH
+        cmd = [nvcc, "-shared", "-o", lib_path] + objs + ARCH + ["-ldl"]
         res = subprocess.run(cmd, capture_output=True, text=True)
         if res.returncode != 0:
             sys.stderr.write(res.stdout + res.stderr)

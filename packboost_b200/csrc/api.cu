@@ -124,10 +124,15 @@ static int collect(void* prof, double* ms_by_kind, int64_t* launches_by_kind, in
     if (ms_by_kind)
         for (int k = 0; k < pb::kProfKinds; ++k) { ms_by_kind[k] = 0.0; launches_by_kind[k] = 0; }
     int64_t n = 0;
+    size_t taken = 0;
     for (auto& u : p->used) {
+        // launches come back in issue order; the first one that has not finished yet ends the batch
+        // (the caller may be enqueuing ahead of the device) and stays for the next collection
+        if (cudaEventQuery(u.second.second) == cudaErrorNotReady) break;
         float ms = 0.f;
         cudaError_t e = cudaEventElapsedTime(&ms, u.second.first, u.second.second);
-        if (e != cudaSuccess) return pb::fail_cuda(e, "cudaEventElapsedTime (synchronise the stream first)");
+        if (e != cudaSuccess) return pb::fail_cuda(e, "cudaEventElapsedTime");
+        ++taken;
         if (ms_by_kind) {
             ms_by_kind[u.first] += ms;
             launches_by_kind[u.first] += 1;
@@ -140,7 +145,7 @@ static int collect(void* prof, double* ms_by_kind, int64_t* launches_by_kind, in
         p->pool.push_back(u.second.first);
         p->pool.push_back(u.second.second);
     }
-    p->used.clear();
+    p->used.erase(p->used.begin(), p->used.begin() + (long)taken);
     if (n_out) *n_out = n;
     return PB_OK;
 }

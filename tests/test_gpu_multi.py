@@ -22,9 +22,10 @@ def _free_port():
     return p
 
 
-def _worker(rank, world, port, name, shard, out):
+def _worker(rank, world, port, name, shard, out, comm="torch"):
     import torch.distributed as dist
     os.environ["PACKBOOST_SHARD_CODES"] = "1" if shard else "0"
+    os.environ["PACKBOOST_COMM"] = comm
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
     torch.cuda.set_device(rank)
@@ -40,11 +41,14 @@ def _worker(rank, world, port, name, shard, out):
     dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("name,shard", [("prebinned5", True), ("prebinned5", False), ("ragged_eras", True),
-                                        ("dro_direction", False)])
-def test_two_gpu_fit_equals_one_gpu_fit(name, shard):
+@pytest.mark.parametrize("name,shard,comm", [("prebinned5", True, "torch"), ("prebinned5", False, "torch"),
+                                             ("ragged_eras", True, "torch"), ("dro_direction", False, "torch"),
+                                             ("prebinned5", True, "native"), ("config1", False, "native")])
+def test_two_gpu_fit_equals_one_gpu_fit(name, shard, comm):
     """`shard`: every rank holds only its own feature rows and the go-left bitmask is exchanged;
-    otherwise the packed matrix is replicated and only the candidate table is exchanged."""
+    otherwise the packed matrix is replicated and only the candidate table is exchanged.
+    `comm`: the exchanges go through torch.distributed, or through the library's own NCCL entry
+    points (pb_comm_*)."""
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
     import torch.multiprocessing as mp
@@ -55,7 +59,7 @@ def test_two_gpu_fit_equals_one_gpu_fit(name, shard):
     off1, cols1 = flatten_trees(single.trees)
     p1, h1 = single.train_predictions(), single.predict(Xh)
     out = mp.Manager().dict()
-    mp.spawn(_worker, args=(2, _free_port(), name, shard, out), nprocs=2, join=True)
+    mp.spawn(_worker, args=(2, _free_port(), name, shard, out, comm), nprocs=2, join=True)
     for rank in range(2):
         off, cols, p, h = out[rank]
         np.testing.assert_array_equal(off, off1)

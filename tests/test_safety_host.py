@@ -139,3 +139,23 @@ def test_a_state_without_workspace_is_accepted_and_workspace_entries_say_so(lib)
     st.workspace_bytes = 16            # a pointer with too few bytes still is, too
     with pytest.raises(ValueError, match="workspace too small"):
         B.check(lib.pb_train_prepare(C.byref(st), eo.ctypes.data))
+
+
+def test_comm_entries_validate_their_arguments_without_a_gpu(lib):
+    """The NCCL-backed exchange entries refuse bad arguments before touching NCCL or a device."""
+    from packboost_b200 import backends as B
+    comm = C.c_void_p()
+    ident = (C.c_ubyte * 128)()
+    for n_ranks, rank in ((0, 0), (2, 2), (2, -1)):
+        with pytest.raises(ValueError, match="out of range"):
+            B.check(lib.pb_comm_init(C.byref(comm), ident, n_ranks, rank))
+    with pytest.raises(ValueError, match="null"):
+        B.check(lib.pb_comm_init(None, ident, 2, 0))
+    with pytest.raises(ValueError, match="null"):
+        B.check(lib.pb_comm_unique_id(None))
+    with pytest.raises(ValueError, match="communicator is null"):
+        B.check(lib.pb_comm_allreduce_mask(None, 1 << 20, 16, None))
+    st = _state(B)
+    with pytest.raises(ValueError, match="communicator is null"):
+        B.check(lib.pb_comm_allreduce_candidates(None, C.byref(st), 0, 4, None))
+    assert lib.pb_comm_destroy(None) == 0
