@@ -156,7 +156,11 @@ typedef struct pb_train_state {
                                     taken per depth at the quantiles of its bin masses over the frontier rows
                                     (packboost/backends/cpu/frontier_cpu.cpp:59-109); thr_ids is then unused */
     void* profile;               /* pb_profile_create() object, or NULL: see "Instrumentation" */
-    int64_t reserved[1];
+    int64_t direction_form;      /* directional term of the score (direction_weight != 0): 0 = agreement of the two
+                                    child directions with the parent's, the torch frontier's form
+                                    (packboost/booster.py:1811-1815, 1873-1880); 1 = +1 where the left child value
+                                    exceeds the right one, else -1, the form of the reference's helper and native
+                                    code (packboost/booster.py:869-907, backends/cpu/frontier_cpu.cpp:395-401) */
 } pb_train_state;
 
 /* Index checks for debugging (the reference checks its inputs on the host,

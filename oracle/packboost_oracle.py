@@ -69,6 +69,11 @@ class OracleParams:
     # frontier rows).  With this switch the oracle takes the thresholds the C++ code would take and
     # scores them with the torch frontier's arithmetic, instead of raising.
     native_mass_cuts: bool = False
+    # Directional term: "frontier" is the torch frontier's agreement of the child directions with
+    # the parent's (``booster.py:1811-1815, 1873-1880``); "helper" is the +1 / -1 form of the
+    # reference's ``_directional_agreement`` helper and of its native code (``booster.py:869-907``,
+    # ``backends/cpu/frontier_cpu.cpp:395-401``), which the torch frontier never uses.
+    direction_form: str = "frontier"
     # ``max_bins`` above 128 is refused by the reference (int8 storage,
     # ``packboost/booster.py:394-395``, ``packboost/data.py:47-48``).  The
     # widened oracle stores codes as int16 instead and is otherwise identical.
@@ -542,7 +547,8 @@ def find_splits(
         mean = torch.zeros_like(wsum)
         m2 = torch.zeros_like(wsum)
         lc_all = torch.zeros((Bb, Nn, K), dtype=cnt.dtype)
-        use_dir = (dir_w != 0.0) and bool((P_dir != 0).any())
+        helper_dir = p.direction_form == "helper"
+        use_dir = (dir_w != 0.0) and (helper_dir or bool((P_dir != 0).any()))
         if use_dir:
             a_num = torch.zeros_like(wsum)
             a_den = torch.zeros_like(wsum)
@@ -578,7 +584,10 @@ def find_splits(
             if use_dir:
                 vl = -lg / dl
                 vr = -rg / dr
-                agree = 0.5 * ((torch.sign(vl) == pa).float() + (torch.sign(vr) == pa).float())
+                if helper_dir:
+                    agree = torch.where(vl > vr, torch.ones_like(vl), -torch.ones_like(vl))
+                else:
+                    agree = 0.5 * ((torch.sign(vl) == pa).float() + (torch.sign(vr) == pa).float())
                 a_num = a_num + w_full * agree
                 a_den = a_den + w_full
             lc_all = lc_all + lc

@@ -60,7 +60,7 @@ class TrainState(C.Structure):
         ("preds", vp), ("gq", vp), ("slot", vp), ("leaf", vp), ("ctl", vp), ("workspace", vp),
         ("workspace_bytes", i64),
         ("max_era_rows", i64), ("hist_rows_per_tile", i64), ("gq_bits", i64), ("count_bits", i64),
-        ("lo_bits", i64), ("cut_mass", i64), ("profile", vp), ("reserved", i64 * 1),
+        ("lo_bits", i64), ("cut_mass", i64), ("profile", vp), ("direction_form", i64),
     ]
 
 

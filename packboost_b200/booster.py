@@ -230,6 +230,9 @@ class _DeviceTrainer:
         st.n_thresholds = int(thr.shape[0])
         st.feature_block_size = int(cfg.feature_block_size)
         st.cut_mass = 1 if self.cut_mass else 0
+        # PACKBOOST_DIRECTION_FORM=helper: the +1 / -1 directional term of the reference's helper and
+        # native code instead of the torch frontier's agreement with the parent direction
+        st.direction_form = 1 if os.getenv("PACKBOOST_DIRECTION_FORM") == "helper" else 0
         st.lambda_l2 = float(cfg.lambda_l2)
         st.lambda_dro = float(cfg.lambda_dro)
         st.direction_weight = float(cfg.direction_weight)

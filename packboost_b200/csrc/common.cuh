@@ -210,6 +210,7 @@ struct ScoreLaunch {
     const int32_t* thr_ids;      // [n_thr] ascending bin ids, or [n_feat][n_thr] with thr_per_feature
     int thr_per_feature;         // 1: every feature of the block has its own threshold list (mass cuts)
     float lambda_l2, lambda_dro, direction_weight, era_alpha;
+    int direction_form;          // 0: agreement with the parent's direction, 1: +1 / -1 by comparing the child values
     int min_samples_leaf;
     Cand* cand;                  // [n_sampled][node_stride]
     // scratch of the two-kernel scorer, for the n_feat features of this block

@@ -690,6 +690,7 @@ static int hist_score_blocks(const pb_train_state* st, int64_t depth, const int3
         s.lambda_l2 = (float)st->lambda_l2;
         s.lambda_dro = (float)st->lambda_dro;
         s.direction_weight = (float)st->direction_weight;
+        s.direction_form = st->direction_form ? 1 : 0;
         s.era_alpha = (float)(st->era_alpha > 0.0 ? st->era_alpha : 0.0);
         s.min_samples_leaf = (int)st->min_samples_leaf;
         s.cand = cand;

@@ -401,7 +401,9 @@ __global__ void __launch_bounds__(kChainThreads) chain_kernel(ChainArgs a) {
     const int f = blockIdx.x;
     const int E = s.n_eras, K = s.n_thr;
     const float lam = s.lambda_l2;
-    const bool use_dir = (s.direction_weight != 0.f) && (*s.any_dir_ptr != 0);
+    // (the parent-agreement form drops the term when no frontier node has a direction at all; the
+    // comparing form depends on the children only)
+    const bool use_dir = (s.direction_weight != 0.f) && (s.direction_form == 1 || *s.any_dir_ptr != 0);
 
     // shared layout: res_lg int64 [npc*K] | staged table float2 [2][EC][npc*K] | res_score, res_cnt
     const int npck = npc * K;
@@ -507,8 +509,9 @@ __global__ void __launch_bounds__(kChainThreads) chain_kernel(ChainArgs a) {
                 const float lh = (float)lc, th = (float)tc;
                 const float vl = f_div(-lg, f_add(lh, lam));
                 const float vr = f_div(-f_sub(tg, lg), f_add(f_sub(th, lh), lam));
-                const float agree =
-                    f_mul(0.5f, f_add((sign_of(vl) == pa) ? 1.f : 0.f, (sign_of(vr) == pa) ? 1.f : 0.f));
+                const float agree = (s.direction_form == 1)
+                    ? ((vl > vr) ? 1.f : -1.f)
+                    : f_mul(0.5f, f_add((sign_of(vl) == pa) ? 1.f : 0.f, (sign_of(vr) == pa) ? 1.f : 0.f));
                 a_num = f_add(a_num, f_mul(w, agree));
                 a_den = f_add(a_den, w);
             }

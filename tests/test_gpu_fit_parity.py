@@ -441,3 +441,24 @@ def test_mass_k_cuts_match_the_compiled_reference_and_the_oracle(name, k):
             np.testing.assert_array_equal(cols_g[key], cols_r[key], err_msg=f"compiled reference: {key}")
         scale = np.abs(ref.train_preds).max()
         np.testing.assert_allclose(booster.train_predictions(), ref.train_preds, rtol=1e-5, atol=1e-5 * scale)
+
+
+@pytest.mark.parametrize("name", ["dro_direction", "interleaved"])
+def test_helper_form_direction_term_matches_the_oracle(name, monkeypatch):
+    """``PACKBOOST_DIRECTION_FORM=helper``: the ``+1 / -1`` directional term of the reference's helper
+    and native code (``packboost/booster.py:869-907``) instead of the torch frontier's agreement
+    with the parent direction; bit-identical to the oracle's restatement of that form."""
+    monkeypatch.setenv("PACKBOOST_DIRECTION_FORM", "helper")
+    X, y, era, cfg, rounds, Xh = cases.CASES[name]()
+    cfg = dict(cfg)
+    cfg.update(direction_weight=0.2)
+    model = po.fit(X, y, era, po.OracleParams(exact_sums=True, direction_form="helper", **cfg), rounds, record_depths=True)
+    booster = _fit_gpu(X, y, era, cfg, rounds)
+    off_o, cols_o = flatten_oracle(model.trees)
+    off_g, cols_g = flatten_trees(booster.trees)
+    np.testing.assert_array_equal(off_g, off_o)
+    for key in ("feature", "threshold", "left", "right", "is_leaf"):
+        np.testing.assert_array_equal(cols_g[key], cols_o[key], err_msg=key)
+    np.testing.assert_array_equal(booster.split_records()["score"].view(np.int32),
+                                  np.asarray([r["score"] for r in model.depth_records], dtype=np.float32).view(np.int32))
+    np.testing.assert_array_equal(booster.train_predictions().view(np.int32), model.train_preds.view(np.int32))

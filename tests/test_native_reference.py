@@ -52,3 +52,16 @@ def test_mass_and_even_cut_helpers_on_hand_cases():
     assert po.mass_cuts_native(np.array([0, 0, 100, 0, 0]), 5, 3) == [0, 1, 2]
     assert po.mass_cuts_native(np.array([10, 10, 10, 10, 10]), 5, 4) == [0, 1, 2, 3]
     assert po.mass_cuts_native(np.zeros(5, dtype=np.int64), 5, 2) == [0, 3]
+
+
+@pytest.mark.parametrize("name", ["dro_direction", "config1", "interleaved"])
+def test_helper_form_direction_term_is_pinned_by_the_compiled_split_finder(name):
+    """The ``+1 / -1`` directional term (``packboost/booster.py:869-907``) runs in the reference's
+    native code (``frontier_cpu.cpp:395-401``), never in its torch frontier; the oracle's
+    ``direction_form="helper"`` must grow the same trees as the compiled split finder."""
+    X, y, era, cfg, rounds, _ = cases.CASES[name]()
+    cfg = dict(cfg)
+    cfg.update(direction_weight=0.2)
+    a = po.fit(X, y, era, po.OracleParams(direction_form="helper", **cfg), min(rounds, 3))
+    b = native_ref.fit(X, y, era, po.OracleParams(**cfg), min(rounds, 3))
+    _same_structure(a, b)
