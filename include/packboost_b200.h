@@ -346,6 +346,30 @@ typedef struct pb_round_log_header {
 int pb_hist_build(const pb_train_state* st, const int32_t* feat_rows, int64_t n_feat,
                   int64_t n_nodes, int64_t node_stride, uint32_t* cnt, int64_t* gsum, void* stream);
 
+/* Best threshold of every feature for ONE node with general (per-row) hessians: the single-node
+ * form of the frontier (`PackBoost._find_best_split`, packboost/booster.py:1010-1290, exercised by
+ * the reference's hand-built DES test, tests/test_des.py:9-217).  `cnt` / `gsum` / `hsum` are the
+ * node's histograms `[n_feat][n_eras][max_bins]` (two pb_hist_build passes with node_stride 1: the
+ * second with the fixed-point hessians in place of the gradients); `inv_scale_g` / `inv_scale_h`
+ * turn the integer sums back into float32; `total_count` / `total_gq` are the node's row count and
+ * fixed-point gradient sum.  The training loop does not use this entry (the squared loss has unit
+ * hessians).  `out[f]` receives the feature's best threshold under (score, left count, index). */
+typedef struct pb_split_general {
+    float score;
+    int32_t k;            /* index into thr_ids, -1: none */
+    int32_t threshold;    /* bin id */
+    int32_t has_nan;      /* a threshold of this feature scored NaN */
+    int64_t left_count;
+    int64_t left_gq;      /* fixed-point sums of the left child */
+    int64_t left_hq;
+} pb_split_general;
+int pb_score_node_general(const uint32_t* cnt, const int64_t* gsum, const int64_t* hsum, int64_t n_feat,
+                          int64_t n_eras, int64_t max_bins, const int32_t* thr_ids, int64_t n_thresholds,
+                          float inv_scale_g, float inv_scale_h, float lambda_l2, float lambda_dro,
+                          float direction_weight, float era_alpha, int64_t direction_form,
+                          int64_t min_samples_leaf, int64_t total_count, int64_t total_gq,
+                          pb_split_general* out, void* stream);
+
 /* ---- prediction ----------------------------------------------------------------------- */
 
 /* Ensemble over row-major packed codes (see pb_pack_rows):

@@ -1,3 +1,3 @@
 """Alias of ``packboost_b200.booster`` under the reference's module path (``packboost/booster.py``)."""
 
-from packboost_b200.booster import PackBoost, Tree, TreeBuilder, TreeNode  # noqa: F401
+from packboost_b200.booster import NodeShard, PackBoost, SplitDecision, Tree, TreeBuilder, TreeNode  # noqa: F401

@@ -103,6 +103,8 @@ _PROTOS: dict[str, tuple[Any, list[Any]]] = {
     "pb_era_correlation": (C.c_int, [vp, vp, vp, i64, vp, vp]),
     "pb_round_log_buffer": (C.c_int, [C.POINTER(TrainState), C.POINTER(vp), C.POINTER(i64)]),
     "pb_hist_build": (C.c_int, [C.POINTER(TrainState), vp, i64, i64, i64, vp, vp, vp]),
+    "pb_score_node_general": (C.c_int, [vp, vp, vp, i64, i64, i64, vp, i64, C.c_float, C.c_float, C.c_float, C.c_float,
+                                        C.c_float, C.c_float, i64, i64, i64, i64, vp, vp]),
     "pb_predict_rows": (C.c_int, [vp, i64, i64, i64, vp, vp, vp, vp, vp, vp, vp, vp, i64, C.c_float, vp, vp, vp]),
     "pb_predict_rows_packed": (C.c_int, [vp, i64, i64, i64, vp, vp, vp, i64, i64, C.c_float, vp, vp, vp]),
     "pb_predict_bins_fm": (C.c_int, [vp, i64, i64, vp, vp, vp, vp, vp, vp, i64, vp, vp]),

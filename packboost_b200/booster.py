@@ -123,6 +123,34 @@ class TreeBuilder:
         return Tree(nodes=self.nodes)
 
 
+@dataclass(slots=True)
+class NodeShard:
+    """A frontier node as the reference passes it to its single-node helpers: per-era row-id tensors
+    (``packboost/booster.py:197-203``).  The training loop here keeps a row -> node map instead."""
+
+    tree_id: int
+    node_id: int
+    depth: int
+    era_rows: list
+
+
+@dataclass(slots=True)
+class SplitDecision:
+    """``packboost/booster.py:205-217`` (the row lists are filled by ``_find_best_split`` only)."""
+
+    feature: int
+    threshold: int
+    score: float
+    left_grad: float
+    left_hess: float
+    right_grad: float
+    right_hess: float
+    left_count: int
+    right_count: int
+    left_rows: list = field(default_factory=list)
+    right_rows: list = field(default_factory=list)
+
+
 # ------------------------------ decision log ------------------------------
 
 _WINNER_DT = np.dtype({
@@ -909,6 +937,94 @@ class PackBoost:
         from .kernels import histograms_nodes
         return histograms_nodes(bins_matrix, grad_rows, hess_rows, era_ids, node_ids, int(num_nodes), int(num_eras),
                                 int(num_bins))
+
+    def _stack_node_rows(self, era_rows: Sequence[torch.Tensor]) -> tuple[torch.Tensor, torch.Tensor]:
+        """Concatenated row ids of a node and their era index (``packboost/booster.py:2156-2170``)."""
+        rows = [r for r in era_rows if r.numel() > 0]
+        if not rows:
+            return (torch.empty(0, dtype=torch.int64, device=self._device),
+                    torch.empty(0, dtype=torch.int16, device=self._device))
+        eras = [torch.full((r.numel(),), e, dtype=torch.int16, device=r.device)
+                for e, r in enumerate(era_rows) if r.numel() > 0]
+        return torch.cat(rows, 0), torch.cat(eras, 0)
+
+    def _compute_histograms(self, feature_values, grad_rows, hess_rows, era_ids, *, num_eras: int, num_bins: int):
+        """Counts, gradient and hessian sums ``[era, bin]`` of one feature of one node
+        (``packboost/booster.py:979-1002``), built by the histogram kernel."""
+        if num_bins <= 0:
+            raise ValueError("num_bins must be positive")
+        dev = self._device
+        if feature_values.numel() == 0:
+            z = torch.zeros((num_eras, num_bins), dtype=torch.int64, device=dev)
+            return z, z.to(torch.float32), z.to(torch.float32)
+        hess = torch.ones_like(grad_rows) if hess_rows is None else hess_rows
+        node = torch.zeros(feature_values.numel(), dtype=torch.int64, device=dev)
+        c, g, h = self._batched_histograms_nodes(feature_values.view(-1, 1), grad_rows, hess, era_ids, node, 1,
+                                                 num_eras, num_bins)
+        return c[0, 0], g[0, 0], h[0, 0]
+
+    def _weighted_welford(self, values: torch.Tensor, valid: torch.Tensor, weights: torch.Tensor):
+        """Streaming weighted mean / std over the eras of ``values [E, T]`` with invalid entries
+        masked: ``(mean, std, weight sum)`` (``packboost/booster.py:828-867``)."""
+        if values.ndim != 2:
+            raise ValueError("values must be 2D [E, T]")
+        values, valid, weights = values.to(torch.float32), valid.to(torch.bool), weights.to(torch.float32)
+        mean = torch.zeros(values.shape[1], dtype=torch.float32, device=values.device)
+        m2, wsum = torch.zeros_like(mean), torch.zeros_like(mean)
+        for e in range(values.shape[0]):
+            w = torch.where(valid[e], weights[e].clamp_min(0.0), torch.zeros((), device=values.device))
+            wsum_new = wsum + w
+            factor = torch.where(wsum_new > 0, w / wsum_new.clamp_min(1e-38), torch.zeros_like(w))
+            delta = values[e] - mean
+            mean = mean + factor * delta
+            m2 = m2 + w * delta * (values[e] - mean)
+            wsum = wsum_new
+        std = torch.sqrt(torch.clamp_min(m2 / torch.clamp_min(wsum, 1e-12), 0.0))
+        return mean, std, wsum
+
+    def _directional_agreement(self, left_values, right_values, valid, weights, weight_sum) -> torch.Tensor:
+        """Weighted mean over valid eras of ``+1`` where the left leaf value exceeds the right one,
+        else ``-1`` (``packboost/booster.py:869-907``)."""
+        left, right = left_values.to(torch.float32), right_values.to(torch.float32)
+        w = weights.to(torch.float32).clamp_min(0.0).view(-1, 1) * valid.to(torch.float32)
+        direction = torch.where(left > right, 1.0, -1.0)
+        accum = (w * direction).sum(0)
+        denom = torch.clamp_min(weight_sum.to(torch.float32), 1e-12)
+        return accum / denom
+
+    def _find_best_split(self, node: NodeShard, grad: torch.Tensor, hess: torch.Tensor, bins: torch.Tensor,
+                         feature_subset: torch.Tensor) -> SplitDecision | None:
+        """Best split of one node given as per-era row lists, with arbitrary per-row hessians
+        (``packboost/booster.py:1010-1290``): histograms and scores on the device.  The directional
+        term follows ``PACKBOOST_DIRECTION_FORM`` (default: the torch frontier's form)."""
+        from .kernels import best_split_one_node
+        cfg = self.config
+        dev = self._device
+        eras = [r.to(dev).to(torch.int64) for r in node.era_rows]
+        rows = torch.cat(eras) if eras else torch.zeros(0, dtype=torch.int64, device=dev)
+        era_ids = torch.cat([torch.full((int(r.numel()),), e, dtype=torch.int64, device=dev) for e, r in enumerate(eras)]) \
+            if eras else rows
+        feats = feature_subset.to(torch.int64).cpu().numpy()
+        nb, k_user = int(cfg.max_bins), int(cfg.k_cuts)
+        if 0 < k_user < nb - 1:
+            if cfg.cut_selection == "mass":
+                raise RuntimeError("_find_best_split supports the full sweep and even k_cuts only")
+            thr = even_cut_ids(nb, k_user)
+        else:
+            thr = np.arange(nb - 1, dtype=np.int32)
+        codes = bins.to(dev).index_select(0, rows).index_select(1, torch.from_numpy(feats).to(dev))
+        res = best_split_one_node(
+            codes, grad.to(dev).index_select(0, rows), hess.to(dev).index_select(0, rows), era_ids, feats, len(eras),
+            max_bins=nb, thr_ids=thr, lambda_l2=cfg.lambda_l2, lambda_dro=cfg.lambda_dro,
+            direction_weight=cfg.direction_weight, era_alpha=cfg.era_alpha,
+            direction_form=1 if os.getenv("PACKBOOST_DIRECTION_FORM") == "helper" else 0,
+            min_samples_leaf=int(cfg.min_samples_leaf), feature_block_size=int(cfg.feature_block_size))
+        if res is None:
+            return None
+        col = bins.to(dev)[:, res["feature"]]
+        left_rows = [r[col.index_select(0, r) <= res["threshold"]] for r in eras]
+        right_rows = [r[col.index_select(0, r) > res["threshold"]] for r in eras]
+        return SplitDecision(left_rows=left_rows, right_rows=right_rows, **res)
 
     def split_records(self) -> dict[str, np.ndarray]:
         """Every split of the fit in the order the frontier produced it (round, depth, frontier

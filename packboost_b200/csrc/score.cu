@@ -793,6 +793,130 @@ int launch_mass_thresholds(const uint32_t* cnt, int n_feat, const int32_t* n_nod
     return PB_OK;
 }
 
+// ---- one node, general hessians -------------------------------------------------------------------
+// The reference's single-node entry (`_find_best_split`, packboost/booster.py:1010-1290 via the
+// batched frontier) accepts arbitrary per-row hessians; the training loop never produces any (the
+// squared loss has unit hessians), so this form is a kernel of its own instead of a mode of the fast
+// path.  One CTA per feature, one thread per threshold: prefix sums over the bins of every era from
+// the three histograms (counts, fixed-point gradient sums, fixed-point hessian sums), the per-era
+// gain with H = sum of hessians, the weighted Welford recursion over the eras in ascending order,
+// either directional term, the min_samples_leaf mask, and the best threshold of the feature under
+// (score, left count, threshold index).  Same separately rounded float32 operations as the rest of
+// this file.
+namespace {
+
+struct NodeGeneralArgs {
+    const uint32_t* cnt;   // [n_feat][E][nb]
+    const int64_t* gsum;
+    const int64_t* hsum;
+    int E, nb, K;
+    const int32_t* thr_ids;
+    float inv_g, inv_h, lambda_l2, lambda_dro, direction_weight, era_alpha;
+    int direction_form, min_samples_leaf;
+    long long total_count, total_gq;
+    pb_split_general* out;  // [n_feat]
+};
+
+__global__ void __launch_bounds__(256) score_node_general_kernel(NodeGeneralArgs a) {
+    __shared__ float s_score[256];
+    __shared__ long long s_lc[256], s_lg[256], s_lh[256];
+    __shared__ int s_nan;
+    const int f = blockIdx.x, k = threadIdx.x;
+    if (k == 0) s_nan = 0;
+    __syncthreads();
+    const float lam = a.lambda_l2;
+    const bool use_dir = (a.direction_weight != 0.f) && (a.direction_form == 1 || a.total_gq != 0);
+    const float pa = (a.total_gq > 0) ? -1.f : ((a.total_gq < 0) ? 1.f : 0.f);
+    if (k < a.K) {
+        const int thr = a.thr_ids[k];
+        float wsum = 0.f, mean = 0.f, m2 = 0.f, a_num = 0.f, a_den = 0.f;
+        long long lc_all = 0, lg_all = 0, lh_all = 0;
+        for (int e = 0; e < a.E; ++e) {
+            const size_t base = ((size_t)f * a.E + e) * a.nb;
+            long long tc = 0, tgq = 0, thq = 0, lc = 0, lgq = 0, lhq = 0;
+            for (int b = 0; b < a.nb; ++b) {
+                const long long c = a.cnt[base + b], g = a.gsum[base + b], h = a.hsum[base + b];
+                tc += c; tgq += g; thq += h;
+                if (b <= thr) { lc += c; lgq += g; lhq += h; }
+            }
+            if (tc == 0) continue;  // era absent from the node: weight 0
+            const float w_e = (a.era_alpha > 0.f) ? f_add((float)tc, a.era_alpha) : 1.f;
+            const float w = (lc > 0 && tc - lc > 0) ? w_e : 0.f;
+            const float lg = f_mul(__ll2float_rn(lgq), a.inv_g), tg = f_mul(__ll2float_rn(tgq), a.inv_g);
+            const float lh = f_mul(__ll2float_rn(lhq), a.inv_h), th = f_mul(__ll2float_rn(thq), a.inv_h);
+            const float rg = f_sub(tg, lg), rh = f_sub(th, lh);
+            const float dl = f_add(lh, lam), dr = f_add(rh, lam);
+            const float parent = f_div(f_mul(0.5f, f_mul(tg, tg)), f_add(th, lam));
+            const float gain = f_sub(f_mul(0.5f, f_add(f_div(f_mul(lg, lg), dl), f_div(f_mul(rg, rg), dr))), parent);
+            welford_step(gain, w, wsum, mean, m2);
+            if (use_dir) {
+                const float vl = f_div(-lg, dl), vr = f_div(-rg, dr);
+                const float agree = (a.direction_form == 1)
+                    ? ((vl > vr) ? 1.f : -1.f)
+                    : f_mul(0.5f, f_add((sign_of(vl) == pa) ? 1.f : 0.f, (sign_of(vr) == pa) ? 1.f : 0.f));
+                a_num = f_add(a_num, f_mul(w, agree));
+                a_den = f_add(a_den, w);
+            }
+            lc_all += lc; lg_all += lgq; lh_all += lhq;
+        }
+        const float ws = (wsum < 1e-12f) ? 1e-12f : wsum;
+        float var = f_div(m2, ws);
+        if (var < 0.f) var = 0.f;
+        float score = f_sub(mean, f_mul(a.lambda_dro, __fsqrt_rn(var)));
+        if (use_dir) score = f_add(score, f_mul(a.direction_weight, (a_den > 0.f) ? f_div(a_num, a_den) : 0.f));
+        const bool ok = (lc_all >= a.min_samples_leaf) && (a.total_count - lc_all >= a.min_samples_leaf);
+        if (score != score) s_nan = 1;
+        s_score[k] = ok ? score : -INFINITY;
+        s_lc[k] = lc_all; s_lg[k] = lg_all; s_lh[k] = lh_all;
+    }
+    __syncthreads();
+    if (k == 0) {
+        float bs = -INFINITY;
+        long long bc = -1;
+        int bk = -1;
+        for (int j = 0; j < a.K; ++j) {
+            const float sc = s_score[j];
+            if (sc != sc) continue;
+            if (sc > bs || (sc == bs && s_lc[j] >= bc)) { bs = sc; bc = s_lc[j]; bk = j; }
+        }
+        pb_split_general o;
+        o.score = bs;
+        o.k = bk;
+        o.threshold = (bk >= 0) ? a.thr_ids[bk] : -1;
+        o.has_nan = s_nan;
+        o.left_count = (bk >= 0) ? s_lc[bk] : 0;
+        o.left_gq = (bk >= 0) ? s_lg[bk] : 0;
+        o.left_hq = (bk >= 0) ? s_lh[bk] : 0;
+        a.out[f] = o;
+    }
+}
+
+}  // namespace
+
+}  // namespace pb
+
+extern "C" int pb_score_node_general(const uint32_t* cnt, const int64_t* gsum, const int64_t* hsum, int64_t n_feat,
+                                     int64_t n_eras, int64_t max_bins, const int32_t* thr_ids, int64_t n_thresholds,
+                                     float inv_scale_g, float inv_scale_h, float lambda_l2, float lambda_dro,
+                                     float direction_weight, float era_alpha, int64_t direction_form,
+                                     int64_t min_samples_leaf, int64_t total_count, int64_t total_gq,
+                                     pb_split_general* out, void* stream) {
+    using namespace pb;
+    PB_REQUIRE(cnt && gsum && hsum && thr_ids && out, "null buffer");
+    PB_REQUIRE(n_feat >= 1 && n_eras >= 1 && max_bins >= 2 && max_bins <= 256, "bad shape");
+    PB_REQUIRE(n_thresholds >= 1 && n_thresholds < max_bins, "n_thresholds out of range");
+    PB_REQUIRE(lambda_l2 > 0.f, "lambda_l2 must be positive");
+    NodeGeneralArgs a{cnt, gsum, hsum, (int)n_eras, (int)max_bins, (int)n_thresholds, thr_ids, inv_scale_g, inv_scale_h,
+                      lambda_l2, lambda_dro, direction_weight, era_alpha > 0.f ? era_alpha : 0.f, direction_form ? 1 : 0,
+                      (int)min_samples_leaf, (long long)total_count, (long long)total_gq, out};
+    score_node_general_kernel<<<(unsigned)n_feat, 256, 0, (cudaStream_t)stream>>>(a);
+    count_launch(1);
+    PB_LAUNCH_CHECK("score_node_general_kernel");
+    return PB_OK;
+}
+
+namespace pb {
+
 size_t score_scratch_bytes_per_feature(int node_stride, int n_eras, int n_thr) {
     return (size_t)node_stride * n_eras * n_thr * sizeof(float2) + (size_t)node_stride * n_thr * 12;
 }

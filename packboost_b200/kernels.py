@@ -35,12 +35,24 @@ def histograms_nodes(bins_matrix: torch.Tensor, grad_rows: torch.Tensor, hess_ro
     rows given (``bins_matrix`` is ``[rows, features]``), built by the histogram kernel: rows are
     ordered by era, packed feature-major, and the kernel runs once with the gradients and once with
     the hessians as its fixed-point addend.  Sums are exact in fixed point and converted once."""
-    lib = B.lib()
     dev = torch.device("cuda", torch.cuda.current_device())
     R, F = int(bins_matrix.shape[0]), int(bins_matrix.shape[1])
     if R == 0 or F == 0:
         z = torch.zeros((F, num_nodes, num_eras, num_bins), device=dev)
         return z.to(torch.int64), z.to(torch.float32), z.to(torch.float32)
+    cnt, sums = histograms_raw(bins_matrix, [grad_rows, hess_rows], era_ids, node_ids, num_nodes, num_eras, num_bins)
+    out = [(q.to(torch.float64) * inv).to(torch.float32).permute(0, 2, 1, 3).contiguous() for q, inv in sums]
+    return cnt.to(torch.int64).permute(0, 2, 1, 3).contiguous(), out[0], out[1]
+
+
+def histograms_raw(bins_matrix: torch.Tensor, addends: list[torch.Tensor], era_ids: torch.Tensor,
+                   node_ids: torch.Tensor, num_nodes: int, num_eras: int, num_bins: int):
+    """``(cnt int32 [F, E, nodes, bins], [(sum int64 [F, E, nodes, bins], inv_scale), ...])``: one
+    histogram pass per per-row addend, each quantised to fixed point with its own power-of-two
+    scale (``sum * inv_scale`` is the float sum)."""
+    lib = B.lib()
+    dev = torch.device("cuda", torch.cuda.current_device())
+    R, F = int(bins_matrix.shape[0]), int(bins_matrix.shape[1])
     if num_nodes > 65534:
         raise ValueError("too many nodes")
     era = era_ids.to(dev).to(torch.int64)
@@ -77,12 +89,76 @@ def histograms_nodes(bins_matrix: torch.Tensor, grad_rows: torch.Tensor, hess_ro
     cells = (F, num_eras, num_nodes, num_bins)
     out = []
     cnt = torch.empty(cells, dtype=torch.int32, device=dev)
-    for values in (grad_rows, hess_rows):
+    for values in addends:
         q, inv = _fixed_point(values.to(dev).to(torch.float32).index_select(0, order), int(st.gq_bits))
         gq[:R] = q
         gsum = torch.empty(cells, dtype=torch.int64, device=dev)
         B.check(lib.pb_hist_build(C.byref(st), feats.data_ptr(), F, num_nodes, num_nodes, cnt.data_ptr(),
                                   gsum.data_ptr(), stream))
-        out.append((gsum.to(torch.float64) * inv).to(torch.float32).permute(0, 2, 1, 3).contiguous())
-    counts = cnt.to(torch.int64).permute(0, 2, 1, 3).contiguous()
-    return counts, out[0], out[1]
+        out.append((gsum, inv))
+    torch.cuda.current_stream().synchronize()   # (the temporaries above are released after the kernels ran)
+    return cnt, out
+
+
+_SPLIT_DT = np.dtype([("score", "<f4"), ("k", "<i4"), ("threshold", "<i4"), ("has_nan", "<i4"),
+                      ("left_count", "<i8"), ("left_gq", "<i8"), ("left_hq", "<i8")])
+
+
+def best_split_one_node(codes: torch.Tensor, grad: torch.Tensor, hess: torch.Tensor, era_ids: torch.Tensor,
+                        features: np.ndarray, num_eras: int, *, max_bins: int, thr_ids: np.ndarray, lambda_l2: float,
+                        lambda_dro: float, direction_weight: float, era_alpha: float, direction_form: int,
+                        min_samples_leaf: int, feature_block_size: int) -> dict | None:
+    """Best split of one node whose rows are given (``codes`` is ``[rows, len(features)]``), with
+    arbitrary per-row hessians: histograms by the histogram kernel (gradients and hessians as
+    fixed-point addends), per-feature best thresholds by ``pb_score_node_general``, then the
+    reference's order over the features (inside a block of ``feature_block_size`` sampled features:
+    score, left count, later position; across blocks: score, left count, feature id, threshold;
+    ``packboost/booster.py:1912-1981``).  Returns the fields of a ``SplitDecision`` or ``None``."""
+    lib = B.lib()
+    dev = torch.device("cuda", torch.cuda.current_device())
+    R, F = int(codes.shape[0]), int(codes.shape[1])
+    if R < 2 * min_samples_leaf or F == 0:
+        return None
+    node_ids = torch.zeros(R, dtype=torch.int64, device=dev)
+    cnt, sums = histograms_raw(codes, [grad, hess], era_ids, node_ids, 1, num_eras, max_bins)
+    (gsum, inv_g), (hsum, inv_h) = sums
+    total_gq = int(gsum[0].sum().item())
+    total_hq = int(hsum[0].sum().item())
+    thr_t = torch.from_numpy(np.ascontiguousarray(thr_ids, dtype=np.int32)).to(dev)
+    out = torch.zeros(F * _SPLIT_DT.itemsize, dtype=torch.uint8, device=dev)
+    B.check(lib.pb_score_node_general(cnt.data_ptr(), gsum.data_ptr(), hsum.data_ptr(), F, num_eras, max_bins,
+                                      thr_t.data_ptr(), int(thr_t.numel()), float(inv_g), float(inv_h), float(lambda_l2),
+                                      float(lambda_dro), float(direction_weight), float(era_alpha), int(direction_form),
+                                      int(min_samples_leaf), R, total_gq, out.data_ptr(),
+                                      torch.cuda.current_stream().cuda_stream))
+    rec = out.cpu().numpy().view(_SPLIT_DT)
+    blk = feature_block_size if 0 < feature_block_size <= F else F
+    best = None   # (score, left_count, feature, threshold, position)
+    for b0 in range(0, F, blk):
+        inblk = None
+        if rec["has_nan"][b0:b0 + blk].any():
+            continue   # a NaN score voids the block's maximum, as torch.max does
+        for p in range(b0, min(F, b0 + blk)):
+            r = rec[p]
+            if r["k"] < 0:
+                continue
+            key = (float(r["score"]), int(r["left_count"]), p)
+            if inblk is None or key[:2] > inblk[0][:2] or (key[:2] == inblk[0][:2] and p > inblk[0][2]):
+                inblk = (key, p)
+        if inblk is None:
+            continue
+        p = inblk[1]
+        cand = (float(rec[p]["score"]), int(rec[p]["left_count"]), int(features[p]), int(rec[p]["threshold"]), p)
+        if best is None or cand[:4] > best[:4]:
+            best = cand
+    if best is None:
+        return None
+    p = best[4]
+    f32 = np.float32
+    lg = f32(f32(int(rec[p]["left_gq"])) * f32(inv_g))
+    lh = f32(f32(int(rec[p]["left_hq"])) * f32(inv_h))
+    tg = f32(f32(total_gq) * f32(inv_g))
+    th = f32(f32(total_hq) * f32(inv_h))
+    return {"feature": best[2], "threshold": best[3], "score": best[0], "left_grad": float(lg), "left_hess": float(lh),
+            "right_grad": float(tg) - float(lg), "right_hess": float(th) - float(lh), "left_count": best[1],
+            "right_count": R - best[1]}

@@ -260,3 +260,129 @@ def test_config_defaults():
     assert cfg.max_depth == 6
     assert cfg.device == "cuda"
     assert cfg.max_bins <= 256
+
+
+@pytest.mark.parametrize("era_alpha", [0.0, 1.5])
+def test_des_metrics_match_numpy(era_alpha, monkeypatch):
+    """tests/test_des.py:9-217: the reference's hand-built node (six rows, one feature, two eras,
+    four bins, non-unit hessians).  Its expectations are the helper form of the directional term,
+    which the reference's own torch frontier does not use (the test fails there on that account);
+    here the form is selected with PACKBOOST_DIRECTION_FORM=helper and the whole test holds:
+    histograms, per-era gains, weighted mean / std, direction, score, and the split returned by
+    ``_find_best_split`` (histograms and scoring with general hessians on the device)."""
+    from packboost.booster import NodeShard, PackBoost
+    from packboost.config import PackBoostConfig
+    monkeypatch.setenv("PACKBOOST_DIRECTION_FORM", "helper")
+    config = PackBoostConfig(max_bins=4, min_samples_leaf=1, lambda_l2=0.5, lambda_dro=0.1, direction_weight=0.2,
+                             era_alpha=era_alpha)
+    booster = PackBoost(config)
+    device = booster._device
+    grad = torch.tensor([0.5, -0.2, 0.1, -0.3, 0.4, -0.1], dtype=torch.float32, device=device)
+    hess = torch.tensor([1.0, 0.8, 1.2, 1.0, 0.9, 1.1], dtype=torch.float32, device=device)
+    bins = torch.tensor([[0], [1], [1], [2], [2], [3]], dtype=torch.int64, device=device)
+    era_rows = [torch.tensor([0, 1], dtype=torch.int64, device=device),
+                torch.tensor([2, 3, 4, 5], dtype=torch.int64, device=device)]
+    node = NodeShard(tree_id=0, node_id=0, depth=0, era_rows=era_rows)
+    feature_subset = torch.tensor([0], dtype=torch.int64, device=device)
+
+    all_rows, era_ids = booster._stack_node_rows(node.era_rows)
+    counts, grad_hist, hess_hist = booster._compute_histograms(
+        bins[all_rows, 0].to(dtype=torch.int64), grad[all_rows], hess[all_rows], era_ids, num_eras=len(era_rows),
+        num_bins=config.max_bins)
+    prefix_counts = counts[:, :-1].cumsum(dim=1)
+    prefix_grad = grad_hist[:, :-1].cumsum(dim=1)
+    prefix_hess = hess_hist[:, :-1].cumsum(dim=1)
+    total_count_e = counts.sum(dim=1, keepdim=True)
+    total_grad_e = grad_hist.sum(dim=1, keepdim=True)
+    total_hess_e = hess_hist.sum(dim=1, keepdim=True)
+    left_count, right_count = prefix_counts, total_count_e - prefix_counts
+    valid = (left_count > 0) & (right_count > 0)
+    left_grad, right_grad = prefix_grad, total_grad_e - prefix_grad
+    left_hess, right_hess = prefix_hess, total_hess_e - prefix_hess
+    parent_gain = 0.5 * (total_grad_e ** 2) / (total_hess_e + config.lambda_l2)
+    era_gain = (0.5 * (left_grad ** 2) / (left_hess + config.lambda_l2)
+                + 0.5 * (right_grad ** 2) / (right_hess + config.lambda_l2) - parent_gain)
+    left_value = -left_grad / (left_hess + config.lambda_l2)
+    right_value = -right_grad / (right_hess + config.lambda_l2)
+    era_counts = torch.tensor([float(r.numel()) for r in era_rows], dtype=torch.float32, device=device)
+    era_weights = booster._compute_era_weights(era_counts)
+    mean_gain, std_gain, weight_sum = booster._weighted_welford(era_gain, valid, era_weights)
+    agreement_mean = booster._directional_agreement(left_value, right_value, valid, era_weights, weight_sum)
+    left_count_total = counts.sum(dim=0).cumsum(dim=0)[:-1]
+    right_count_total = all_rows.numel() - left_count_total
+    valid_global = (left_count_total >= config.min_samples_leaf) & (right_count_total >= config.min_samples_leaf)
+    score = mean_gain - config.lambda_dro * std_gain + config.direction_weight * agreement_mean
+    score = torch.where(valid_global, score, torch.full_like(score, float("-inf")))
+
+    # plain numpy loops over eras and thresholds, as in the reference's test
+    counts_np, grad_np, hess_np = counts.cpu().numpy(), grad_hist.cpu().numpy(), hess_hist.cpu().numpy()
+    n_eras, n_bins = counts_np.shape
+    T = n_bins - 1
+    gain_np = np.zeros((n_eras, T), dtype=np.float32)
+    lv_np, rv_np = np.zeros_like(gain_np), np.zeros_like(gain_np)
+    valid_np = np.zeros_like(gain_np, dtype=bool)
+    lam = config.lambda_l2
+    for e in range(n_eras):
+        for t in range(T):
+            lc, rc = counts_np[e, :t + 1].sum(), counts_np[e, t + 1:].sum()
+            if lc <= 0 or rc <= 0:
+                continue
+            valid_np[e, t] = True
+            lg, rg = grad_np[e, :t + 1].sum(), grad_np[e, t + 1:].sum()
+            lh, rh = hess_np[e, :t + 1].sum(), hess_np[e, t + 1:].sum()
+            pg, ph = grad_np[e].sum(), hess_np[e].sum()
+            gain_np[e, t] = 0.5 * lg ** 2 / (lh + lam) + 0.5 * rg ** 2 / (rh + lam) - 0.5 * pg ** 2 / (ph + lam)
+            lv_np[e, t], rv_np[e, t] = -lg / (lh + lam), -rg / (rh + lam)
+    ec = np.array([r.numel() for r in era_rows], dtype=np.float32)
+    weights_np = np.where(ec > 0, ec + era_alpha, 0.0) if era_alpha > 0 else np.where(ec > 0, 1.0, 0.0)
+    mean_np, std_np, dir_np = (np.zeros(T, dtype=np.float32) for _ in range(3))
+    for t in range(T):
+        w = weights_np * valid_np[:, t]
+        if w.sum() <= 0:
+            continue
+        mean_np[t] = float(np.dot(gain_np[:, t], w) / w.sum())
+        std_np[t] = np.sqrt(max(float(np.dot(w, (gain_np[:, t] - mean_np[t]) ** 2) / w.sum()), 0.0))
+        dir_np[t] = float(np.dot(np.where(lv_np[:, t] > rv_np[:, t], 1.0, -1.0), w) / w.sum())
+    lct_np = np.cumsum(counts_np.sum(axis=0))[:-1]
+    vg_np = (lct_np >= config.min_samples_leaf) & (all_rows.numel() - lct_np >= config.min_samples_leaf)
+    score_np = np.where(vg_np, mean_np - config.lambda_dro * std_np + config.direction_weight * dir_np, -np.inf)
+
+    mv = valid.cpu().numpy()
+    np.testing.assert_array_equal(mv, valid_np)
+    np.testing.assert_allclose(era_gain.cpu().numpy()[mv], gain_np[mv], rtol=1e-6, atol=1e-6)
+    mw = weight_sum.cpu().numpy() > 0
+    np.testing.assert_allclose(mean_gain.cpu().numpy()[mw], mean_np[mw], rtol=1e-6, atol=1e-6)
+    np.testing.assert_allclose(std_gain.cpu().numpy()[mw], std_np[mw], rtol=1e-6, atol=1e-6)
+    np.testing.assert_allclose(agreement_mean.cpu().numpy()[mw], dir_np[mw], rtol=1e-6, atol=1e-6)
+    np.testing.assert_allclose(score.cpu().numpy()[vg_np], score_np[vg_np], rtol=1e-6, atol=1e-6)
+
+    split = booster._find_best_split(node, grad, hess, bins, feature_subset)
+    assert split is not None
+    assert split.feature == 0
+    expected = int(np.argmax(score_np))
+    assert split.threshold == expected
+    assert np.isclose(split.score, score_np[expected], rtol=1e-6, atol=1e-6)
+    assert split.left_count == int(lct_np[expected])
+
+
+@pytest.mark.parametrize("alpha", [0.0, 1.5])
+def test_find_best_split_reproduces_the_reference_frontier_on_the_known_answer_node(alpha):
+    """The same node through the reference's torch frontier (its default direction form): the
+    fixture ``des_known_answer.npz`` holds what the unmodified reference's ``_find_best_split``
+    returned (feature, threshold, child counts, score, child gradient / hessian sums)."""
+    import os
+    import cases
+    from packboost.booster import NodeShard, PackBoost
+    from packboost.config import PackBoostConfig
+    grad, hess, codes, era_rows, cfg = cases.des_known_answer_inputs()
+    gold = np.load(os.path.join(os.path.dirname(os.path.abspath(cases.__file__)), "des_known_answer.npz"))
+    b = PackBoost(PackBoostConfig(era_alpha=alpha, **cfg))
+    dev = b._device
+    node = NodeShard(tree_id=0, node_id=0, depth=0, era_rows=[torch.from_numpy(r).to(dev) for r in era_rows])
+    dec = b._find_best_split(node, torch.from_numpy(grad).to(dev), torch.from_numpy(hess).to(dev),
+                             torch.from_numpy(codes).to(dev), torch.tensor([0], dtype=torch.int64))
+    gi, gf = gold[f"a{alpha}"], gold[f"a{alpha}_f"]
+    assert [dec.feature, dec.threshold, dec.left_count, dec.right_count] == gi.tolist()
+    got = np.array([dec.score, dec.left_grad, dec.left_hess, dec.right_grad, dec.right_hess])
+    np.testing.assert_allclose(got, gf, rtol=2e-6, atol=1e-7)
+    assert [int(r.numel()) for r in dec.left_rows] == [1, 0] and [int(r.numel()) for r in dec.right_rows] == [1, 4]
