@@ -423,6 +423,9 @@ def main():
             X_np = np.empty((n_rows, n_feat), dtype=np.uint8)
             np.copyto(X_np, X_host.numpy())
             del X_host
+            import gc
+            gc.collect()
+            torch.cuda.empty_cache()   # the page-locked copy is released here, not inside the next timed fit
             e2e_numpy, digests["model_digest_numpy"], _ = e2e_leg(X_np, False)
             e2e_numpy["note"] = "the same fit on a pageable numpy array (the input type of the reference's API)"
             del X_np

@@ -463,10 +463,24 @@ class _DeviceTrainer:
         return self._round_enqueued(slot, redo)
 
     def _capture(self, k: int, n_local: list[int], signature) -> None:
+        """Capture the launches of one round into a CUDA graph.  The capture is driven directly
+        (``capture_begin`` / ``capture_end`` on a side stream) rather than through the
+        ``torch.cuda.graph`` context, whose entry collects garbage and empties the allocator caches —
+        tens of milliseconds per fit, and far more when a large page-locked buffer of the caller
+        happens to be waiting in the host cache; nothing is allocated while these launches are
+        recorded, so the private pool that step prepares is not needed."""
         before = int(self.lib.pb_launch_count())
         graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph, capture_error_mode="thread_local"):
-            self._enqueue_phases(k, n_local, 1)
+        side = torch.cuda.Stream(device=self.dev)
+        cur = torch.cuda.current_stream()
+        side.wait_stream(cur)
+        with torch.cuda.stream(side):
+            graph.capture_begin(capture_error_mode="thread_local")
+            try:
+                self._enqueue_phases(k, n_local, 1)
+            finally:
+                graph.capture_end()
+        cur.wait_stream(side)
         self.graph, self.graph_signature = graph, signature
         self.graph_launches = int(self.lib.pb_launch_count()) - before  # kernels per replay
 

@@ -118,8 +118,8 @@ def _device() -> torch.device:
 _CHUNK_BYTES = 256 << 20
 
 
-def _row_chunks(n_rows: int, row_bytes: int) -> Iterable[tuple[int, int]]:
-    step = max(256, (_CHUNK_BYTES // max(row_bytes, 1)) // 256 * 256)
+def _row_chunks(n_rows: int, row_bytes: int, chunk_bytes: int = _CHUNK_BYTES) -> Iterable[tuple[int, int]]:
+    step = max(256, (chunk_bytes // max(row_bytes, 1)) // 256 * 256)
     for a in range(0, n_rows, step):
         yield a, min(n_rows, a + step)
 
@@ -236,7 +236,9 @@ def pack_feature_major(
     if row_order is not None and is_tensor:
         order_t = torch.from_numpy(np.ascontiguousarray(row_order, dtype=np.int64)).to(X.device)
     top = torch.zeros((), dtype=torch.uint8, device=dev)
-    chunks = [(r0 + a, r0 + b) for a, b in _row_chunks(r1 - r0, n_feat * item)]
+    # (smaller pieces for a pageable source: its two page-locked staging buffers are allocated on first
+    # use, at about half a second per GB)
+    chunks = [(r0 + a, r0 + b) for a, b in _row_chunks(r1 - r0, n_feat * item, _CHUNK_BYTES if direct else 64 << 20)]
     stage = None
     for i, (a, b) in enumerate(chunks):
         n = b - a
