@@ -419,6 +419,10 @@ def main():
             room = psutil.virtual_memory().available > 2.5 * n_rows * n_feat * max(world, 1)
         except Exception:
             room = world == 1
+        if world > 1:   # every rank takes the same decision (a rank that skipped the leg would leave the others waiting)
+            flag = torch.tensor([1 if room else 0], dtype=torch.int32, device=dev)
+            dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+            room = bool(int(flag.item()))
         if room:
             X_np = np.empty((n_rows, n_feat), dtype=np.uint8)
             np.copyto(X_np, X_host.numpy())
