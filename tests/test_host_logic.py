@@ -297,3 +297,34 @@ def test_round_loop_draws_features_like_the_reference_when_rounds_end_early(run_
         assert any(redo for _, _, redo in trainer.attempts)
     else:
         assert not any(redo for _, _, redo in trainer.attempts)
+
+
+def test_row_split_upload_reassembles_the_single_gpu_layout():
+    """Every rank packs 1/world of the rows of all features into a slab ``[F_pad][seg]``; an
+    all-gather (replicated layout) or an all-to-all (sharded layout) followed by one strided copy
+    must give exactly the feature-major matrix one GPU would have packed.  The exchange is emulated
+    on CPU tensors: this pins the index algebra of ``pack_feature_major_distributed``."""
+    from packboost_b200.data import rows_per_rank
+    from packboost_b200.sharding import block_size
+    for world, F, n_rows, bits in [(2, 7, 1000, 4), (3, 10, 5000, 8), (4, 96, 20_000, 4), (8, 2376, 9_000, 4)]:
+        per = rows_per_rank(n_rows, world)
+        assert per % 256 == 0 and per * world >= n_rows and per * (world - 1) < n_rows + 256 * world
+        seg = per * bits // 8
+        assert seg % 128 == 0
+        blk = block_size(F, world)
+        f_pad = blk * world
+        full = torch.randint(0, 256, (f_pad, world * seg), dtype=torch.uint8,
+                             generator=torch.Generator().manual_seed(world))
+        slabs = [full[:, r * seg:(r + 1) * seg].contiguous() for r in range(world)]   # what each rank packs
+        # replicated layout: all_gather_into_tensor(parts, slab) on every rank
+        parts = torch.stack(slabs)                                                    # [world, f_pad, seg]
+        rebuilt = torch.empty_like(full)
+        rebuilt.view(f_pad, world, seg).copy_(parts.permute(1, 0, 2))
+        assert torch.equal(rebuilt, full)
+        # sharded layout: all_to_all_single(parts, slab.view(world, blk, seg)) -> rank dst receives
+        # from every source the feature block it owns
+        for dst in range(world):
+            recv = torch.stack([slabs[src].view(world, blk, seg)[dst] for src in range(world)])   # [world, blk, seg]
+            mine = torch.empty((blk, world * seg), dtype=torch.uint8)
+            mine.view(blk, world, seg).copy_(recv.permute(1, 0, 2))
+            assert torch.equal(mine, full[dst * blk:(dst + 1) * blk])
