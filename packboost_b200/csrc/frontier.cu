@@ -560,7 +560,7 @@ struct BlockPlan {
 
 // The era-summed tables of the fused flush are laid out per lane of the histogram kernel and so
 // cover the features of the last CTA in full: up to this many features more than the block has.
-constexpr int64_t kTotPad = 128;
+constexpr int64_t kTotPad = 256;
 
 static bool plan_block(size_t avail, int stride, int64_t n_eras, int64_t max_bins, int64_t n_thr, int64_t n_feat,
                        bool fused, BlockPlan* p) {
@@ -735,6 +735,7 @@ extern "C" int pb_train_prepare(pb_train_state* st, const int32_t* era_offsets_h
     const int64_t tile = (mx < kTileRowsMax) ? mx : kTileRowsMax;
     int cb = 1;
     while ((1ll << cb) <= tile) ++cb;  // tile < 2^cb
+    if (cb < 11) cb = 11;  // (costs no gradient bits; the lane kernel keeps a cell index below the count field)
     st->count_bits = cb;
     st->lo_bits = 32 - 2 * cb;
     st->gq_bits = (63 - 3 * cb < kGqBitsMax) ? (63 - 3 * cb) : kGqBitsMax;

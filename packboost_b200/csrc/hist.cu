@@ -225,23 +225,34 @@ __global__ void __launch_bounds__(THREADS) hist_kernel(HistKernelArgs a) {
 // ---- lane-private kernel for small cell counts ------------------------------------------------
 
 constexpr int kLaneCellBytes = 256;        // word A of lane l at l*4, word B at 128 + l*4: bank == lane
-constexpr int kLaneSmemMax = 104 * 1024;   // cells of one CTA (two CTAs per SM)
+constexpr int kLaneCellsMax = 100 * 1024;  // bytes of cells of one CTA (two CTAs per SM with the staged codes)
 constexpr int kLaneWarps = 8;
-constexpr int kLaneRows = 64;              // rows per warp step: 32 bytes of 4-bit codes per feature
+constexpr int kLaneRows = 32;              // rows per warp and CTA step
+constexpr int kBlockRows = kLaneWarps * kLaneRows;  // 256 rows: one 128-byte line of 4-bit codes per feature
+constexpr int kStagePitch = 144;           // bytes per feature of the staged code block (see below)
 
+// The CTA walks its tile in blocks of 256 rows.  The codes of a block are one 128-byte line per
+// feature; they are copied to shared memory with 16-byte asynchronous copies in which eight
+// consecutive threads fetch one line, so that every memory request is a whole line.  (A warp whose
+// lanes each read 32 bytes of a different feature row issues 32 one-sector requests per
+// instruction; the memory system serves requests, not bytes, and that pattern measured 1.6 TB/s
+// against 6.1 TB/s for whole lines on the same data.)  Warp w then owns rows [32 w, 32 w + 32) of
+// the block: a lane reads the 16 bytes of those rows of each of its features from the staged block
+// into registers (feature slots 144 bytes apart: consecutive lanes read consecutive slots, which
+// spreads a quarter-warp over all banks), and the next block is fetched while the rows are
+// accumulated.
+//
 // All lanes of a warp walk the same rows, so the row state is warp-uniform.  It is staged per
-// warp as one 8-byte record per row {byte offset of the node's first cell | 1 when the row is
-// accumulated, fixed-point gradient}, written once per row by one lane and read by all lanes with
-// a single broadcast load; the two addends follow from it with three integer operations.  A row
-// that is not accumulated has an all-zero record: it adds zero to the cells of node 0, so the row
-// steps carry no branch.  A lane owns T tuples of A features (T*A consecutive sampled features),
-// each tuple with its own set of cells.  The codes and the raw row state of the warp's next chunk
-// are loaded while the current chunk is accumulated.
+// warp as one 8-byte record per row {word A addend with the index of the node's first cell in its
+// unused bits, word B addend}, written once per row by one lane and read by all lanes with a single
+// broadcast load.  A row that is not accumulated has an all-zero record: it adds zero to the cells
+// of node 0, so the row steps carry no branch.  A lane owns T tuples of A features (T*A consecutive
+// sampled features), each tuple with its own set of cells.
 //
 // With few features per launch (a feature shard of a multi-GPU run) the warp is split into R row
-// phases: 32 / R lanes own tuples and phase p of them walks rows [p, p + 1) * 64 / R of the chunk,
-// so a row step of the warp covers R rows.  The R lanes that own the same tuple keep private cell
-// columns as always; the flush adds them up.
+// phases: 32 / R lanes own tuples and phase p of them walks rows [p, p + 1) * 32 / R of the warp's
+// rows, so a row step of the warp covers R rows.  The R lanes that own the same tuple keep private
+// cell columns as always; the flush adds them up.
 constexpr int kLaneBinsMax = 16;  // 4-bit codes
 
 // The nb bins of one (feature, node) are contiguous in both output arrays but start on an odd or
@@ -268,9 +279,15 @@ __device__ __forceinline__ void store_bins(uint32_t* cnt, int64_t* gsum, const u
     }
 }
 
+// Shared memory of a lane-kernel CTA: cells | row records | staged code block | feature row offsets.
+__host__ __device__ constexpr size_t lane_record_bytes(int R) { return (size_t)kLaneWarps * (kLaneRows + R) * sizeof(uint2); }
+__host__ __device__ constexpr size_t lane_extra_bytes(int R, int fpl) {
+    return lane_record_bytes(R) + (size_t)(32 / R) * fpl * (kStagePitch + sizeof(int64_t));
+}
+
 template <int A, int T, int R>
 __global__ void __launch_bounds__(kLaneWarps * 32, 2) hist_lane_kernel(HistKernelArgs a) {
-    extern __shared__ __align__(16) unsigned char smb[];  // cells [T][n_cells] | staging [warps][64] uint2
+    extern __shared__ __align__(16) unsigned char smb[];
     const int n_nodes = a.n_nodes_ptr ? min(*a.n_nodes_ptr, a.n_nodes) : a.n_nodes;
     if (n_nodes <= 0) return;
     const int era = blockIdx.x / a.tiles_per_era;
@@ -287,157 +304,171 @@ __global__ void __launch_bounds__(kLaneWarps * 32, 2) hist_lane_kernel(HistKerne
     for (int i = 1; i < A; ++i) cpn *= nb;
     const int n_cells = a.n_nodes * cpn;  // per tuple, sized for the upper bound of nodes
     const uint32_t slot_bytes = (uint32_t)n_cells * kLaneCellBytes;
+    constexpr int FPL = A * T;
+    constexpr int TL = 32 / R;            // tuple-owning lanes per phase
+    constexpr int NF = TL * FPL;          // features of the CTA
+    constexpr int PR = kLaneRows / R;     // rows of a warp step walked by one phase
+    constexpr int WPP = PR / 8;           // 32-bit code words per feature and phase
     uint32_t* cells = reinterpret_cast<uint32_t*>(smb);
-    uint2* staging = reinterpret_cast<uint2*>(smb + (size_t)T * slot_bytes);
+    uint2* records = reinterpret_cast<uint2*>(smb + (size_t)T * slot_bytes);
+    unsigned char* stage = smb + (size_t)T * slot_bytes + lane_record_bytes(R);
+    int64_t* frow_s = reinterpret_cast<int64_t*>(stage + (size_t)NF * kStagePitch);
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int CB = a.count_bits, LB = a.lo_bits;
     const uint32_t lo_mask = (1u << LB) - 1u;
+    // record word x = (lo << CB) | (first cell of the node << 1) | 1: the addend of word A with the
+    // cell index in the bits the count field leaves free (a tile has fewer than 2^CB rows and a
+    // tuple fewer than 2^(CB-1) cells: pb_train_prepare keeps CB >= 11)
+    const uint32_t off_mask = ((1u << (CB - 1)) - 1u) << 8;
+    const uint32_t a_mask = ~(((1u << CB) - 1u) & ~1u);
 
     for (int i = threadIdx.x; i < T * n_cells * 64; i += blockDim.x) cells[i] = 0u;
 
-    // features of this lane: T tuples of A consecutive sampled features
-    constexpr int FPL = A * T;
-    constexpr int TL = 32 / R;            // tuple-owning lanes per phase
-    constexpr int PR = kLaneRows / R;     // rows of a chunk walked by one phase
-    constexpr int WPP = PR / 8;           // 32-bit code words per feature and phase
+    // features of this lane: T tuples of A consecutive sampled features.  Staged slot of feature i
+    // of tuple-lane l: i * TL + l.
     const int phase = lane / TL;
-    const int feat0 = (blockIdx.y * TL + (lane - phase * TL)) * FPL;
+    const int col0 = lane - phase * TL;
+    const int feat0 = (blockIdx.y * TL + col0) * FPL;
     const int n_mine = max(0, min(FPL, a.n_feat - feat0));
-    const uint8_t* frow[FPL];
-#pragma unroll
-    for (int i = 0; i < FPL; ++i)
-        frow[i] = a.codes + (int64_t)__ldg(a.feat_rows + min(feat0 + i, a.n_feat - 1)) * a.pitch;
+    for (int s = threadIdx.x; s < NF; s += blockDim.x) {
+        const int f = (blockIdx.y * TL + (s % TL)) * FPL + s / TL;
+        frow_s[s] = (int64_t)__ldg(a.feat_rows + min(f, a.n_feat - 1)) * a.pitch;
+    }
     __syncthreads();
+
+    // one block of codes: NF lines of 128 bytes, eight consecutive threads per line
+    auto fetch_block = [&](int b) {
+        for (int p = threadIdx.x; p < NF * 8; p += blockDim.x) {
+            const int s = p >> 3, part = p & 7;
+            const unsigned char* src = a.codes + frow_s[s] + (int64_t)b * (kBlockRows / 2) + part * 16;
+            const uint32_t dst = (uint32_t)__cvta_generic_to_shared(stage + s * kStagePitch + part * 16);
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(dst), "l"(src) : "memory");
+        }
+        asm volatile("cp.async.commit_group;\n" ::: "memory");
+    };
 
     unsigned char* lane_base = smb + lane * 4;
     // (a phase's records start one entry further apart than its rows, which keeps the R broadcast
     // addresses of a row step in different banks)
-    uint2* st = staging + warp * (kLaneRows + R);
+    uint2* st = records + warp * (kLaneRows + R);
     const uint2* st_mine = st + phase * (PR + 1);
-    const int c0 = r0 / kLaneRows, c1 = (r1 + kLaneRows - 1) / kLaneRows;
-    const uint32_t nb_scaled = (uint32_t)nb * kLaneCellBytes;
+    const int b0 = r0 / kBlockRows, b1 = (r1 + kBlockRows - 1) / kBlockRows;
 
-    uint32_t w[FPL][WPP];
-    int raw_s[2], raw_g[2];
-    auto load_chunk = [&](int c, uint32_t (&ww)[FPL][WPP], int (&rs)[2], int (&rg)[2]) {
-        const int r = c * kLaneRows + 2 * lane;  // lane l stages rows 2l and 2l+1 of the chunk
-        const uint32_t sv = *reinterpret_cast<const uint32_t*>(a.slot + r);
-        const int2 gv = *reinterpret_cast<const int2*>(a.gq + r);
-        rs[0] = sv & 0xFFFF;
-        rs[1] = sv >> 16;
-        rg[0] = gv.x;
-        rg[1] = gv.y;
+    int raw_s = 0, raw_g = 0;  // slot and gradient of row (block, warp, lane), loaded one block ahead
+    auto load_state = [&](int b, int& rs, int& rg) {
+        const int r = b * kBlockRows + warp * kLaneRows + lane;
+        rs = a.slot[r];
+        rg = a.gq[r];
+    };
+    if (b0 < b1) {
+        fetch_block(b0);
+        load_state(b0, raw_s, raw_g);
+    }
+    for (int b = b0; b < b1; ++b) {
+        asm volatile("cp.async.wait_group 0;\n" ::: "memory");
+        __syncthreads();  // the block is complete
+        uint32_t w[FPL][WPP];
 #pragma unroll
         for (int i = 0; i < FPL; ++i) {
-            const unsigned char* p = frow[i] + (int64_t)c * (kLaneRows / 2) + phase * (PR / 2);
+            const unsigned char* p = stage + (i * TL + col0) * kStagePitch + warp * (kLaneRows / 2) + phase * (PR / 2);
             if (R == 1) {
-                // one 32-byte sector per lane in a single 256-bit load
-                uint4 v0, v1;
-                asm("ld.global.nc.v8.u32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];\n"
-                    : "=r"(v0.x), "=r"(v0.y), "=r"(v0.z), "=r"(v0.w), "=r"(v1.x), "=r"(v1.y), "=r"(v1.z), "=r"(v1.w)
-                    : "l"(p));
-                ww[i][0] = v0.x; ww[i][1] = v0.y; ww[i][2] = v0.z; ww[i][3] = v0.w;
-                ww[i][WPP - 4] = v1.x; ww[i][WPP - 3] = v1.y; ww[i][WPP - 2] = v1.z; ww[i][WPP - 1] = v1.w;
+                const uint4 v = *reinterpret_cast<const uint4*>(p);
+                w[i][0] = v.x; w[i][1 % WPP] = v.y; w[i][2 % WPP] = v.z; w[i][3 % WPP] = v.w;
             } else if (R == 2) {
-                const uint4 v0 = __ldg(reinterpret_cast<const uint4*>(p));
-                ww[i][0] = v0.x; ww[i][1] = v0.y; ww[i][WPP - 2] = v0.z; ww[i][WPP - 1] = v0.w;
+                const uint2 v = *reinterpret_cast<const uint2*>(p);
+                w[i][0] = v.x; w[i][1 % WPP] = v.y;
             } else {
-                const uint2 v0 = __ldg(reinterpret_cast<const uint2*>(p));
-                ww[i][0] = v0.x; ww[i][WPP - 1] = v0.y;
+                w[i][0] = *reinterpret_cast<const uint32_t*>(p);
             }
         }
-    };
-    int c = c0 + warp;
-    if (c < c1) load_chunk(c, w, raw_s, raw_g);
-    for (; c < c1; c += kLaneWarps) {
-        bool any_ok = false;
-#pragma unroll
-        for (int h = 0; h < 2; ++h) {
-            const int r = c * kLaneRows + 2 * lane + h;
-            const bool ok = (r >= r0) & (r < r1) & (raw_s[h] < n_nodes);
+        __syncthreads();  // every warp holds its codes: the stage is free for the next block
+        if (b + 1 < b1) fetch_block(b + 1);
+
+        const int r = b * kBlockRows + warp * kLaneRows + lane;
+        const bool ok = (r >= r0) & (r < r1) & (raw_s < n_nodes);
 #ifdef PB_DEBUG_BOUNDS
-            if ((r >= r0) & (r < r1) & (raw_s[h] != (int)kSlotNone) & (raw_s[h] >= a.n_nodes) && a.debug_flags)
-                atomicOr(a.debug_flags, kDbgSlot);
+        if ((r >= r0) & (r < r1) & (raw_s != (int)kSlotNone) & (raw_s >= a.n_nodes) && a.debug_flags)
+            atomicOr(a.debug_flags, kDbgSlot);
 #endif
-            any_ok |= ok;
-            // a row that is not accumulated adds zero to the cells of node 0: the row steps below
-            // carry no branch, so the rows of a batch and the tuples of a lane interleave freely.
-            // Record: {byte offset of the node's cells | 1 when the row counts, gradient}: 8 bytes, so
-            // that the broadcast load of a row step is two shared-memory wavefronts, not four.
+        {
             uint2 rec;
-            rec.x = ok ? ((uint32_t)(raw_s[h] * cpn) * kLaneCellBytes) | 1u : 0u;
-            rec.y = ok ? (uint32_t)raw_g[h] : 0u;
-            st[(2 * lane + h) + (2 * lane + h) / PR] = rec;
+            rec.x = ok ? ((((uint32_t)raw_g & lo_mask) << CB) | ((uint32_t)(raw_s * cpn) << 1) | 1u) : 0u;
+            rec.y = ok ? (uint32_t)(raw_g >> LB) : 0u;
+            st[lane + lane / PR] = rec;
         }
-        const bool chunk_on = __any_sync(0xFFFFFFFFu, any_ok);  // (also orders the staging stores)
-        uint32_t wn[FPL][WPP];
-        int nraw_s[2], nraw_g[2];
-        const int cn = c + kLaneWarps;
-        if (cn < c1) load_chunk(cn, wn, nraw_s, nraw_g);
+        const bool chunk_on = __any_sync(0xFFFFFFFFu, ok);  // (also orders the record stores)
+        int nraw_s = 0, nraw_g = 0;
+        if (b + 1 < b1) load_state(b + 1, nraw_s, nraw_g);
         if (n_mine > 0 && chunk_on) {
+            uint32_t jw[T][2];  // joint codes of eight rows: even rows, odd rows (A == 2)
+            uint2 rawn[4];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) rawn[q] = st_mine[q];
 #pragma unroll
             for (int jb = 0; jb < PR; jb += 4) {
+                // the records of the next four rows are loaded before the atomics of these four
                 uint2 raw[4];
 #pragma unroll
-                for (int q = 0; q < 4; ++q) raw[q] = st_mine[jb + q];  // broadcast loads, issued together
+                for (int q = 0; q < 4; ++q) raw[q] = rawn[q];
+                if (jb + 4 < PR) {
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) rawn[q] = st_mine[jb + 4 + q];
+                }
                 uint4 rec[4];  // {cell offset, word A addend, word B addend}
 #pragma unroll
                 for (int q = 0; q < 4; ++q) {
-                    rec[q].x = raw[q].x & ~1u;
-                    rec[q].y = ((raw[q].y & lo_mask) << CB) + (raw[q].x & 1u);
-                    rec[q].z = (uint32_t)((int32_t)raw[q].y >> LB);
+                    rec[q].x = (raw[q].x << 7) & off_mask;
+                    rec[q].y = raw[q].x & a_mask;
+                    rec[q].z = raw[q].y;
                 }
 #pragma unroll
                 for (int q = 0; q < 4; ++q) {
                     const int j = jb + q;
-                    {
-                        const int bit = (j & 7) * 4;
+                    const int bit = (j & 7) * 4;
 #pragma unroll
-                        for (int t = 0; t < T; ++t) {
-                            // joint code of the tuple, pre-scaled by the cell pitch (256 bytes)
-                            const uint32_t w0 = w[t * A][j >> 3];
+                    for (int t = 0; t < T; ++t) {
+                        const uint32_t w0 = w[t * A][j >> 3];
 #ifdef PB_DEBUG_BOUNDS
-                            if (rec[q].y | rec[q].z | (raw[q].x & 1u)) {  // an accumulated row: its codes must be bins
-                                bool bad = ((w0 >> bit) & 0xFu) >= (uint32_t)nb;
+                        if (raw[q].x & 1u) {  // an accumulated row: its codes must be bins
+                            bool bad = ((w0 >> bit) & 0xFu) >= (uint32_t)nb;
 #pragma unroll
-                                for (int i = 1; i < A; ++i) bad |= ((w[t * A + i][j >> 3] >> bit) & 0xFu) >= (uint32_t)nb;
-                                if (bad && A * t < n_mine) {
-                                    if (a.debug_flags) atomicOr(a.debug_flags, kDbgCode);
-                                    continue;
-                                }
+                            for (int i = 1; i < A; ++i) bad |= ((w[t * A + i][j >> 3] >> bit) & 0xFu) >= (uint32_t)nb;
+                            if (bad && A * t < n_mine) {
+                                if (a.debug_flags) atomicOr(a.debug_flags, kDbgCode);
+                                continue;
                             }
-#endif
-                            uint32_t off = (bit >= 8) ? ((w0 >> (bit - 8)) & 0xF00u) : ((w0 << (8 - bit)) & 0xF00u);
-                            uint32_t mul = nb_scaled;
-#pragma unroll
-                            for (int i = 1; i < A; ++i) {
-                                off += mul * ((w[t * A + i][j >> 3] >> bit) & 0xFu);
-                                mul *= (uint32_t)nb;
-                            }
-                            unsigned char* cell = lane_base + (rec[q].x + off + (uint32_t)t * slot_bytes);
-                            atomicAdd(reinterpret_cast<uint32_t*>(cell), rec[q].y);
-                            atomicAdd(reinterpret_cast<int*>(cell + 128), (int)rec[q].z);
                         }
+#endif
+                        uint32_t off;  // joint code of the tuple times the cell pitch (256 bytes)
+                        if (A == 2) {
+                            // Joint codes of eight rows at a time: the even and the odd nibbles of the two
+                            // code words as bytes c0 + nb * c1 (at most 240: no carry between bytes); a
+                            // row's cell offset is its byte moved to bits 8-15.
+                            if ((j & 7) == 0) {
+                                const uint32_t w1 = w[t * A + 1][j >> 3];
+                                jw[t][0] = (w1 & 0x0F0F0F0Fu) * (uint32_t)nb + (w0 & 0x0F0F0F0Fu);
+                                jw[t][1] = ((w1 >> 4) & 0x0F0F0F0Fu) * (uint32_t)nb + ((w0 >> 4) & 0x0F0F0F0Fu);
+                            }
+                            off = __byte_perm(jw[t][j & 1], 0u, 0x4404u | (uint32_t)(((j & 7) >> 1) << 4));
+                        } else {
+                            off = (bit >= 8) ? ((w0 >> (bit - 8)) & 0xF00u) : ((w0 << (8 - bit)) & 0xF00u);
+                        }
+                        unsigned char* cell = lane_base + (rec[q].x + off + (uint32_t)t * slot_bytes);
+                        atomicAdd(reinterpret_cast<uint32_t*>(cell), rec[q].y);
+                        atomicAdd(reinterpret_cast<int*>(cell + 128), (int)rec[q].z);
                     }
                 }
             }
         }
-        __syncwarp();
-        if (cn < c1) {
-#pragma unroll
-            for (int i = 0; i < FPL; ++i)
-#pragma unroll
-                for (int q = 0; q < WPP; ++q) w[i][q] = wn[i][q];
-            raw_s[0] = nraw_s[0]; raw_s[1] = nraw_s[1];
-            raw_g[0] = nraw_g[0]; raw_g[1] = nraw_g[1];
-        }
+        __syncwarp();  // the records are rewritten in the next step
+        raw_s = nraw_s;
+        raw_g = nraw_g;
     }
     __syncthreads();
 
     // flush: marginals of this lane's joint tables -> [feature][era][node][bin]; the R phases of a
     // warp take different items and add up the columns of the R lanes that own the tuple
     const uint32_t cmask = (1u << CB) - 1u;
-    const int col0 = lane - phase * TL;
     if (a.fuse) {
         // ---- fused flush: per-era gains instead of the histogram -----------------------------------
         // The CTA holds the complete cells of its era (one tile per era), so everything the scorer
@@ -718,7 +749,7 @@ __global__ void __launch_bounds__(kLaneWarps * 32, 2) hist_lane_kernel(HistKerne
 
 template <int A, int T, int R>
 int launch_lane_r(const HistKernelArgs& a, size_t cell_bytes, cudaStream_t stream) {
-    const size_t smem = cell_bytes + (size_t)kLaneWarps * (kLaneRows + R) * sizeof(uint2);
+    const size_t smem = cell_bytes + lane_extra_bytes(R, A * T);
     if (smem > 48 * 1024)
         PB_CUDA_TRY(cudaFuncSetAttribute(hist_lane_kernel<A, T, R>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          (int)smem));
@@ -745,7 +776,7 @@ int hist_max_arity() {
 
 bool hist_can_fuse(const HistLaunch& h) {
     return h.code_bits == 4 && h.max_era_rows <= kTileRowsMax &&
-           (int64_t)h.n_nodes * h.max_bins * kLaneCellBytes <= kLaneSmemMax && h.n_feat > 0 && h.n_nodes > 0;
+           (int64_t)h.n_nodes * h.max_bins * kLaneCellBytes <= kLaneCellsMax && h.n_feat > 0 && h.n_nodes > 0;
 }
 
 int launch_hist(const HistLaunch& h, cudaStream_t stream) {
@@ -794,35 +825,46 @@ int launch_hist(const HistLaunch& h, cudaStream_t stream) {
 
     // lane-private kernel when a lane's cells are few: tuples of A features (joint code) as wide as
     // the cells allow, then T tuples per lane while shared memory lasts (A * T <= 4)
-    if (h.code_bits == 4 && (int64_t)h.n_nodes * h.max_bins * kLaneCellBytes <= kLaneSmemMax) {
+    if (h.code_bits == 4 && (int64_t)h.n_nodes * h.max_bins * kLaneCellBytes <= kLaneCellsMax) {
         // Pick the tuple width A (joint code), the tuples per lane T and the row phases R by a cost
-        // model fitted to measured launches (microseconds for a tile of 4 700 rows): a CTA spends
-        // 28.7 * (0.9 + T) / R per tile on the row steps (0.9: staging and record load, 1 per tuple:
-        // its two atomics and code extraction) plus 0.08 per KB of cells for zeroing and flushing
-        // them, and CTAs beyond two per SM queue up.
+        // model of one CTA (microseconds for a tile of 4 700 rows): the row steps cost
+        // kRowUs * (kRowFixed + T) / R (kRowFixed: record load and decode, 1 per tuple: its two atomics
+        // and code extraction), zeroing and flushing the cells kCellUs per KB, and an SM holds as
+        // many CTAs as their shared memory allows, at most kCtasMax.
         const int cap = h.max_arity < 2 ? h.max_arity : 2;  // wider joint codes measured slower
         int arity = 1, tuples = 1, phases = 1;
         static const int max_phases = [] {  // PACKBOOST_HIST_PHASES=1|2 lowers the row-phase cap (tuning)
             const char* e = getenv("PACKBOOST_HIST_PHASES");
             return (e && (e[0] == '1' || e[0] == '2') && e[1] == 0) ? e[0] - '0' : 4;
         }();
+        static const int force_tuples = [] {  // PACKBOOST_HIST_TUPLES=1|2|4 caps the tuples per lane (tuning)
+            const char* e = getenv("PACKBOOST_HIST_TUPLES");
+            return (e && (e[0] == '1' || e[0] == '2' || e[0] == '4') && e[1] == 0) ? e[0] - '0' : 4;
+        }();
         int64_t cpn = h.max_bins;
         double best = 1e30;
         {
+            constexpr double kRowUs = 14.0, kRowFixed = 0.9, kCellUs = 0.08;
+            constexpr int kCtasMax = 2;  // (registers)
             const double tile_scale = (double)max_tile / 4700.0;
             int64_t c = h.max_bins;
             for (int a_try = 1; a_try <= cap; ++a_try, c *= h.max_bins) {
-                for (int t_try = 1; t_try * a_try <= 4; t_try *= 2) {
+                for (int t_try = 1; t_try <= force_tuples; t_try *= 2) {
                     const size_t bytes = (size_t)h.n_nodes * c * kLaneCellBytes * t_try;
-                    if (bytes > (size_t)kLaneSmemMax) continue;
+                    if (bytes > (size_t)kLaneCellsMax) continue;
                     for (int r_try = 1; r_try <= max_phases; r_try *= 2) {
                         const int per_cta = (32 / r_try) * a_try * t_try;
                         const int blocks = (h.n_feat + per_cta - 1) / per_cta;
+                        const size_t smem = bytes + lane_extra_bytes(r_try, a_try * t_try) + 1024;
+                        int per_sm = (int)((size_t)228 * 1024 / smem);
+                        if (per_sm > kCtasMax) per_sm = kCtasMax;
+                        if (per_sm < 1) continue;
                         const double ctas = (double)h.n_eras * a.tiles_per_era * blocks;
-                        const double waves = ctas > 296.0 ? ctas / 296.0 : 1.0;
+                        const double slots = 148.0 * per_sm;
+                        const double waves = ctas > slots ? ctas / slots : 1.0;
                         // (a few per cent against more phases: equal estimates favour whole-warp tuples)
-                        const double cost = (r_try == 1 ? 1.0 : r_try == 2 ? 1.04 : 1.08) * waves *
-                                            (tile_scale * 28.7 * (0.9 + t_try) / r_try + 0.08 * (double)bytes / 1024.0);
+                        const double cost = (r_try == 1 ? 1.0 : r_try == 2 ? 1.04 : 1.08) * waves * per_sm *
+                                            (tile_scale * kRowUs * (kRowFixed + t_try) / r_try + kCellUs * (double)bytes / 1024.0);
                         if (cost < best * (1.0 - 1e-9)) { best = cost; arity = a_try; tuples = t_try; phases = r_try; cpn = c; }
                     }
                 }
@@ -833,7 +875,7 @@ int launch_hist(const HistLaunch& h, cudaStream_t stream) {
         a.feats_per_cta = (32 / phases) * arity * tuples;
         a.group = arity;
         a.copies = 1;
-        const size_t smem = slot * tuples;  // cells; the launcher adds the per-warp staging
+        const size_t smem = slot * tuples;  // cells; the launcher adds the records and the staged codes
         if (h.fuse && !a.use_atomics) {
             a.fuse = 1;
             h.fuse->tot_fpl = arity * tuples;
@@ -847,7 +889,8 @@ int launch_hist(const HistLaunch& h, cudaStream_t stream) {
         }
         prof_begin(h.prof, kProfHist, stream);
         int rc;
-        if (arity == 2) rc = (tuples == 2) ? launch_lane<2, 2>(a, smem, phases, stream) : launch_lane<2, 1>(a, smem, phases, stream);
+        if (arity == 2) rc = (tuples == 4) ? launch_lane<2, 4>(a, smem, phases, stream)
+                             : (tuples == 2) ? launch_lane<2, 2>(a, smem, phases, stream) : launch_lane<2, 1>(a, smem, phases, stream);
         else rc = (tuples == 4) ? launch_lane<1, 4>(a, smem, phases, stream)
                   : (tuples == 2) ? launch_lane<1, 2>(a, smem, phases, stream) : launch_lane<1, 1>(a, smem, phases, stream);
         prof_end(h.prof, kProfHist, stream);
