@@ -30,6 +30,7 @@
 //
 // Output layout: [feature][era][node_stride][bin] for both arrays.
 
+#include <stdio.h>
 #include <stdlib.h>
 
 #include <type_traits>
@@ -827,49 +828,52 @@ int launch_hist(const HistLaunch& h, cudaStream_t stream) {
     // the cells allow, then T tuples per lane while shared memory lasts (A * T <= 4)
     if (h.code_bits == 4 && (int64_t)h.n_nodes * h.max_bins * kLaneCellBytes <= kLaneCellsMax) {
         // Pick the tuple width A (joint code), the tuples per lane T and the row phases R by a cost
-        // model of one CTA (microseconds for a tile of 4 700 rows): the row steps cost
-        // kRowUs * (kRowFixed + T) / R (kRowFixed: record load and decode, 1 per tuple: its two atomics
-        // and code extraction), zeroing and flushing the cells kCellUs per KB, and an SM holds as
-        // many CTAs as their shared memory allows, at most kCtasMax.
+        // model fitted to measured launches (238 features, 574 tiles of 4 700 rows; relative units):
+        // a CTA spends kRow * (kRowFixed + T) / R on the row steps (kRowFixed: record load and
+        // decode, 1 per tuple: its two atomics and code extraction) plus kCell per KB of cells for
+        // zeroing and flushing them; an SM holds two CTAs (registers) when their shared memory
+        // allows, and a single CTA per SM runs its rows about 1.2 times slower than its share of two.
         const int cap = h.max_arity < 2 ? h.max_arity : 2;  // wider joint codes measured slower
         int arity = 1, tuples = 1, phases = 1;
         static const int max_phases = [] {  // PACKBOOST_HIST_PHASES=1|2 lowers the row-phase cap (tuning)
             const char* e = getenv("PACKBOOST_HIST_PHASES");
             return (e && (e[0] == '1' || e[0] == '2') && e[1] == 0) ? e[0] - '0' : 4;
         }();
-        static const int force_tuples = [] {  // PACKBOOST_HIST_TUPLES=1|2|4 caps the tuples per lane (tuning)
-            const char* e = getenv("PACKBOOST_HIST_TUPLES");
-            return (e && (e[0] == '1' || e[0] == '2' || e[0] == '4') && e[1] == 0) ? e[0] - '0' : 4;
+        // PACKBOOST_HIST_SHAPE="A T R" forces the launch shape where it fits and logs what is launched (tuning)
+        static const int* const forced = [] {
+            static int v[3];
+            const char* e = getenv("PACKBOOST_HIST_SHAPE");
+            return (e && sscanf(e, "%d %d %d", &v[0], &v[1], &v[2]) == 3) ? v : (const int*)nullptr;
         }();
         int64_t cpn = h.max_bins;
         double best = 1e30;
         {
-            constexpr double kRowUs = 14.0, kRowFixed = 0.9, kCellUs = 0.08;
-            constexpr int kCtasMax = 2;  // (registers)
+            constexpr double kRow = 38.5, kRowFixed = 0.3, kCell = 0.16;
             const double tile_scale = (double)max_tile / 4700.0;
             int64_t c = h.max_bins;
             for (int a_try = 1; a_try <= cap; ++a_try, c *= h.max_bins) {
-                for (int t_try = 1; t_try <= force_tuples; t_try *= 2) {
+                for (int t_try = 1; t_try * a_try <= 8; t_try *= 2) {
                     const size_t bytes = (size_t)h.n_nodes * c * kLaneCellBytes * t_try;
                     if (bytes > (size_t)kLaneCellsMax) continue;
                     for (int r_try = 1; r_try <= max_phases; r_try *= 2) {
                         const int per_cta = (32 / r_try) * a_try * t_try;
                         const int blocks = (h.n_feat + per_cta - 1) / per_cta;
                         const size_t smem = bytes + lane_extra_bytes(r_try, a_try * t_try) + 1024;
-                        int per_sm = (int)((size_t)228 * 1024 / smem);
-                        if (per_sm > kCtasMax) per_sm = kCtasMax;
-                        if (per_sm < 1) continue;
+                        const int per_sm = (2 * smem <= (size_t)228 * 1024) ? 2 : 1;
                         const double ctas = (double)h.n_eras * a.tiles_per_era * blocks;
                         const double slots = 148.0 * per_sm;
                         const double waves = ctas > slots ? ctas / slots : 1.0;
                         // (a few per cent against more phases: equal estimates favour whole-warp tuples)
-                        const double cost = (r_try == 1 ? 1.0 : r_try == 2 ? 1.04 : 1.08) * waves * per_sm *
-                                            (tile_scale * kRowUs * (kRowFixed + t_try) / r_try + kCellUs * (double)bytes / 1024.0);
+                        double cost = (r_try == 1 ? 1.0 : r_try == 2 ? 1.04 : 1.08) * waves * per_sm * (per_sm == 1 ? 1.2 : 1.0) *
+                                      (tile_scale * kRow * (kRowFixed + t_try) / r_try + kCell * (double)bytes / 1024.0);
+                        if (forced) cost = (a_try == forced[0] && t_try == forced[1] && r_try == forced[2]) ? 0.0 : cost + 1e9;
                         if (cost < best * (1.0 - 1e-9)) { best = cost; arity = a_try; tuples = t_try; phases = r_try; cpn = c; }
                     }
                 }
             }
         }
+        if (forced)
+            fprintf(stderr, "hist_lane_kernel<%d,%d,%d> nodes=%d features=%d\n", arity, tuples, phases, h.n_nodes, h.n_feat);
         const size_t slot = (size_t)h.n_nodes * cpn * kLaneCellBytes;
         a.nodes_per_chunk = h.n_nodes;
         a.feats_per_cta = (32 / phases) * arity * tuples;
@@ -891,7 +895,8 @@ int launch_hist(const HistLaunch& h, cudaStream_t stream) {
         int rc;
         if (arity == 2) rc = (tuples == 4) ? launch_lane<2, 4>(a, smem, phases, stream)
                              : (tuples == 2) ? launch_lane<2, 2>(a, smem, phases, stream) : launch_lane<2, 1>(a, smem, phases, stream);
-        else rc = (tuples == 4) ? launch_lane<1, 4>(a, smem, phases, stream)
+        else rc = (tuples == 8) ? launch_lane<1, 8>(a, smem, phases, stream)
+                  : (tuples == 4) ? launch_lane<1, 4>(a, smem, phases, stream)
                   : (tuples == 2) ? launch_lane<1, 2>(a, smem, phases, stream) : launch_lane<1, 1>(a, smem, phases, stream);
         prof_end(h.prof, kProfHist, stream);
         if (rc) return rc;
