@@ -226,6 +226,7 @@ __global__ void __launch_bounds__(THREADS) hist_kernel(HistKernelArgs a) {
 // ---- lane-private kernel for small cell counts ------------------------------------------------
 
 constexpr int kLaneCellBytes = 256;        // word A of lane l at l*4, word B at 128 + l*4: bank == lane
+__host__ __device__ constexpr int lane_cell_bytes(int R) { return R == 2 ? 128 : 256; }  // (two row phases share a column)
 constexpr int kLaneCellsMax = 100 * 1024;  // bytes of cells of one CTA (two CTAs per SM with the staged codes)
 constexpr int kLaneWarps = 8;
 constexpr int kLaneRows = 32;              // rows per warp and CTA step
@@ -304,7 +305,18 @@ __global__ void __launch_bounds__(kLaneWarps * 32, 2) hist_lane_kernel(HistKerne
 #pragma unroll
     for (int i = 1; i < A; ++i) cpn *= nb;
     const int n_cells = a.n_nodes * cpn;  // per tuple, sized for the upper bound of nodes
-    const uint32_t slot_bytes = (uint32_t)n_cells * kLaneCellBytes;
+    // Cell layout.  R != 2: every lane has a private column, word A of lane l at l*4 and word B at
+    // 128 + l*4 of a 256-byte cell.  R == 2: the two row phases of a tuple-lane share one column of a
+    // 128-byte cell (word A of column c at c*4, word B at 64 + c*4): phase 0 adds the word A of its
+    // row while phase 1 adds the word B of its own, then the other way round, so a warp instruction
+    // still touches every bank once, and twice as many cells fit.
+    constexpr bool SHARED = (R == 2);
+    constexpr int CELL_BYTES = lane_cell_bytes(R);
+    constexpr int CSH = SHARED ? 7 : 8;          // log2(CELL_BYTES)
+    constexpr int CW = CELL_BYTES / 4;           // words per cell
+    constexpr int BOFF = CW / 2;                 // word B follows the word-A columns
+    constexpr int PHS = SHARED ? 1 : R;          // phase columns the flush adds up
+    const uint32_t slot_bytes = (uint32_t)n_cells * CELL_BYTES;
     constexpr int FPL = A * T;
     constexpr int TL = 32 / R;            // tuple-owning lanes per phase
     constexpr int NF = TL * FPL;          // features of the CTA
@@ -320,10 +332,10 @@ __global__ void __launch_bounds__(kLaneWarps * 32, 2) hist_lane_kernel(HistKerne
     // record word x = (lo << CB) | (first cell of the node << 1) | 1: the addend of word A with the
     // cell index in the bits the count field leaves free (a tile has fewer than 2^CB rows and a
     // tuple fewer than 2^(CB-1) cells: pb_train_prepare keeps CB >= 11)
-    const uint32_t off_mask = ((1u << (CB - 1)) - 1u) << 8;
+    const uint32_t off_mask = ((1u << (CB - 1)) - 1u) << CSH;
     const uint32_t a_mask = ~(((1u << CB) - 1u) & ~1u);
 
-    for (int i = threadIdx.x; i < T * n_cells * 64; i += blockDim.x) cells[i] = 0u;
+    for (int i = threadIdx.x; i < T * n_cells * CW; i += blockDim.x) cells[i] = 0u;
 
     // features of this lane: T tuples of A consecutive sampled features.  Staged slot of feature i
     // of tuple-lane l: i * TL + l.
@@ -348,7 +360,9 @@ __global__ void __launch_bounds__(kLaneWarps * 32, 2) hist_lane_kernel(HistKerne
         asm volatile("cp.async.commit_group;\n" ::: "memory");
     };
 
-    unsigned char* lane_base = smb + lane * 4;
+    // first word this lane adds to and the distance to the second one
+    unsigned char* lane_base = SHARED ? smb + col0 * 4 + phase * 64 : smb + lane * 4;
+    const int second = SHARED ? (phase ? -64 : 64) : 128;
     // (a phase's records start one entry further apart than its rows, which keeps the R broadcast
     // addresses of a row step in different banks)
     uint2* st = records + warp * (kLaneRows + R);
@@ -418,9 +432,10 @@ __global__ void __launch_bounds__(kLaneWarps * 32, 2) hist_lane_kernel(HistKerne
                 uint4 rec[4];  // {cell offset, word A addend, word B addend}
 #pragma unroll
                 for (int q = 0; q < 4; ++q) {
-                    rec[q].x = (raw[q].x << 7) & off_mask;
-                    rec[q].y = raw[q].x & a_mask;
-                    rec[q].z = raw[q].y;
+                    rec[q].x = (raw[q].x << (CSH - 1)) & off_mask;
+                    const uint32_t wa = raw[q].x & a_mask, wb = raw[q].y;
+                    rec[q].y = (SHARED && phase) ? wb : wa;  // added to the first word
+                    rec[q].z = (SHARED && phase) ? wa : wb;  // added to the second
                 }
 #pragma unroll
                 for (int q = 0; q < 4; ++q) {
@@ -440,23 +455,23 @@ __global__ void __launch_bounds__(kLaneWarps * 32, 2) hist_lane_kernel(HistKerne
                             }
                         }
 #endif
-                        uint32_t off;  // joint code of the tuple times the cell pitch (256 bytes)
+                        uint32_t off;  // joint code of the tuple times the cell pitch
                         if (A == 2) {
                             // Joint codes of eight rows at a time: the even and the odd nibbles of the two
                             // code words as bytes c0 + nb * c1 (at most 240: no carry between bytes); a
-                            // row's cell offset is its byte moved to bits 8-15.
+                            // row's cell offset is its byte times the cell pitch.
                             if ((j & 7) == 0) {
                                 const uint32_t w1 = w[t * A + 1][j >> 3];
                                 jw[t][0] = (w1 & 0x0F0F0F0Fu) * (uint32_t)nb + (w0 & 0x0F0F0F0Fu);
                                 jw[t][1] = ((w1 >> 4) & 0x0F0F0F0Fu) * (uint32_t)nb + ((w0 >> 4) & 0x0F0F0F0Fu);
                             }
-                            off = __byte_perm(jw[t][j & 1], 0u, 0x4404u | (uint32_t)(((j & 7) >> 1) << 4));
+                            off = __byte_perm(jw[t][j & 1], 0u, 0x4440u | (uint32_t)((j & 7) >> 1)) << CSH;
                         } else {
-                            off = (bit >= 8) ? ((w0 >> (bit - 8)) & 0xF00u) : ((w0 << (8 - bit)) & 0xF00u);
+                            off = ((w0 >> bit) & 0xFu) << CSH;
                         }
                         unsigned char* cell = lane_base + (rec[q].x + off + (uint32_t)t * slot_bytes);
                         atomicAdd(reinterpret_cast<uint32_t*>(cell), rec[q].y);
-                        atomicAdd(reinterpret_cast<int*>(cell + 128), (int)rec[q].z);
+                        atomicAdd(reinterpret_cast<uint32_t*>(cell + second), rec[q].z);
                     }
                 }
             }
@@ -517,7 +532,7 @@ __global__ void __launch_bounds__(kLaneWarps * 32, 2) hist_lane_kernel(HistKerne
                     if (c) atomicAdd(z.lc_tot + tot0 + b * tot_step, c);
                     if (g) atomicAdd(reinterpret_cast<unsigned long long*>(z.lg_tot + tot0 + b * tot_step), (unsigned long long)g);
                 }
-                reinterpret_cast<float4*>(out)[0] = make_float4(gk[0].x, gk[0].y, gk[1].x, gk[1].y);
+reinterpret_cast<float4*>(out)[0] = make_float4(gk[0].x, gk[0].y, gk[1].x, gk[1].y);
                 reinterpret_cast<float4*>(out)[1] = make_float4(gk[2].x, gk[2].y, gk[3].x, gk[3].y);
             } else {
                 int kk = 0;
@@ -541,11 +556,11 @@ __global__ void __launch_bounds__(kLaneWarps * 32, 2) hist_lane_kernel(HistKerne
         for (int item = warp * R + phase; item < n_nodes * T; item += kLaneWarps * R) {
             const int n = item / T, t = item - n * T;
             if (A * t >= n_mine) continue;
-            const uint32_t* tcells = cells + (size_t)t * n_cells * 64;
+            const uint32_t* tcells = cells + (size_t)t * n_cells * CW;
             if (A == 2 && nb == 5) {
                 // every joint cell is read once and added to the row sum of one feature and the column
                 // sum of the other
-                const uint32_t* tc2 = tcells + (size_t)(n * 25) * 64 + col0;
+                const uint32_t* tc2 = tcells + (size_t)(n * 25) * CW + col0;
                 uint32_t a0[kLaneBinsMax], b0[kLaneBinsMax], a1[kLaneBinsMax], b1[kLaneBinsMax];
 #pragma unroll
                 for (int b = 0; b < kLaneBinsMax; ++b) a0[b] = b0[b] = a1[b] = b1[b] = 0u;
@@ -555,9 +570,9 @@ __global__ void __launch_bounds__(kLaneWarps * 32, 2) hist_lane_kernel(HistKerne
                     for (int c0 = 0; c0 < 5; ++c0) {
                         uint32_t aw = 0, bw = 0;
 #pragma unroll
-                        for (int ph = 0; ph < R; ++ph) {
-                            aw += tc2[(c1 * 5 + c0) * 64 + ph * TL];
-                            bw += tc2[(c1 * 5 + c0) * 64 + ph * TL + 32];
+                        for (int ph = 0; ph < PHS; ++ph) {
+                            aw += tc2[(c1 * 5 + c0) * CW + ph * TL];
+                            bw += tc2[(c1 * 5 + c0) * CW + ph * TL + BOFF];
                         }
                         a0[c0] += aw;
                         b0[c0] += bw;
@@ -581,11 +596,11 @@ __global__ void __launch_bounds__(kLaneWarps * 32, 2) hist_lane_kernel(HistKerne
                         uint32_t a_sum = 0, b_sum = 0;
                         for (int hi = 0; hi < above; ++hi)
                             for (int lo = 0; lo < below; ++lo) {
-                                const uint32_t cell = (uint32_t)(n * cpn + (hi * nb + b) * below + lo) * 64u + col0;
+                                const uint32_t cell = (uint32_t)(n * cpn + (hi * nb + b) * below + lo) * (uint32_t)CW + col0;
 #pragma unroll
-                                for (int ph = 0; ph < R; ++ph) {
+                                for (int ph = 0; ph < PHS; ++ph) {
                                     a_sum += tcells[cell + ph * TL];
-                                    b_sum += tcells[cell + ph * TL + 32];
+                                    b_sum += tcells[cell + ph * TL + BOFF];
                                 }
                             }
                         aw[b] = a_sum;
@@ -645,7 +660,7 @@ __global__ void __launch_bounds__(kLaneWarps * 32, 2) hist_lane_kernel(HistKerne
             const int g = item / T, t = item - g * T;
             if (A * t >= n_mine) continue;
             const int n0 = 4 * g;
-            const uint32_t* tc = cells + (size_t)t * n_cells * 64 + col0;
+            const uint32_t* tc = cells + (size_t)t * n_cells * CW + col0;
             uint32_t a0[20], b0[20], a1[20], b1[20];
 #pragma unroll
             for (int i = 0; i < 20; ++i) a0[i] = b0[i] = a1[i] = b1[i] = 0u;
@@ -655,9 +670,9 @@ __global__ void __launch_bounds__(kLaneWarps * 32, 2) hist_lane_kernel(HistKerne
 #pragma unroll
                     for (int c0 = 0; c0 < 5; ++c0) {
 #pragma unroll
-                        for (int ph = 0; ph < R; ++ph) {
-                            a0[q * 5 + c0] += tc[((n0 + q) * 5 + c0) * 64 + ph * TL];
-                            b0[q * 5 + c0] += tc[((n0 + q) * 5 + c0) * 64 + ph * TL + 32];
+                        for (int ph = 0; ph < PHS; ++ph) {
+                            a0[q * 5 + c0] += tc[((n0 + q) * 5 + c0) * CW + ph * TL];
+                            b0[q * 5 + c0] += tc[((n0 + q) * 5 + c0) * CW + ph * TL + BOFF];
                         }
                     }
                 } else {
@@ -669,9 +684,9 @@ __global__ void __launch_bounds__(kLaneWarps * 32, 2) hist_lane_kernel(HistKerne
                         for (int c0 = 0; c0 < 5; ++c0) {
                             uint32_t aw = 0, bw = 0;
 #pragma unroll
-                            for (int ph = 0; ph < R; ++ph) {
-                                aw += tc[((n0 + q) * 25 + c1 * 5 + c0) * 64 + ph * TL];
-                                bw += tc[((n0 + q) * 25 + c1 * 5 + c0) * 64 + ph * TL + 32];
+                            for (int ph = 0; ph < PHS; ++ph) {
+                                aw += tc[((n0 + q) * 25 + c1 * 5 + c0) * CW + ph * TL];
+                                bw += tc[((n0 + q) * 25 + c1 * 5 + c0) * CW + ph * TL + BOFF];
                             }
                             a0[q * 5 + c0] += aw;
                             b0[q * 5 + c0] += bw;
@@ -691,7 +706,7 @@ __global__ void __launch_bounds__(kLaneWarps * 32, 2) hist_lane_kernel(HistKerne
         for (int item = warp * R + phase; item < n_nodes * T; item += kLaneWarps * R) {
             const int n = item / T, t = item - n * T;
             if (2 * t >= n_mine) continue;
-            const uint32_t* tc = cells + (size_t)t * n_cells * 64 + (size_t)(n * 25) * 64 + col0;
+            const uint32_t* tc = cells + (size_t)t * n_cells * CW + (size_t)(n * 25) * CW + col0;
             uint32_t a0[kLaneBinsMax], b0[kLaneBinsMax], a1[kLaneBinsMax], b1[kLaneBinsMax];
 #pragma unroll
             for (int b = 0; b < kLaneBinsMax; ++b) a0[b] = b0[b] = a1[b] = b1[b] = 0u;
@@ -701,9 +716,9 @@ __global__ void __launch_bounds__(kLaneWarps * 32, 2) hist_lane_kernel(HistKerne
                 for (int c0 = 0; c0 < 5; ++c0) {
                     uint32_t aw = 0, bw = 0;
 #pragma unroll
-                    for (int ph = 0; ph < R; ++ph) {
-                        aw += tc[(c1 * 5 + c0) * 64 + ph * TL];
-                        bw += tc[(c1 * 5 + c0) * 64 + ph * TL + 32];
+                    for (int ph = 0; ph < PHS; ++ph) {
+                        aw += tc[(c1 * 5 + c0) * CW + ph * TL];
+                        bw += tc[(c1 * 5 + c0) * CW + ph * TL + BOFF];
                     }
                     a0[c0] += aw;
                     b0[c0] += bw;
@@ -722,7 +737,7 @@ __global__ void __launch_bounds__(kLaneWarps * 32, 2) hist_lane_kernel(HistKerne
         int below = 1;  // bins^fi
         for (int i = 0; i < fi; ++i) below *= nb;
         const int above = cpn / (below * nb);
-        const uint32_t* tcells = cells + (size_t)t * n_cells * 64;
+        const uint32_t* tcells = cells + (size_t)t * n_cells * CW;
         uint32_t aw[kLaneBinsMax], bw[kLaneBinsMax];   // packed sums of the bins of this (feature, node)
 #pragma unroll
         for (int b = 0; b < kLaneBinsMax; ++b) {
@@ -734,11 +749,11 @@ __global__ void __launch_bounds__(kLaneWarps * 32, 2) hist_lane_kernel(HistKerne
             uint32_t a_sum = 0, b_sum = 0;
             for (int hi = 0; hi < above; ++hi)
                 for (int lo = 0; lo < below; ++lo) {
-                    const uint32_t cell = (uint32_t)(n * cpn + (hi * nb + b) * below + lo) * 64u + col0;
+                    const uint32_t cell = (uint32_t)(n * cpn + (hi * nb + b) * below + lo) * (uint32_t)CW + col0;
 #pragma unroll
-                    for (int ph = 0; ph < R; ++ph) {
+                    for (int ph = 0; ph < PHS; ++ph) {
                         a_sum += tcells[cell + ph * TL];
-                        b_sum += tcells[cell + ph * TL + 32];
+                        b_sum += tcells[cell + ph * TL + BOFF];
                     }
                 }
             aw[b] = a_sum;
@@ -828,11 +843,13 @@ int launch_hist(const HistLaunch& h, cudaStream_t stream) {
     // the cells allow, then T tuples per lane while shared memory lasts (A * T <= 4)
     if (h.code_bits == 4 && (int64_t)h.n_nodes * h.max_bins * kLaneCellBytes <= kLaneCellsMax) {
         // Pick the tuple width A (joint code), the tuples per lane T and the row phases R by a cost
-        // model fitted to measured launches (238 features, 574 tiles of 4 700 rows; relative units):
-        // a CTA spends kRow * (kRowFixed + T) / R on the row steps (kRowFixed: record load and
-        // decode, 1 per tuple: its two atomics and code extraction) plus kCell per KB of cells for
-        // zeroing and flushing them; an SM holds two CTAs (registers) when their shared memory
-        // allows, and a single CTA per SM runs its rows about 1.2 times slower than its share of two.
+        // model fitted to measured launches (238 features, 574 tiles of 4 700 rows, microseconds per
+        // launch).  A pass (the CTAs of one feature range) costs kPass + kPassFeat per feature of a
+        // lane (block fetch, code reads, records, barriers) + kTuple * T / R (the row steps: two
+        // atomics and the code extraction per tuple) + kCell per KB of cells (zeroing and flush);
+        // an SM holds two CTAs (registers) when their shared memory allows, and a single CTA per SM
+        // runs about 1.2 times slower than its share of two.  The model reproduces the measured order
+        // of every shape at every depth of that workload.
         const int cap = h.max_arity < 2 ? h.max_arity : 2;  // wider joint codes measured slower
         int arity = 1, tuples = 1, phases = 1;
         static const int max_phases = [] {  // PACKBOOST_HIST_PHASES=1|2 lowers the row-phase cap (tuning)
@@ -848,14 +865,14 @@ int launch_hist(const HistLaunch& h, cudaStream_t stream) {
         int64_t cpn = h.max_bins;
         double best = 1e30;
         {
-            constexpr double kRow = 38.5, kRowFixed = 0.3, kCell = 0.16;
+            constexpr double kPass = 15.0, kPassFeat = 2.2, kTuple = 33.0, kCell = 0.145;
             const double tile_scale = (double)max_tile / 4700.0;
             int64_t c = h.max_bins;
             for (int a_try = 1; a_try <= cap; ++a_try, c *= h.max_bins) {
                 for (int t_try = 1; t_try * a_try <= 8; t_try *= 2) {
-                    const size_t bytes = (size_t)h.n_nodes * c * kLaneCellBytes * t_try;
-                    if (bytes > (size_t)kLaneCellsMax) continue;
                     for (int r_try = 1; r_try <= max_phases; r_try *= 2) {
+                        const size_t bytes = (size_t)h.n_nodes * c * lane_cell_bytes(r_try) * t_try;
+                        if (bytes > (size_t)kLaneCellsMax) continue;
                         const int per_cta = (32 / r_try) * a_try * t_try;
                         const int blocks = (h.n_feat + per_cta - 1) / per_cta;
                         const size_t smem = bytes + lane_extra_bytes(r_try, a_try * t_try) + 1024;
@@ -865,7 +882,8 @@ int launch_hist(const HistLaunch& h, cudaStream_t stream) {
                         const double waves = ctas > slots ? ctas / slots : 1.0;
                         // (a few per cent against more phases: equal estimates favour whole-warp tuples)
                         double cost = (r_try == 1 ? 1.0 : r_try == 2 ? 1.04 : 1.08) * waves * per_sm * (per_sm == 1 ? 1.2 : 1.0) *
-                                      (tile_scale * kRow * (kRowFixed + t_try) / r_try + kCell * (double)bytes / 1024.0);
+                                      (tile_scale * (kPass + kPassFeat * a_try * t_try + kTuple * t_try / r_try) +
+                                       kCell * (double)bytes / 1024.0);
                         if (forced) cost = (a_try == forced[0] && t_try == forced[1] && r_try == forced[2]) ? 0.0 : cost + 1e9;
                         if (cost < best * (1.0 - 1e-9)) { best = cost; arity = a_try; tuples = t_try; phases = r_try; cpn = c; }
                     }
@@ -874,7 +892,7 @@ int launch_hist(const HistLaunch& h, cudaStream_t stream) {
         }
         if (forced)
             fprintf(stderr, "hist_lane_kernel<%d,%d,%d> nodes=%d features=%d\n", arity, tuples, phases, h.n_nodes, h.n_feat);
-        const size_t slot = (size_t)h.n_nodes * cpn * kLaneCellBytes;
+        const size_t slot = (size_t)h.n_nodes * cpn * lane_cell_bytes(phases);
         a.nodes_per_chunk = h.n_nodes;
         a.feats_per_cta = (32 / phases) * arity * tuples;
         a.group = arity;
