@@ -137,8 +137,8 @@ typedef struct pb_train_state {
     const int32_t* era_offsets;  /* [n_eras + 1] */
     const int32_t* thr_ids;      /* [n_thresholds] threshold (bin) ids, ascending */
     const int32_t* feat_local;   /* [n_features_total] local row of a global feature, -1 if not held */
-    const float* y;              /* [n_rows] */
-    float* preds;                /* [n_rows] */
+    const float* y;              /* [n_rows], 16-byte aligned */
+    float* preds;                /* [n_rows], 16-byte aligned */
     int32_t* gq;                 /* [rows_padded], 16-byte aligned */
     uint16_t* slot;              /* [rows_padded], 16-byte aligned; pb_round_begin sets the entries past n_rows to 0xFFFF */
     uint16_t* leaf;              /* [rows_padded], 16-byte aligned */

@@ -39,19 +39,46 @@ __global__ void round_reset_kernel(Ctl c) {
     }
 }
 
-// preds += delta[leaf] (optional), track max |preds - y|
+// preds += delta[leaf] (optional), track max |preds - y|.  Four rows per thread and step (all row
+// arrays are 16-byte aligned; y and preds hold n rows, so their last group is read row by row).
 __global__ void __launch_bounds__(kRowThreads) preds_absmax_kernel(
     float* __restrict__ preds, const float* __restrict__ y, const uint16_t* __restrict__ leaf,
     const float* __restrict__ delta, int64_t n, int apply, CtlHead* head) {
     float m = 0.f;
-    for (int64_t r = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; r < n; r += (int64_t)gridDim.x * blockDim.x) {
-        float p = preds[r];
-        if (apply) {
-            p = __fadd_rn(p, delta[leaf[r]]);
-            preds[r] = p;
+    const int64_t n4 = (n + 3) >> 2;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t r = i << 2;
+        float p[4] = {0.f, 0.f, 0.f, 0.f}, yy[4] = {0.f, 0.f, 0.f, 0.f};
+        if (r + 3 < n) {
+            const float4 pv = *reinterpret_cast<const float4*>(preds + r);
+            const float4 yv = *reinterpret_cast<const float4*>(y + r);
+            p[0] = pv.x; p[1] = pv.y; p[2] = pv.z; p[3] = pv.w;
+            yy[0] = yv.x; yy[1] = yv.y; yy[2] = yv.z; yy[3] = yv.w;
+        } else {  // (y and preds hold n rows, not the padded count)
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+                if (r + u < n) {
+                    p[u] = preds[r + u];
+                    yy[u] = y[r + u];
+                }
         }
-        const float g = __fsub_rn(p, y[r]);
-        m = fmaxf(m, fabsf(g));
+        if (apply) {
+            const uint2 lv = *reinterpret_cast<const uint2*>(leaf + r);
+            const uint32_t l[4] = {lv.x & 0xFFFFu, lv.x >> 16, lv.y & 0xFFFFu, lv.y >> 16};
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+                if (r + u < n) p[u] = __fadd_rn(p[u], delta[l[u]]);
+            if (r + 3 < n) {
+                *reinterpret_cast<float4*>(preds + r) = make_float4(p[0], p[1], p[2], p[3]);
+            } else {
+#pragma unroll
+                for (int u = 0; u < 4; ++u)
+                    if (r + u < n) preds[r + u] = p[u];
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+            if (r + u < n) m = fmaxf(m, fabsf(__fsub_rn(p[u], yy[u])));
     }
     for (int d = 16; d > 0; d >>= 1) m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, d));
     __shared__ float wm[kRowThreads / 32];
@@ -63,25 +90,44 @@ __global__ void __launch_bounds__(kRowThreads) preds_absmax_kernel(
     }
 }
 
-// gq = rint((preds - y) * scale); rows back to the root; sum of gq
+// gq = rint((preds - y) * scale); rows back to the root; sum of gq.  Four rows per thread and step.
 __global__ void __launch_bounds__(kRowThreads) quantise_kernel(
     const float* __restrict__ preds, const float* __restrict__ y, int32_t* __restrict__ gq,
     uint16_t* __restrict__ slot, uint16_t* __restrict__ leaf, int64_t n, int64_t n_pad, CtlHead* head, int gq_bits) {
     float inv;
     const float scale = scale_from_max(__uint_as_float(head->max_abs_bits), gq_bits, &inv);
     long long acc = 0;
-    for (int64_t r = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; r < n_pad; r += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t n4 = n_pad >> 2;  // n_pad is a multiple of 256
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t r = i << 2;
+        int q[4] = {0, 0, 0, 0};
+        uint32_t sl[4] = {kSlotNone, kSlotNone, kSlotNone, kSlotNone};
         if (r < n) {
-            const float g = __fsub_rn(preds[r], y[r]);
-            const int q = __float2int_rn(__fmul_rn(g, scale));
-            gq[r] = q;
-            slot[r] = 0;
-            acc += q;
-        } else {
-            gq[r] = 0;
-            slot[r] = kSlotNone;
+            float p[4] = {0.f, 0.f, 0.f, 0.f}, yy[4] = {0.f, 0.f, 0.f, 0.f};
+            if (r + 3 < n) {
+                const float4 pv = *reinterpret_cast<const float4*>(preds + r);
+                const float4 yv = *reinterpret_cast<const float4*>(y + r);
+                p[0] = pv.x; p[1] = pv.y; p[2] = pv.z; p[3] = pv.w;
+                yy[0] = yv.x; yy[1] = yv.y; yy[2] = yv.z; yy[3] = yv.w;
+            } else {  // (y and preds hold n rows, not the padded count)
+#pragma unroll
+                for (int u = 0; u < 4; ++u)
+                    if (r + u < n) {
+                        p[u] = preds[r + u];
+                        yy[u] = y[r + u];
+                    }
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+                if (r + u < n) {
+                    q[u] = __float2int_rn(__fmul_rn(__fsub_rn(p[u], yy[u]), scale));
+                    sl[u] = 0u;
+                    acc += q[u];
+                }
         }
-        leaf[r] = 0;
+        *reinterpret_cast<int4*>(gq + r) = make_int4(q[0], q[1], q[2], q[3]);
+        *reinterpret_cast<uint2*>(slot + r) = make_uint2(sl[0] | (sl[1] << 16), sl[2] | (sl[3] << 16));
+        *reinterpret_cast<uint2*>(leaf + r) = make_uint2(0u, 0u);
     }
     for (int d = 16; d > 0; d >>= 1) acc += __shfl_xor_sync(0xFFFFFFFFu, acc, d);
     __shared__ long long ws[kRowThreads / 32];
@@ -538,6 +584,7 @@ static int check_state(const pb_train_state* st) {
     PB_REQUIRE((uintptr_t)st->codes % 32 == 0, "codes must be 32-byte aligned");
     PB_REQUIRE(((uintptr_t)st->gq % 16 == 0) && ((uintptr_t)st->slot % 16 == 0) && ((uintptr_t)st->leaf % 16 == 0),
                "gq, slot and leaf must be 16-byte aligned");
+    PB_REQUIRE(((uintptr_t)st->y % 16 == 0) && ((uintptr_t)st->preds % 16 == 0), "y and preds must be 16-byte aligned");
     return PB_OK;
 }
 
