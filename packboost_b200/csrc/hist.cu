@@ -335,7 +335,10 @@ __global__ void __launch_bounds__(kLaneWarps * 32, 2) hist_lane_kernel(HistKerne
     const uint32_t off_mask = ((1u << (CB - 1)) - 1u) << CSH;
     const uint32_t a_mask = ~(((1u << CB) - 1u) & ~1u);
 
-    for (int i = threadIdx.x; i < T * n_cells * CW; i += blockDim.x) cells[i] = 0u;
+    {  // (a cell is 128 or 256 bytes: whole 16-byte stores)
+        uint4* z = reinterpret_cast<uint4*>(cells);
+        for (int i = threadIdx.x; i < T * n_cells * (CW / 4); i += blockDim.x) z[i] = make_uint4(0u, 0u, 0u, 0u);
+    }
 
     // features of this lane: T tuples of A consecutive sampled features.  Staged slot of feature i
     // of tuple-lane l: i * TL + l.
