@@ -1,6 +1,7 @@
 """Kernel-level parity through the C ABI: binning/packing, histograms, legacy predictors."""
 
 import ctypes as C
+import os
 
 import numpy as np
 import pytest
@@ -250,3 +251,34 @@ def test_scorer_candidates_match_oracle_bit_for_bit(case, round_idx, depth):
         if (np.float32(g["score"]).view(np.int32) != s.view(np.int32)) or int(g["k"]) != k or int(g["left_count"]) != c:
             bad.append((p, n, float(g["score"]), int(g["k"]), int(g["left_count"]), float(s), k, c))
     assert not bad, f"{len(bad)} of {len(want)} candidates differ, first: {bad[:5]}"
+
+
+_SHAPE_SCRIPT = """
+import sys
+sys.path.insert(0, {root!r})
+from tests.test_gpu_kernels import _hist_case
+_hist_case(7000, 70, 3, 5, 2, seed=11)
+_hist_case(5000, 40, 2, 16, 1, seed=12)
+_hist_case(9000, 300, 4, 5, 4, seed=13)
+_hist_case(6000, 24, 3, 3, 9, seed=14)
+_hist_case(4100, 16, 2, 5, 30, seed=15)
+print("ok")
+"""
+
+
+@pytest.mark.parametrize("shape", ["1 8 1", "1 4 2", "1 1 4", "2 4 1", "2 2 2", "2 1 4", "2 4 2", "1 8 2", "1 2 1"])
+def test_histogram_exact_in_every_launch_shape(shape):
+    """The launcher picks the shape <features per joint code, tuples per lane, row phases> of the
+    lane kernel by a cost model, so a given test size exercises one shape only.  The tuning
+    override forces each shape in turn (it is read once per process, hence the child process) and
+    the same exact-integer comparison runs on several sizes; the launch log must show that the
+    forced shape really ran."""
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, PACKBOOST_HIST_SHAPE=shape)
+    res = subprocess.run([sys.executable, "-c", _SHAPE_SCRIPT.format(root=root)], env=env, capture_output=True,
+                         text=True, timeout=600)
+    assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-4000:]
+    assert res.stdout.strip().endswith("ok")
+    assert "hist_lane_kernel<%s>" % shape.replace(" ", ",") in res.stderr, res.stderr[-2000:]
