@@ -462,3 +462,20 @@ def test_helper_form_direction_term_matches_the_oracle(name, monkeypatch):
     np.testing.assert_array_equal(booster.split_records()["score"].view(np.int32),
                                   np.asarray([r["score"] for r in model.depth_records], dtype=np.float32).view(np.int32))
     np.testing.assert_array_equal(booster.train_predictions().view(np.int32), model.train_preds.view(np.int32))
+
+
+@pytest.mark.parametrize("shape", ["1 8 1", "2 4 1", "2 2 2", "1 2 4"])
+def test_fit_is_bit_identical_in_forced_histogram_shapes(shape):
+    """The fused flush of the histogram kernel reads the cells in the layout of the launch shape
+    (private columns, or one column shared by two row phases).  The bit-for-bit comparison with
+    the exact-sum oracle and the golden comparison run again in a child process that forces one
+    shape wherever it fits (the override is read once per process)."""
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, PACKBOOST_HIST_SHAPE=shape)
+    res = subprocess.run([sys.executable, "-m", "pytest", os.path.join(root, "tests", "test_gpu_fit_parity.py"), "-q", "-x", "-s",
+                          "-m", "gpu", "-k", "exact_sum_oracle or matches_reference_golden"], env=env, cwd=root,
+                         capture_output=True, text=True, timeout=1200)
+    assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-2000:]
+    assert "hist_lane_kernel<%s>" % shape.replace(" ", ",") in res.stderr + res.stdout, "forced shape never launched"
