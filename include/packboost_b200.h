@@ -234,7 +234,9 @@ int pb_depth_clear_candidates(const pb_train_state* st, int64_t depth, int64_t n
  * Nothing is allocated or freed.  A shape whose single-feature scratch at `depth`,
  *   (1 << depth) * (n_eras * (max_bins * 12 + n_thresholds * 8) + n_thresholds * 12) + 1280 bytes
  * (histogram, per-era gain table, era-summed left counts and gradient sums, alignment), exceeds
- * the array is rejected with PB_ERR_ARG.  The first call on a device looks up the array's device
+ * the array is rejected with PB_ERR_ARG.  (Where the histogram kernel computes the gains itself
+ * (few bins, one tile per era) the histogram term max_bins * 12 drops out and
+ * (1 << depth) * n_thresholds * 3072 bytes of table padding are added.)  The first call on a device looks up the array's device
  * address (cudaGetSymbolAddress) with that device current; make that first call outside any
  * stream capture.  All calls in a process share the one array, which keeps whatever the previous
  * call left in it: the kernels rewrite every cell they later read, but two calls whose kernels
