@@ -974,6 +974,9 @@ int launch_score(const ScoreLaunch& s, cudaStream_t stream) {
     if (unit) {
         int npc = kUnitSlotsMax / K;
         if (npc > s.n_nodes_max) npc = s.n_nodes_max;
+        // A feature shard of a multi-GPU run has fewer features than the GPU has SMs: spread the nodes
+        // over more CTAs until every SM has one (a CTA with many slots is bound by its own issue rate)
+        while (npc > 2 && (int64_t)s.n_feat * ((s.n_nodes_max + npc - 1) / npc) < 148) npc >>= 1;
         c.nodes_per_cta = npc;
         int ec = (int)((16 * 1024) / ((size_t)npc * K * sizeof(float2))) / 8 * 8;  // multiple of the unrolled group
         if (ec < 8) ec = 8;
