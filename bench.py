@@ -481,11 +481,25 @@ def main():
         dist.destroy_process_group()
 
 
+def source_digest(path):
+    """sha256 of a C++/CUDA source without its // comments and blank lines, so that editing a
+    comment does not look like a kernel change."""
+    import hashlib
+    import re
+    lines = []
+    for line in open(path, encoding="utf-8"):
+        code = re.sub(r"//.*$", "", line).strip()
+        if code:
+            lines.append(code)
+    return hashlib.sha256("\n".join(lines).encode()).hexdigest()
+
+
 def hist_traffic(n_rows, world):
     """DRAM bytes per histogram launch from the committed ncu summary of the kernel that is timed
     (read + written at the captured row count, scaled by rows: the traffic is proportional to rows x
-    sampled features).  The summary records the sha256 of the kernel source it was taken from; when
-    the source has changed since, the figure is withheld and the reason is given instead."""
+    sampled features).  The summary records the sha256 of the kernel source it was taken from
+    (comments and blank lines left out, see source_digest); when the code has changed since, the
+    figure is withheld and the reason is given instead."""
     import hashlib
     import re
     path = os.path.join(ROOT, "profiles", "hist_lane_kernel_fused_config3_small.md")
@@ -498,7 +512,7 @@ def hist_traffic(n_rows, world):
     m_sha = re.search(r"hist_cu_sha256:\s*([0-9a-f]+)", text)
     if not (m_bytes and m_rows and m_sha):
         return None, "the committed ncu summary lacks the traffic fields"
-    now = hashlib.sha256(open(src, "rb").read()).hexdigest()
+    now = source_digest(src)
     if not now.startswith(m_sha.group(1)):
         return None, "hist.cu has changed since the committed ncu capture: traffic withheld until it is re-captured"
     return float(m_bytes.group(1)) * n_rows / float(m_rows.group(1)) / world, \

@@ -1,14 +1,10 @@
 // Per-(feature, node, era, bin) histograms of counts and fixed-point gradient sums.
 //
 // Rows are ordered by era, so an era is a contiguous row range.  One CTA owns one row tile of
-// one era (at most kTileRowsMax rows) and a contiguous range of the sampled features.  Every
-// thread owns one 16-byte chunk of codes per feature (32 rows of 4-bit codes, 16 rows of 8-bit
-// codes); the slot and gradient of those rows are loaded once and stay in registers while the
-// thread walks the CTA's features, prefetching the next feature's chunk while it accumulates
-// the current one.  Features are accumulated in groups in shared memory and each group is
-// written (or, when an era is cut into several tiles, atomically added) to the global
-// histogram.  Every cell is an integer, so the result does not depend on the order of the
-// additions.
+// one era (at most kTileRowsMax rows) and a contiguous range of the sampled features, accumulates
+// them in shared memory and writes (or, when an era is cut into several tiles, atomically adds)
+// the result to the global histogram.  Every cell is an integer, so the result does not depend
+// on the order of the additions.
 //
 // Shared-memory cell: two 32-bit words updated with one native 32-bit shared atomic each
 // (64-bit shared atomics are an order of magnitude slower on this part):
@@ -22,10 +18,13 @@
 //  * hist_lane_kernel (few cells per feature: nodes * bins^A <= kLaneCellsMax): a lane owns a
 //    tuple of A features and a private column of cells (bank == lane, so the shared atomics of a
 //    warp never conflict); all lanes of a warp walk the same rows, whose state (cell base, word A,
-//    word B) is staged per warp and read with one broadcast load.  With A > 1 the cell index is
+//    word B) is staged per warp and read with one broadcast load; the codes reach the lanes through
+//    a block staged in shared memory by whole-line asynchronous copies.  With A > 1 the cell index is
 //    the joint code of the tuple, one pair of atomics serves A features, and the per-feature
 //    histograms are the marginals of the joint table, taken when the tile is flushed.
-//  * hist_kernel (everything else): lanes own 16-byte chunks of rows of one feature; cells of a
+//  * hist_kernel (everything else): a thread owns one 16-byte chunk of codes per feature (32 rows
+//    of 4-bit codes, 16 rows of 8-bit codes); the slot and gradient of those rows stay in registers
+//    while the thread walks the CTA's features, prefetching the next feature's chunk.  Cells of a
 //    feature are shared by the CTA and, when few, replicated ("copies") to thin out conflicts.
 //
 // Output layout: [feature][era][node_stride][bin] for both arrays.
