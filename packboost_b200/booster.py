@@ -33,6 +33,7 @@ import logging
 import json
 import math
 import os
+import sys
 from dataclasses import dataclass, field
 from time import perf_counter
 from typing import Callable, Iterable, List, Sequence, Tuple
@@ -357,8 +358,7 @@ class _DeviceTrainer:
             self.prof = None
 
     def __del__(self):
-        import sys
-        if sys.is_finalizing():   # (the CUDA context may be gone already; the process is ending anyway)
+        if sys is None or sys.is_finalizing():   # (the CUDA context may be gone already; the process is ending anyway)
             return
         try:
             self.disable_profile()
@@ -582,16 +582,20 @@ def _tree_from_log(head, winners, max_depth: int) -> tuple[Tree, list[int]]:
         if n_ctx[d] == 0:
             break
         base = (1 << d) - 1
-        for w in winners[base: base + n_ctx[d]]:
-            nid = int(w["tree_node"])
-            if int(w["feature"]) < 0:
-                tb.set_leaf(nid, float(w["left_value"]))
+        sl = winners[base: base + n_ctx[d]]
+        # (field columns as plain lists: element access on structured records is what costs here)
+        for nid, feat, thr, lid, rid, lv, rv in zip(sl["tree_node"].tolist(), sl["feature"].tolist(),
+                                                    sl["threshold"].tolist(), sl["left_id"].tolist(),
+                                                    sl["right_id"].tolist(), sl["left_value"].tolist(),
+                                                    sl["right_value"].tolist()):
+            if feat < 0:
+                tb.set_leaf(nid, lv)
                 continue
-            l, r = tb.split(nid, int(w["feature"]), int(w["threshold"]))
-            if l != int(w["left_id"]) or r != int(w["right_id"]):
+            l, r = tb.split(nid, feat, thr)
+            if l != lid or r != rid:
                 raise RuntimeError("device and host child numbering disagree")
-            tb.set_leaf(l, float(w["left_value"]))
-            tb.set_leaf(r, float(w["right_value"]))
+            tb.set_leaf(l, lv)
+            tb.set_leaf(r, rv)
     if len(tb.nodes) != int(head["n_tree_nodes"]):
         raise RuntimeError("device and host tree sizes disagree")
     return tb.build(), n_ctx
